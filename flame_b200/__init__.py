@@ -1,0 +1,29 @@
+"""B200-native activation offload/restore path behind the flame-core API.
+
+Only what the hot path needs: the CUDA kernels and C ABI (``csrc/``,
+``libflame_offload.so``), and Python mirrors of the reference interface
+(``ActivationOffloadPool``, ``PinnedHostBuffer``, ``PinnedPool``,
+``CheckpointPolicy`` / ``CheckpointManager``, ``checkpoint_offload``).
+
+Importing the package does not load CUDA.  Every operation goes through the
+shared library; there is no CPU or eager fallback, and a missing library is an
+ImportError.
+"""
+from .pinned import PinnedAllocFlags, PinnedHostBuffer, StagingDeviceBuf  # noqa: F401
+from .pinned_pool import PinnedPool  # noqa: F401
+from .activation_offload import (  # noqa: F401
+    ActivationOffloadPool,
+    OffloadCompression,
+    OffloadHandle,
+    OffloadError,
+    InvalidInput,
+    InvalidOperation,
+    Unsupported,
+    CudaError,
+)
+
+__all__ = [
+    "PinnedAllocFlags", "PinnedHostBuffer", "StagingDeviceBuf", "PinnedPool",
+    "ActivationOffloadPool", "OffloadCompression", "OffloadHandle",
+    "OffloadError", "InvalidInput", "InvalidOperation", "Unsupported", "CudaError",
+]

@@ -1,0 +1,209 @@
+"""ActivationOffloadPool: mirror of src/activation_offload.rs:323-760.
+
+Same constructor arguments, accessors, ``push`` / ``pull`` / ``clear`` and
+error cases as the reference; the work happens in libflame_offload.so
+(flame_offload_pool_*).  Tensors are torch CUDA tensors; only their data
+pointer, element count and dtype cross the C ABI.
+
+Differences from the reference, all additive:
+
+* two more compression modes, ``INT8_B128`` and ``FP8_B128`` (per-128-element
+  fp32 scales), next to ``NONE`` and the fixed-scale ``FP8``;
+* ``pull_into`` restores into a tensor the caller already owns, optionally
+  without making the current stream wait (``defer_wait``) so that a restore can
+  be issued ahead of its consumer and joined later with ``wait_ready``;
+* a non-contiguous source is refused (the reference copies from the storage
+  base pointer and ignores view offsets, src/activation_offload.rs:771-800);
+* the pool keeps the source tensor alive only until its device-to-host copy
+  has finished (the reference holds it until pull,
+  src/activation_offload.rs:600-605), so offloading actually frees device memory.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib
+from .errors import (CudaError, InvalidInput, InvalidOperation, OffloadError, Timeout,  # noqa: F401
+                     Unsupported, raise_for_status)
+
+
+class OffloadCompression(enum.IntEnum):
+    """src/activation_offload.rs:89-96 plus the two per-block codecs."""
+
+    NONE = 0
+    FP8 = 1          # reference mode: fixed per-tensor scale 8/448
+    INT8_B128 = 2
+    FP8_B128 = 3
+
+
+@dataclass(frozen=True)
+class OffloadHandle:
+    """Copyable ticket returned by push (src/activation_offload.rs:292-303)."""
+
+    slot: int
+    epoch: int
+
+    def _c(self) -> _lib.Handle:
+        return _lib.Handle(self.slot, self.epoch)
+
+
+def _dtype_tag(t) -> int:
+    import torch
+
+    if t.dtype == torch.bfloat16:
+        return 0
+    if t.dtype == torch.float32:
+        return 1
+    raise Unsupported(f"ActivationOffloadPool::push: dtype {t.dtype} not supported (BF16/F32 only)")
+
+
+class ActivationOffloadPool:
+    def __init__(self, device, num_slots: int, max_bytes: int,
+                 compression: OffloadCompression = OffloadCompression.NONE, *,
+                 chunk_bytes: int = 0, staging_tiles: int = 0, codec_flags: int = 0,
+                 host_budget_bytes: int = 0, host_alloc_flags: int = 0, codec_max_ctas: int = 0,
+                 numa_node: int = -2):
+        import torch
+
+        self._torch = torch
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise Unsupported("ActivationOffloadPool needs a CUDA device; there is no CPU path")
+        index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.device = torch.device("cuda", index)
+        cfg = _lib.PoolConfig(C.sizeof(_lib.PoolConfig), index, chunk_bytes, staging_tiles, codec_flags,
+                              host_budget_bytes, host_alloc_flags, codec_max_ctas, numa_node, 0)
+        self._lib = _lib.lib()
+        with torch.cuda.device(index):
+            self._h = self._lib.flame_offload_pool_create(num_slots, max_bytes, int(compression), C.byref(cfg))
+        if not self._h:
+            msg = _lib.last_error()
+            if "must be > 0" in msg or "chunk_bytes" in msg or "unknown compression" in msg:
+                raise InvalidInput(msg)
+            raise CudaError(msg)
+        self.compression = OffloadCompression(compression)
+        self._meta: dict[int, tuple] = {}        # slot -> (shape, dtype)
+        self._keep_alive: dict[int, tuple] = {}  # slot -> (handle, tensor)
+
+    # -- accessors (src/activation_offload.rs:429-455) ---------------------------------
+    def num_slots(self) -> int:
+        return self._lib.flame_offload_pool_num_slots(self._h)
+
+    def slot_bytes(self) -> int:
+        return self._lib.flame_offload_pool_slot_bytes(self._h)
+
+    def host_bytes(self) -> int:
+        return self._lib.flame_offload_pool_host_bytes(self._h)
+
+    def in_flight(self) -> int:
+        return self._lib.flame_offload_pool_in_flight(self._h)
+
+    # -- push / pull -----------------------------------------------------------------------
+    def _stream(self) -> int:
+        return self._torch.cuda.current_stream(self.device).cuda_stream
+
+    def _sweep_keep_alive(self) -> None:
+        """Drops source tensors whose device-to-host copy has completed."""
+        for slot in list(self._keep_alive):
+            handle, _ = self._keep_alive[slot]
+            if self._lib.flame_offload_pool_source_released(self._h, handle._c()) != 0:
+                del self._keep_alive[slot]
+
+    def push(self, tensor) -> OffloadHandle:
+        """Asynchronously offload `tensor`; never blocks the host (activation_offload.rs:465-611)."""
+        tag = _dtype_tag(tensor)
+        if tensor.device != self.device:
+            raise InvalidInput(f"ActivationOffloadPool::push: tensor on {tensor.device}, pool on {self.device}")
+        if not tensor.is_contiguous():
+            raise InvalidInput("ActivationOffloadPool::push: tensor must be contiguous")
+        self._sweep_keep_alive()
+        h = _lib.Handle()
+        st = self._lib.flame_offload_pool_push(self._h, tensor.data_ptr() if tensor.numel() else None,
+                                              tensor.numel(), tag, self._stream(), C.byref(h))
+        raise_for_status(st, _lib.last_error())
+        handle = OffloadHandle(h.slot, h.epoch)
+        self._meta[h.slot] = (tuple(tensor.shape), tensor.dtype)
+        self._keep_alive[h.slot] = (handle, tensor.detach())
+        return handle
+
+    def pull_into(self, handle: OffloadHandle, dst, defer_wait: bool = False) -> None:
+        """Restore into `dst` (contiguous, same dtype, at least as many bytes)."""
+        if not dst.is_contiguous() or dst.device != self.device:
+            raise InvalidInput("ActivationOffloadPool::pull_into: destination must be a contiguous tensor on the pool's device")
+        st = self._lib.flame_offload_pool_pull_into(self._h, handle._c(), dst.data_ptr(), dst.numel() * dst.element_size(),
+                                                   self._stream(), 1 if defer_wait else 0)
+        raise_for_status(st, _lib.last_error())
+        if not defer_wait:
+            self._keep_alive.pop(handle.slot, None)
+        self._meta.pop(handle.slot, None)
+
+    def pull(self, handle: OffloadHandle):
+        """Restore into a freshly allocated tensor (activation_offload.rs:619-731)."""
+        info = _lib.SlotInfo()
+        raise_for_status(self._lib.flame_offload_pool_slot_info(self._h, handle._c(), C.byref(info)), _lib.last_error())
+        shape, dtype = self._meta[handle.slot]
+        out = self._torch.empty(shape, dtype=dtype, device=self.device)
+        self.pull_into(handle, out)
+        return out
+
+    def wait_ready(self, slot: int) -> None:
+        """Makes the current stream wait for the latest restore issued from `slot`."""
+        raise_for_status(self._lib.flame_offload_pool_wait_ready(self._h, slot, self._stream()), _lib.last_error())
+        self._keep_alive.pop(slot, None)
+
+    def clear(self) -> None:
+        """Invalidate every handle, free every slot; does not synchronise (activation_offload.rs:742-760)."""
+        raise_for_status(self._lib.flame_offload_pool_clear(self._h), _lib.last_error())
+        self._meta.clear()
+        self._keep_alive.clear()
+
+    # -- extras ------------------------------------------------------------------------------
+    def synchronize(self, timeout_s: float = 60.0) -> None:
+        raise_for_status(self._lib.flame_offload_pool_synchronize(self._h, timeout_s), _lib.last_error())
+
+    def source_released(self, handle: OffloadHandle) -> bool:
+        r = self._lib.flame_offload_pool_source_released(self._h, handle._c())
+        if r < 0:
+            raise_for_status(-r, _lib.last_error())
+        return r == 1
+
+    def slot_info(self, handle: OffloadHandle) -> dict:
+        info = _lib.SlotInfo()
+        raise_for_status(self._lib.flame_offload_pool_slot_info(self._h, handle._c(), C.byref(info)), _lib.last_error())
+        return {n: getattr(info, n) for n, _ in _lib.SlotInfo._fields_}
+
+    def read_slot(self, handle: OffloadHandle, timeout_s: float = 60.0):
+        """What the pinned slab holds for `handle`, in canonical order: (codes, scales) numpy arrays."""
+        info = self.slot_info(handle)
+        if self.compression == OffloadCompression.NONE:
+            codes = np.empty(info["bytes"], np.uint8)
+            scales = None
+        else:
+            codes = np.empty(info["numel"], np.uint8)
+            nsc = 1 if self.compression == OffloadCompression.FP8 else (info["numel"] + 127) // 128
+            scales = np.empty(nsc, np.float32)
+        st = self._lib.flame_offload_pool_read_slot(self._h, handle._c(), codes.ctypes.data,
+                                                   scales.ctypes.data if scales is not None else None, timeout_s)
+        raise_for_status(st, _lib.last_error())
+        return codes, scales
+
+    def stats(self) -> dict:
+        s = _lib.Stats()
+        raise_for_status(self._lib.flame_offload_pool_stats(self._h, C.byref(s)), _lib.last_error())
+        return {n: getattr(s, n) for n, _ in _lib.Stats._fields_}
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._keep_alive.clear()
+            self._lib.flame_offload_pool_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

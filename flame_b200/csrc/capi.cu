@@ -1,0 +1,133 @@
+// C ABI: error text, pinned host memory, async copies and the codec entry
+// points.  The pool, the pinned cache and the policy live in their own files.
+#include <atomic>
+#include <cstring>
+
+#include "codec_kernels.cuh"
+#include "common.h"
+
+namespace flame_b200 {
+
+namespace {
+thread_local std::string t_last_error;
+std::atomic<int> g_fault_kind{FLAME_OFFLOAD_FAULT_NONE};
+std::atomic<int> g_fault_countdown{0};
+}  // namespace
+
+void set_last_error(const std::string& msg) { t_last_error = msg; }
+
+FlameOffloadStatus fail(FlameOffloadStatus st, const std::string& msg) {
+  t_last_error = msg;
+  return st;
+}
+
+FlameOffloadStatus fail_cuda(cudaError_t e, const char* what) {
+  t_last_error = std::string(what) + ": " + cudaGetErrorName(e) + " (" + std::to_string((int)e) + ")";
+  return FLAME_OFFLOAD_ERR_CUDA;
+}
+
+bool fault_fires(int kind) {
+  if (g_fault_kind.load(std::memory_order_relaxed) != kind) return false;
+  if (g_fault_countdown.fetch_sub(1) == 1) {
+    g_fault_kind.store(FLAME_OFFLOAD_FAULT_NONE);
+    return true;
+  }
+  return false;
+}
+
+cudaError_t memcpy_async_checked(void* dst, const void* src, size_t bytes, cudaMemcpyKind kind, cudaStream_t s) {
+  if (fault_fires(FLAME_OFFLOAD_FAULT_MEMCPY)) return cudaErrorUnknown;
+  return cudaMemcpyAsync(dst, src, bytes, kind, s);
+}
+
+cudaError_t host_alloc_checked(void** p, size_t bytes, unsigned flags) {
+  if (fault_fires(FLAME_OFFLOAD_FAULT_HOST_ALLOC)) { *p = nullptr; return cudaErrorMemoryAllocation; }
+  return cudaHostAlloc(p, bytes, flags);
+}
+
+}  // namespace flame_b200
+
+using namespace flame_b200;
+
+extern "C" {
+
+const char* flame_offload_last_error(void) { return t_last_error.c_str(); }
+
+void flame_offload_inject_fault(int kind, int countdown) {
+  g_fault_countdown.store(countdown > 0 ? countdown : 1);
+  g_fault_kind.store(kind);
+}
+
+// ---- pinned host memory (src/cuda/pinned_host.cu:4-45 in the reference) ------
+
+void* flame_cuda_alloc_pinned_host(size_t size, unsigned int flags) {
+  void* p = nullptr;
+  return host_alloc_checked(&p, size, flags) == cudaSuccess ? p : nullptr;
+}
+
+int flame_cuda_free_pinned_host(void* ptr) { return (int)cudaFreeHost(ptr); }
+
+int flame_cuda_memcpy_async(void* dst, const void* src, size_t bytes, int kind, void* stream) {
+  cudaMemcpyKind k = cudaMemcpyDefault;
+  if (kind == 1) k = cudaMemcpyHostToDevice;
+  else if (kind == 2) k = cudaMemcpyDeviceToHost;
+  else if (kind == 3) k = cudaMemcpyDeviceToDevice;
+  return (int)memcpy_async_checked(dst, src, bytes, k, (cudaStream_t)stream);
+}
+
+int flame_cuda_host_register(void* ptr, size_t bytes, unsigned int flags) { return (int)cudaHostRegister(ptr, bytes, flags); }
+int flame_cuda_host_unregister(void* ptr) { return (int)cudaHostUnregister(ptr); }
+
+// ---- FlameCudaStatus-style copies (src/ffi/cuda_ffi.c:90-109) ------------------
+
+static FlameOffloadStatus copy_status(void* dst, const void* src, uint64_t bytes, cudaMemcpyKind k, void* stream, const char* what) {
+  if (!dst || !src || bytes == 0) return fail(FLAME_OFFLOAD_ERR_INVALID, std::string(what) + ": null pointer or zero bytes");
+  cudaError_t e = memcpy_async_checked(dst, src, (size_t)bytes, k, (cudaStream_t)stream);
+  return e == cudaSuccess ? FLAME_OFFLOAD_OK : fail_cuda(e, what);
+}
+
+FlameOffloadStatus flame_h2d_async(void* dst, const void* src, uint64_t bytes, void* stream) {
+  return copy_status(dst, src, bytes, cudaMemcpyHostToDevice, stream, "flame_h2d_async");
+}
+FlameOffloadStatus flame_d2h_async(void* dst, const void* src, uint64_t bytes, void* stream) {
+  return copy_status(dst, src, bytes, cudaMemcpyDeviceToHost, stream, "flame_d2h_async");
+}
+FlameOffloadStatus flame_d2d_async(void* dst, const void* src, uint64_t bytes, void* stream) {
+  return copy_status(dst, src, bytes, cudaMemcpyDeviceToDevice, stream, "flame_d2d_async");
+}
+
+// ---- element-wise FP8 (src/cuda/fp8_quant.cu:74-93, src/cuda/fp8_dequant.cu:41-59)
+
+int flame_bf16_to_fp8(const void* input, void* output, float inv_scale, size_t n, void* stream) {
+  if (n == 0) return 0;
+  if (fault_fires(FLAME_OFFLOAD_FAULT_KERNEL)) return (int)cudaErrorLaunchFailure;
+  return (int)launch_bf16_to_fp8(input, output, inv_scale, n, (cudaStream_t)stream, 0);
+}
+
+int flame_fp8_to_bf16(const void* input, void* output, float scale, size_t n, void* stream) {
+  if (n == 0) return 0;
+  if (fault_fires(FLAME_OFFLOAD_FAULT_KERNEL)) return (int)cudaErrorLaunchFailure;
+  return (int)launch_fp8_to_bf16(input, output, scale, n, (cudaStream_t)stream, 0);
+}
+
+// ---- per-128-block codecs --------------------------------------------------------
+
+int flame_act_quant_int8_b128(const void* in, void* codes, void* scales, size_t n, unsigned int flags, void* stream) {
+  return (int)launch_compress(kCodecInt8, in, codes, scales, n, flags, (cudaStream_t)stream, 0);
+}
+int flame_act_dequant_int8_b128(const void* codes, const void* scales, void* out, size_t n, void* stream) {
+  return (int)launch_dequant(kCodecInt8, codes, scales, out, n, (cudaStream_t)stream, 0);
+}
+int flame_act_quant_fp8_b128(const void* in, void* codes, void* scales, size_t n, unsigned int flags, void* stream) {
+  return (int)launch_compress(kCodecFp8, in, codes, scales, n, flags, (cudaStream_t)stream, 0);
+}
+int flame_act_dequant_fp8_b128(const void* codes, const void* scales, void* out, size_t n, void* stream) {
+  return (int)launch_dequant(kCodecFp8, codes, scales, out, n, (cudaStream_t)stream, 0);
+}
+
+size_t flame_act_packed_scales_offset(size_t n) { return (n + 255u) & ~(size_t)255u; }
+size_t flame_act_packed_bytes(size_t n) { return flame_act_packed_scales_offset(n) + 4u * ((n + 127u) / 128u); }
+
+int flame_act_set_max_ctas(int max_ctas) { return set_max_ctas(max_ctas); }
+
+}  // extern "C"

@@ -1,0 +1,633 @@
+// Activation offload pool: host-side state machine and the chunked,
+// double-buffered copy/codec pipeline behind flame_offload_pool_*.
+//
+// Semantics follow ActivationOffloadPool in the reference
+// (src/activation_offload.rs:323-760): fixed number of slots, LIFO free stack,
+// epoch-stamped handles, Idle/Pushed slot states, push never blocks the host,
+// pool-full / stale-handle / double-pull are errors.  What differs is below the
+// API:
+//   * one pinned slab carved into equal chunks; a slot owns a list of chunks, so
+//     pinned memory is consumed by what is stored, not by slots x max size;
+//   * four non-blocking streams (compress, D2H, H2D, dequantise) so both copy
+//     engines and the codec kernels run concurrently; a ring of device staging
+//     tiles per direction; every hand-over between streams is an event, the
+//     host never waits;
+//   * restore writes into the caller's destination; in the compressed modes
+//     the H2D of chunk k+1 overlaps the dequantise of chunk k;
+//   * the source tensor is needed only until its D2H-complete event, which the
+//     caller can query, instead of until pull.
+//
+// There is no device-side waiting anywhere in this design (no flags, no spin
+// loops): ordering is CUDA events only, and every host wait is a bounded poll.
+
+#include <sys/syscall.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <cctype>
+#include <chrono>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <thread>
+#include <vector>
+
+#include "codec_kernels.cuh"
+#include "common.h"
+
+namespace flame_b200 {
+namespace {
+
+constexpr uint64_t kDefaultChunkBytes = 16ull << 20;
+constexpr uint32_t kDefaultTiles = 3;
+constexpr float kLegacyFp8Scale = 8.0f / 448.0f;  // src/activation_offload.rs:548
+
+size_t packed_scales_offset(size_t n) { return (n + 255u) & ~(size_t)255u; }
+size_t packed_bytes(size_t n) { return packed_scales_offset(n) + 4u * ((n + 127u) / 128u); }
+
+struct Event {
+  cudaEvent_t ev = nullptr;
+  bool recorded = false;
+  cudaError_t create() { return cudaEventCreateWithFlags(&ev, cudaEventDisableTiming); }
+  cudaError_t record(cudaStream_t s) {
+    cudaError_t e = cudaEventRecord(ev, s);
+    if (e == cudaSuccess) recorded = true;
+    return e;
+  }
+  // Makes `s` wait for the last record; a never-recorded event orders nothing.
+  cudaError_t make_wait(cudaStream_t s) const { return recorded ? cudaStreamWaitEvent(s, ev, 0) : cudaSuccess; }
+  void destroy() { if (ev) cudaEventDestroy(ev); ev = nullptr; }
+};
+
+enum class SlotState { Idle, Pushed };
+
+struct Slot {
+  SlotState state = SlotState::Idle;
+  uint64_t numel = 0, bytes = 0, stored_bytes = 0;
+  int dtype = 0;
+  float fp8_scale = 0.0f;
+  std::vector<uint32_t> chunks;
+  Event producer;  // compute stream, at push: the source is complete
+  Event d2h_done;  // D2H stream: the source has been read, the pinned copy is complete
+  Event consumer;  // compute stream, at pull: the destination may be written
+  Event h2d_done;  // H2D stream: the pinned chunks have been read
+  Event ready;     // the destination holds the restored tensor
+};
+
+struct Tile {
+  uint8_t* dev = nullptr;
+  Event full, free_;
+};
+
+// Asks the kernel to prefer `node` for this thread's next allocations.  Best
+// effort: containers may forbid the call, in which case nothing changes.
+void set_preferred_node(int node) {
+#ifdef SYS_set_mempolicy
+  if (node < 0) { syscall(SYS_set_mempolicy, 0 /*MPOL_DEFAULT*/, nullptr, 0); return; }
+  unsigned long mask[16] = {0};
+  if (node >= (int)(sizeof(mask) * 8)) return;
+  mask[node / (8 * sizeof(unsigned long))] |= 1ul << (node % (8 * sizeof(unsigned long)));
+  syscall(SYS_set_mempolicy, 1 /*MPOL_PREFERRED*/, mask, sizeof(mask) * 8);
+#else
+  (void)node;
+#endif
+}
+
+int gpu_numa_node(int device) {
+  char bdf[32] = {0};
+  if (cudaDeviceGetPCIBusId(bdf, sizeof(bdf), device) != cudaSuccess) return -1;
+  for (char* p = bdf; *p; ++p) *p = (char)tolower(*p);
+  char path[128];
+  snprintf(path, sizeof(path), "/sys/bus/pci/devices/%s/numa_node", bdf);
+  FILE* f = fopen(path, "r");
+  if (!f) return -1;
+  int node = -1;
+  if (fscanf(f, "%d", &node) != 1) node = -1;
+  fclose(f);
+  return node;
+}
+
+}  // namespace
+}  // namespace flame_b200
+
+using namespace flame_b200;
+
+struct FlameOffloadPool {
+  std::mutex mu;
+  int device = 0;
+  int compression = 0;
+  size_t num_slots = 0, slot_bytes = 0;
+  uint64_t chunk_src_bytes = 0;   // source bytes covered by one chunk
+  uint64_t chunk_elems = 0;       // BF16 elements per chunk (compressed modes)
+  uint64_t host_chunk_bytes = 0;  // pinned bytes per chunk
+  uint32_t codec_flags = 0;
+  int codec_max_ctas = 0;
+
+  uint8_t* slab = nullptr;
+  size_t slab_bytes = 0;
+  std::vector<uint32_t> free_chunks;      // stack
+  std::vector<int32_t> chunk_last_reader;  // slot whose restore last read the chunk, -1 = none
+  size_t total_chunks = 0;
+
+  std::vector<Slot> slots;
+  std::vector<size_t> free_stack;
+  uint64_t epoch = 1;
+
+  cudaStream_t s_quant = nullptr, s_d2h = nullptr, s_h2d = nullptr, s_dequant = nullptr;
+  std::vector<Tile> out_tiles, in_tiles;
+  uint64_t out_next = 0, in_next = 0;
+
+  FlameOffloadStats stats{};
+
+  bool compressed() const { return compression != FLAME_OFFLOAD_COMPRESSION_NONE; }
+  uint8_t* chunk_ptr(uint32_t c) const { return slab + (size_t)c * host_chunk_bytes; }
+
+  // Pinned bytes one chunk of `e` elements (or `b` raw bytes) occupies.
+  size_t stored_for(uint64_t e_or_bytes) const {
+    switch (compression) {
+      case FLAME_OFFLOAD_COMPRESSION_NONE: return e_or_bytes;
+      case FLAME_OFFLOAD_COMPRESSION_FP8: return e_or_bytes;
+      default: return packed_bytes(e_or_bytes);
+    }
+  }
+
+  void release_chunks(Slot& s, int32_t reader) {
+    for (auto it = s.chunks.rbegin(); it != s.chunks.rend(); ++it) {
+      chunk_last_reader[*it] = reader;
+      free_chunks.push_back(*it);
+    }
+    s.chunks.clear();
+  }
+
+  FlameOffloadStatus check_handle(FlameOffloadHandle h, const char* who) const {
+    if (h.epoch != epoch)
+      return fail(FLAME_OFFLOAD_ERR_STATE, std::string(who) + ": handle epoch " + std::to_string(h.epoch) +
+                  " is stale (current " + std::to_string(epoch) + "); was clear() called between push and pull?");
+    if (h.slot >= slots.size())
+      return fail(FLAME_OFFLOAD_ERR_STATE, std::string(who) + ": slot " + std::to_string(h.slot) + " out of range (" +
+                  std::to_string(slots.size()) + " slots)");
+    if (slots[h.slot].state != SlotState::Pushed)
+      return fail(FLAME_OFFLOAD_ERR_STATE, std::string(who) + ": slot " + std::to_string(h.slot) +
+                  " is Idle, expected Pushed; double pull, or handle reuse after clear?");
+    return FLAME_OFFLOAD_OK;
+  }
+};
+
+namespace {
+
+#define POOL_TRY(expr, what)                                  \
+  do {                                                        \
+    cudaError_t _e = (expr);                                  \
+    if (_e != cudaSuccess) { fail_cuda(_e, what); return _e; } \
+  } while (0)
+
+cudaError_t kernel_guard() { return fault_fires(FLAME_OFFLOAD_FAULT_KERNEL) ? cudaErrorLaunchFailure : cudaSuccess; }
+
+// Enqueue the offload of one tensor.  Returns the first CUDA error.
+cudaError_t enqueue_push(FlameOffloadPool& p, Slot& s, const uint8_t* src, cudaStream_t compute) {
+  POOL_TRY(s.producer.record(compute), "push: cudaEventRecord(producer)");
+  // A chunk that an earlier restore is still reading must not be overwritten.
+  {
+    std::vector<int32_t> seen;
+    for (uint32_t c : s.chunks) {
+      const int32_t r = p.chunk_last_reader[c];
+      if (r < 0 || std::find(seen.begin(), seen.end(), r) != seen.end()) continue;
+      seen.push_back(r);
+      POOL_TRY(p.slots[r].h2d_done.make_wait(p.s_d2h), "push: wait(h2d_done)");
+    }
+  }
+  const size_t nchunks = s.chunks.size();
+  if (!p.compressed()) {
+    POOL_TRY(s.producer.make_wait(p.s_d2h), "push: wait(producer)");
+    for (size_t k = 0; k < nchunks; ++k) {
+      const uint64_t off = k * p.chunk_src_bytes;
+      const uint64_t len = std::min<uint64_t>(p.chunk_src_bytes, s.bytes - off);
+      POOL_TRY(memcpy_async_checked(p.chunk_ptr(s.chunks[k]), src + off, len, cudaMemcpyDeviceToHost, p.s_d2h), "push: D2H");
+      p.stats.bytes_link_out += len;
+    }
+  } else {
+    POOL_TRY(s.producer.make_wait(p.s_quant), "push: wait(producer)");
+    for (size_t k = 0; k < nchunks; ++k) {
+      const uint64_t e0 = k * p.chunk_elems;
+      const uint64_t e = std::min<uint64_t>(p.chunk_elems, s.numel - e0);
+      Tile& t = p.out_tiles[p.out_next++ % p.out_tiles.size()];
+      POOL_TRY(t.free_.make_wait(p.s_quant), "push: wait(tile free)");
+      POOL_TRY(kernel_guard(), "push: compress kernel");
+      const void* in = src + 2 * e0;
+      size_t link = 0;
+      if (p.compression == FLAME_OFFLOAD_COMPRESSION_FP8) {
+        POOL_TRY(launch_bf16_to_fp8(in, t.dev, 1.0f / s.fp8_scale, e, p.s_quant, p.codec_max_ctas), "push: bf16_to_fp8");
+        link = e;
+      } else {
+        POOL_TRY(launch_compress(p.compression, in, t.dev, t.dev + packed_scales_offset(e), e, p.codec_flags,
+                                 p.s_quant, p.codec_max_ctas), "push: compress");
+        link = packed_bytes(e);
+      }
+      p.stats.codec_launches++;
+      POOL_TRY(t.full.record(p.s_quant), "push: record(tile full)");
+      POOL_TRY(t.full.make_wait(p.s_d2h), "push: wait(tile full)");
+      POOL_TRY(memcpy_async_checked(p.chunk_ptr(s.chunks[k]), t.dev, link, cudaMemcpyDeviceToHost, p.s_d2h), "push: D2H");
+      POOL_TRY(t.free_.record(p.s_d2h), "push: record(tile free)");
+      p.stats.bytes_link_out += link;
+    }
+  }
+  POOL_TRY(s.d2h_done.record(p.s_d2h), "push: record(d2h_done)");
+  p.stats.chunks_out += nchunks;
+  return cudaSuccess;
+}
+
+cudaError_t enqueue_pull(FlameOffloadPool& p, Slot& s, uint8_t* dst, cudaStream_t compute, unsigned flags) {
+  POOL_TRY(s.consumer.record(compute), "pull: cudaEventRecord(consumer)");
+  POOL_TRY(s.d2h_done.make_wait(p.s_h2d), "pull: wait(d2h_done)");
+  const size_t nchunks = s.chunks.size();
+  if (!p.compressed()) {
+    POOL_TRY(s.consumer.make_wait(p.s_h2d), "pull: wait(consumer)");
+    for (size_t k = 0; k < nchunks; ++k) {
+      const uint64_t off = k * p.chunk_src_bytes;
+      const uint64_t len = std::min<uint64_t>(p.chunk_src_bytes, s.bytes - off);
+      POOL_TRY(memcpy_async_checked(dst + off, p.chunk_ptr(s.chunks[k]), len, cudaMemcpyHostToDevice, p.s_h2d), "pull: H2D");
+      p.stats.bytes_link_in += len;
+    }
+    POOL_TRY(s.h2d_done.record(p.s_h2d), "pull: record(h2d_done)");
+    POOL_TRY(s.ready.record(p.s_h2d), "pull: record(ready)");
+  } else {
+    POOL_TRY(s.consumer.make_wait(p.s_dequant), "pull: wait(consumer)");
+    for (size_t k = 0; k < nchunks; ++k) {
+      const uint64_t e0 = k * p.chunk_elems;
+      const uint64_t e = std::min<uint64_t>(p.chunk_elems, s.numel - e0);
+      Tile& t = p.in_tiles[p.in_next++ % p.in_tiles.size()];
+      const size_t link = p.compression == FLAME_OFFLOAD_COMPRESSION_FP8 ? (size_t)e : packed_bytes(e);
+      POOL_TRY(t.free_.make_wait(p.s_h2d), "pull: wait(tile free)");
+      POOL_TRY(memcpy_async_checked(t.dev, p.chunk_ptr(s.chunks[k]), link, cudaMemcpyHostToDevice, p.s_h2d), "pull: H2D");
+      POOL_TRY(t.full.record(p.s_h2d), "pull: record(tile full)");
+      POOL_TRY(t.full.make_wait(p.s_dequant), "pull: wait(tile full)");
+      POOL_TRY(kernel_guard(), "pull: dequantise kernel");
+      void* out = dst + 2 * e0;
+      if (p.compression == FLAME_OFFLOAD_COMPRESSION_FP8)
+        POOL_TRY(launch_fp8_to_bf16(t.dev, out, s.fp8_scale, e, p.s_dequant, p.codec_max_ctas), "pull: fp8_to_bf16");
+      else
+        POOL_TRY(launch_dequant(p.compression, t.dev, t.dev + packed_scales_offset(e), out, e, p.s_dequant,
+                                p.codec_max_ctas), "pull: dequantise");
+      p.stats.codec_launches++;
+      POOL_TRY(t.free_.record(p.s_dequant), "pull: record(tile free)");
+      p.stats.bytes_link_in += link;
+    }
+    POOL_TRY(s.h2d_done.record(p.s_h2d), "pull: record(h2d_done)");
+    POOL_TRY(s.ready.record(p.s_dequant), "pull: record(ready)");
+  }
+  if (!(flags & FLAME_OFFLOAD_PULL_DEFER_WAIT)) POOL_TRY(s.ready.make_wait(compute), "pull: wait(ready)");
+  p.stats.chunks_in += nchunks;
+  return cudaSuccess;
+}
+
+void destroy_pool(FlameOffloadPool* p) {
+  for (auto& s : p->slots) { s.producer.destroy(); s.d2h_done.destroy(); s.consumer.destroy(); s.h2d_done.destroy(); s.ready.destroy(); }
+  for (auto* ring : {&p->out_tiles, &p->in_tiles})
+    for (auto& t : *ring) { t.full.destroy(); t.free_.destroy(); if (t.dev) cudaFree(t.dev); }
+  for (cudaStream_t s : {p->s_quant, p->s_d2h, p->s_h2d, p->s_dequant}) if (s) cudaStreamDestroy(s);
+  if (p->slab) cudaFreeHost(p->slab);
+  delete p;
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) switched = cudaSetDevice(dev) == cudaSuccess;
+  }
+  ~DeviceGuard() { if (switched) cudaSetDevice(prev); }
+};
+
+FlameOffloadStatus poll_streams(FlameOffloadPool* p, double timeout_s) {
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::duration<double>(timeout_s);
+  for (;;) {
+    bool busy = false;
+    for (cudaStream_t s : {p->s_quant, p->s_d2h, p->s_h2d, p->s_dequant}) {
+      cudaError_t e = cudaStreamQuery(s);
+      if (e == cudaErrorNotReady) busy = true;
+      else if (e != cudaSuccess) return fail_cuda(e, "synchronize: cudaStreamQuery");
+    }
+    if (!busy) return FLAME_OFFLOAD_OK;
+    if (std::chrono::steady_clock::now() >= deadline)
+      return fail(FLAME_OFFLOAD_ERR_TIMEOUT, "synchronize: pool streams still busy after the timeout");
+    std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+}
+
+FlameOffloadStatus poll_event(cudaEvent_t ev, double timeout_s, const char* what) {
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::duration<double>(timeout_s);
+  for (;;) {
+    cudaError_t e = cudaEventQuery(ev);
+    if (e == cudaSuccess) return FLAME_OFFLOAD_OK;
+    if (e != cudaErrorNotReady) return fail_cuda(e, what);
+    if (std::chrono::steady_clock::now() >= deadline) return fail(FLAME_OFFLOAD_ERR_TIMEOUT, std::string(what) + ": timed out");
+    std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+FlameOffloadPool* flame_offload_pool_create(size_t num_slots, size_t max_bytes, int compression, const FlameOffloadPoolConfig* cfg_in) {
+  // Argument checks of src/activation_offload.rs:371-380.
+  if (num_slots == 0) { fail(FLAME_OFFLOAD_ERR_INVALID, "ActivationOffloadPool::new: num_slots must be > 0"); return nullptr; }
+  if (max_bytes == 0) { fail(FLAME_OFFLOAD_ERR_INVALID, "ActivationOffloadPool::new: max_bytes must be > 0"); return nullptr; }
+  if (compression < 0 || compression > FLAME_OFFLOAD_COMPRESSION_FP8_B128) {
+    fail(FLAME_OFFLOAD_ERR_INVALID, "ActivationOffloadPool::new: unknown compression mode");
+    return nullptr;
+  }
+  FlameOffloadPoolConfig cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.device = -1;
+  cfg.numa_node = -2;  // look the GPU's node up in sysfs
+  if (cfg_in) {
+    if (cfg_in->struct_size == 0 || cfg_in->struct_size > sizeof(cfg)) {
+      fail(FLAME_OFFLOAD_ERR_INVALID, "FlameOffloadPoolConfig.struct_size is not set");
+      return nullptr;
+    }
+    memcpy(&cfg, cfg_in, cfg_in->struct_size);
+  }
+  int device = cfg.device;
+  if (device < 0 && cudaGetDevice(&device) != cudaSuccess) { fail(FLAME_OFFLOAD_ERR_CUDA, "cudaGetDevice failed"); return nullptr; }
+  uint64_t chunk = cfg.chunk_bytes ? cfg.chunk_bytes : kDefaultChunkBytes;
+  if (chunk % (64u << 10) != 0) { fail(FLAME_OFFLOAD_ERR_INVALID, "chunk_bytes must be a multiple of 64 KiB"); return nullptr; }
+
+  DeviceGuard guard(device);
+  auto* p = new FlameOffloadPool();
+  p->device = device;
+  p->compression = compression;
+  p->num_slots = num_slots;
+  p->slot_bytes = max_bytes;
+  p->codec_flags = cfg.codec_flags;
+  p->codec_max_ctas = cfg.codec_max_ctas;
+
+  // A slot that fits in one chunk gets a chunk of exactly its stored size, so a
+  // pool of small slots holds num_slots * stored(max_bytes) pinned bytes like
+  // the reference (src/activation_offload.rs:383-399, 441-449).
+  const bool single = max_bytes <= chunk;
+  p->chunk_src_bytes = single ? max_bytes : chunk;
+  const size_t chunks_per_slot = single ? 1 : (max_bytes + chunk - 1) / chunk;
+  if (compression == FLAME_OFFLOAD_COMPRESSION_NONE) {
+    p->host_chunk_bytes = p->chunk_src_bytes;
+  } else {
+    p->chunk_elems = single ? (max_bytes + 1) / 2 : chunk / 2;
+    p->host_chunk_bytes = p->stored_for(p->chunk_elems);
+  }
+  size_t total = num_slots * chunks_per_slot;
+  if (cfg.host_budget_bytes) total = std::max<size_t>(1, cfg.host_budget_bytes / p->host_chunk_bytes);
+  p->total_chunks = total;
+  p->slab_bytes = total * p->host_chunk_bytes;
+
+  int node = cfg.numa_node == -2 ? gpu_numa_node(device) : cfg.numa_node;
+  if (node >= 0) set_preferred_node(node);
+  void* slab = nullptr;
+  cudaError_t e = host_alloc_checked(&slab, p->slab_bytes, cfg.host_alloc_flags);
+  if (node >= 0) set_preferred_node(-1);
+  if (e != cudaSuccess || !slab) {
+    fail_cuda(e, "ActivationOffloadPool::new: cudaHostAlloc of the pinned slab");
+    destroy_pool(p);
+    return nullptr;
+  }
+  p->slab = static_cast<uint8_t*>(slab);
+  p->chunk_last_reader.assign(total, -1);
+  p->free_chunks.reserve(total);
+  for (size_t c = total; c-- > 0;) p->free_chunks.push_back((uint32_t)c);
+
+  bool ok = true;
+  auto chk = [&](cudaError_t err, const char* what) { if (ok && err != cudaSuccess) { fail_cuda(err, what); ok = false; } };
+  int lo = 0, hi = 0;
+  chk(cudaDeviceGetStreamPriorityRange(&lo, &hi), "cudaDeviceGetStreamPriorityRange");
+  // Codec kernels are short and feed the copy engines: highest priority, so they
+  // are scheduled ahead of queued compute blocks.
+  chk(cudaStreamCreateWithPriority(&p->s_quant, cudaStreamNonBlocking, hi), "cudaStreamCreate(quant)");
+  chk(cudaStreamCreateWithPriority(&p->s_dequant, cudaStreamNonBlocking, hi), "cudaStreamCreate(dequant)");
+  chk(cudaStreamCreateWithFlags(&p->s_d2h, cudaStreamNonBlocking), "cudaStreamCreate(d2h)");
+  chk(cudaStreamCreateWithFlags(&p->s_h2d, cudaStreamNonBlocking), "cudaStreamCreate(h2d)");
+
+  p->slots.resize(num_slots);
+  for (auto& s : p->slots) {
+    chk(s.producer.create(), "cudaEventCreate"); chk(s.d2h_done.create(), "cudaEventCreate");
+    chk(s.consumer.create(), "cudaEventCreate"); chk(s.h2d_done.create(), "cudaEventCreate");
+    chk(s.ready.create(), "cudaEventCreate");
+  }
+  p->free_stack.reserve(num_slots);
+  for (size_t i = num_slots; i-- > 0;) p->free_stack.push_back(i);  // slot 0 on top
+
+  if (p->compressed()) {
+    const uint32_t tiles = cfg.staging_tiles ? cfg.staging_tiles : kDefaultTiles;
+    for (auto* ring : {&p->out_tiles, &p->in_tiles}) {
+      ring->resize(tiles);
+      for (auto& t : *ring) {
+        void* d = nullptr;
+        chk(cudaMalloc(&d, p->host_chunk_bytes), "cudaMalloc(staging tile)");
+        t.dev = static_cast<uint8_t*>(d);
+        chk(t.full.create(), "cudaEventCreate"); chk(t.free_.create(), "cudaEventCreate");
+      }
+    }
+  }
+  if (!ok) { destroy_pool(p); return nullptr; }
+  p->stats.host_chunks_total = total;
+  p->stats.host_chunks_free = total;
+  return p;
+}
+
+void flame_offload_pool_destroy(FlameOffloadPool* p) {
+  if (!p) return;
+  DeviceGuard guard(p->device);
+  poll_streams(p, 30.0);
+  destroy_pool(p);
+}
+
+size_t flame_offload_pool_num_slots(const FlameOffloadPool* p) { return p ? p->num_slots : 0; }
+size_t flame_offload_pool_slot_bytes(const FlameOffloadPool* p) { return p ? p->slot_bytes : 0; }
+size_t flame_offload_pool_host_bytes(const FlameOffloadPool* p) { return p ? p->slab_bytes : 0; }
+int flame_offload_pool_compression(const FlameOffloadPool* p) { return p ? p->compression : -1; }
+
+size_t flame_offload_pool_in_flight(const FlameOffloadPool* pc) {
+  auto* p = const_cast<FlameOffloadPool*>(pc);
+  if (!p) return 0;
+  std::lock_guard<std::mutex> lk(p->mu);
+  size_t n = 0;
+  for (auto& s : p->slots) n += s.state == SlotState::Pushed;
+  return n;
+}
+
+FlameOffloadStatus flame_offload_pool_push(FlameOffloadPool* p, const void* src, size_t numel, int dtype, void* compute_stream, FlameOffloadHandle* out) {
+  if (!p || !out) return fail(FLAME_OFFLOAD_ERR_INVALID, "push: null pool or handle pointer");
+  // Dtype gate, src/activation_offload.rs:467-476.
+  if (dtype != FLAME_OFFLOAD_DTYPE_BF16 && dtype != FLAME_OFFLOAD_DTYPE_F32)
+    return fail(FLAME_OFFLOAD_ERR_UNSUPPORTED, "ActivationOffloadPool::push: dtype not supported (BF16/F32 only)");
+  const size_t esz = dtype == FLAME_OFFLOAD_DTYPE_BF16 ? 2 : 4;
+  const size_t bytes = numel * esz;
+  if (bytes == 0) return fail(FLAME_OFFLOAD_ERR_INVALID, "ActivationOffloadPool::push: tensor is empty");
+  if (!src) return fail(FLAME_OFFLOAD_ERR_INVALID, "ActivationOffloadPool::push: null source pointer");
+  if (bytes > p->slot_bytes)
+    return fail(FLAME_OFFLOAD_ERR_INVALID, "ActivationOffloadPool::push: tensor " + std::to_string(bytes) +
+                " bytes exceeds slot capacity " + std::to_string(p->slot_bytes) + " bytes");
+
+  std::lock_guard<std::mutex> lk(p->mu);
+  DeviceGuard guard(p->device);
+  if (p->free_stack.empty()) {
+    p->stats.push_rejected_full++;
+    return fail(FLAME_OFFLOAD_ERR_STATE, "ActivationOffloadPool full: " + std::to_string(p->num_slots) +
+                " slots all in-flight. Increase num_slots.");
+  }
+  // Compression applies to BF16 only (src/activation_offload.rs:537-542).
+  if (p->compressed() && dtype != FLAME_OFFLOAD_DTYPE_BF16)
+    return fail(FLAME_OFFLOAD_ERR_UNSUPPORTED, "compressed offload only supports BF16 activations");
+
+  const size_t nchunks = p->compressed() ? (numel + p->chunk_elems - 1) / p->chunk_elems
+                                         : (bytes + p->chunk_src_bytes - 1) / p->chunk_src_bytes;
+  if (nchunks > p->free_chunks.size()) {
+    p->stats.push_rejected_full++;
+    return fail(FLAME_OFFLOAD_ERR_STATE, "ActivationOffloadPool full: pinned slab exhausted (" +
+                std::to_string(p->free_chunks.size()) + " chunks free, " + std::to_string(nchunks) + " needed)");
+  }
+  const size_t slot = p->free_stack.back();
+  p->free_stack.pop_back();
+  Slot& s = p->slots[slot];
+  s.numel = numel; s.bytes = bytes; s.dtype = dtype;
+  s.fp8_scale = p->compression == FLAME_OFFLOAD_COMPRESSION_FP8 ? kLegacyFp8Scale : 0.0f;
+  s.chunks.clear();
+  s.stored_bytes = 0;
+  for (size_t k = 0; k < nchunks; ++k) {
+    s.chunks.push_back(p->free_chunks.back());
+    p->free_chunks.pop_back();
+    if (p->compressed()) s.stored_bytes += p->stored_for(std::min<uint64_t>(p->chunk_elems, numel - k * p->chunk_elems));
+  }
+  if (!p->compressed()) s.stored_bytes = bytes;
+
+  cudaError_t e = enqueue_push(*p, s, static_cast<const uint8_t*>(src), (cudaStream_t)compute_stream);
+  if (e != cudaSuccess) {
+    // As the reference does on a failed copy (src/activation_offload.rs:528-533): the slot goes back.
+    p->release_chunks(s, -1);
+    p->free_stack.push_back(slot);
+    return FLAME_OFFLOAD_ERR_CUDA;
+  }
+  s.state = SlotState::Pushed;
+  p->stats.pushes++;
+  p->stats.bytes_logical_out += bytes;
+  p->stats.host_chunks_free = p->free_chunks.size();
+  out->slot = slot;
+  out->epoch = p->epoch;
+  return FLAME_OFFLOAD_OK;
+}
+
+FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* p, FlameOffloadHandle h, void* dst, size_t dst_bytes, void* compute_stream, unsigned int flags) {
+  if (!p) return fail(FLAME_OFFLOAD_ERR_INVALID, "pull: null pool");
+  std::lock_guard<std::mutex> lk(p->mu);
+  FlameOffloadStatus st = p->check_handle(h, "ActivationOffloadPool::pull");
+  if (st != FLAME_OFFLOAD_OK) return st;
+  Slot& s = p->slots[h.slot];
+  if (!dst) return fail(FLAME_OFFLOAD_ERR_INVALID, "pull: null destination");
+  if (dst_bytes < s.bytes)
+    return fail(FLAME_OFFLOAD_ERR_INVALID, "pull: destination holds " + std::to_string(dst_bytes) + " bytes, tensor needs " + std::to_string(s.bytes));
+  DeviceGuard guard(p->device);
+  cudaError_t e = enqueue_pull(*p, s, static_cast<uint8_t*>(dst), (cudaStream_t)compute_stream, flags);
+  if (e != cudaSuccess) return FLAME_OFFLOAD_ERR_CUDA;  // slot stays Pushed (src/activation_offload.rs:704-711)
+  s.state = SlotState::Idle;
+  p->release_chunks(s, (int32_t)h.slot);
+  p->free_stack.push_back(h.slot);
+  p->stats.pulls++;
+  p->stats.bytes_logical_in += s.bytes;
+  p->stats.host_chunks_free = p->free_chunks.size();
+  return FLAME_OFFLOAD_OK;
+}
+
+FlameOffloadStatus flame_offload_pool_wait_ready(FlameOffloadPool* p, size_t slot, void* stream) {
+  if (!p) return fail(FLAME_OFFLOAD_ERR_INVALID, "wait_ready: null pool");
+  std::lock_guard<std::mutex> lk(p->mu);
+  if (slot >= p->slots.size()) return fail(FLAME_OFFLOAD_ERR_STATE, "wait_ready: slot out of range");
+  DeviceGuard guard(p->device);
+  cudaError_t e = p->slots[slot].ready.make_wait((cudaStream_t)stream);
+  return e == cudaSuccess ? FLAME_OFFLOAD_OK : fail_cuda(e, "wait_ready: cudaStreamWaitEvent");
+}
+
+FlameOffloadStatus flame_offload_pool_clear(FlameOffloadPool* p) {
+  if (!p) return fail(FLAME_OFFLOAD_ERR_INVALID, "clear: null pool");
+  std::lock_guard<std::mutex> lk(p->mu);
+  for (size_t i = 0; i < p->slots.size(); ++i) {
+    Slot& s = p->slots[i];
+    s.state = SlotState::Idle;
+    p->release_chunks(s, -1);
+  }
+  p->free_stack.clear();
+  for (size_t i = p->num_slots; i-- > 0;) p->free_stack.push_back(i);
+  p->epoch += 1;
+  if (p->epoch == 0) p->epoch = 1;
+  p->stats.host_chunks_free = p->free_chunks.size();
+  return FLAME_OFFLOAD_OK;
+}
+
+int flame_offload_pool_source_released(FlameOffloadPool* p, FlameOffloadHandle h) {
+  if (!p) return -(int)FLAME_OFFLOAD_ERR_INVALID;
+  std::lock_guard<std::mutex> lk(p->mu);
+  if (h.epoch != p->epoch || h.slot >= p->slots.size()) {
+    fail(FLAME_OFFLOAD_ERR_STATE, "source_released: stale or invalid handle");
+    return -(int)FLAME_OFFLOAD_ERR_STATE;
+  }
+  Slot& s = p->slots[h.slot];
+  if (!s.d2h_done.recorded) return 1;
+  DeviceGuard guard(p->device);
+  cudaError_t e = cudaEventQuery(s.d2h_done.ev);
+  if (e == cudaSuccess) return 1;
+  if (e == cudaErrorNotReady) return 0;
+  fail_cuda(e, "source_released: cudaEventQuery");
+  return -(int)FLAME_OFFLOAD_ERR_CUDA;
+}
+
+FlameOffloadStatus flame_offload_pool_slot_info(FlameOffloadPool* p, FlameOffloadHandle h, FlameOffloadSlotInfo* out) {
+  if (!p || !out) return fail(FLAME_OFFLOAD_ERR_INVALID, "slot_info: null argument");
+  std::lock_guard<std::mutex> lk(p->mu);
+  FlameOffloadStatus st = p->check_handle(h, "slot_info");
+  if (st != FLAME_OFFLOAD_OK) return st;
+  const Slot& s = p->slots[h.slot];
+  out->numel = s.numel; out->dtype = s.dtype; out->compression = p->compression;
+  out->bytes = s.bytes; out->stored_bytes = s.stored_bytes; out->chunks = s.chunks.size();
+  return FLAME_OFFLOAD_OK;
+}
+
+FlameOffloadStatus flame_offload_pool_synchronize(FlameOffloadPool* p, double timeout_s) {
+  if (!p) return fail(FLAME_OFFLOAD_ERR_INVALID, "synchronize: null pool");
+  DeviceGuard guard(p->device);
+  return poll_streams(p, timeout_s);
+}
+
+FlameOffloadStatus flame_offload_pool_read_slot(FlameOffloadPool* p, FlameOffloadHandle h, void* codes_out, void* scales_out, double timeout_s) {
+  if (!p || !codes_out) return fail(FLAME_OFFLOAD_ERR_INVALID, "read_slot: null argument");
+  std::unique_lock<std::mutex> lk(p->mu);
+  FlameOffloadStatus st = p->check_handle(h, "read_slot");
+  if (st != FLAME_OFFLOAD_OK) return st;
+  Slot& s = p->slots[h.slot];
+  DeviceGuard guard(p->device);
+  st = poll_event(s.d2h_done.ev, timeout_s, "read_slot: waiting for the offload");
+  if (st != FLAME_OFFLOAD_OK) return st;
+  auto* co = static_cast<uint8_t*>(codes_out);
+  auto* so = static_cast<float*>(scales_out);
+  for (size_t k = 0; k < s.chunks.size(); ++k) {
+    const uint8_t* c = p->chunk_ptr(s.chunks[k]);
+    if (!p->compressed()) {
+      const uint64_t off = k * p->chunk_src_bytes;
+      memcpy(co + off, c, std::min<uint64_t>(p->chunk_src_bytes, s.bytes - off));
+      continue;
+    }
+    const uint64_t e0 = k * p->chunk_elems;
+    const uint64_t e = std::min<uint64_t>(p->chunk_elems, s.numel - e0);
+    memcpy(co + e0, c, e);
+    if (p->compression != FLAME_OFFLOAD_COMPRESSION_FP8 && so)
+      memcpy(so + e0 / 128, c + packed_scales_offset(e), 4 * ((e + 127) / 128));
+  }
+  if (p->compression == FLAME_OFFLOAD_COMPRESSION_FP8 && so) so[0] = s.fp8_scale;
+  return FLAME_OFFLOAD_OK;
+}
+
+FlameOffloadStatus flame_offload_pool_stats(const FlameOffloadPool* pc, FlameOffloadStats* out) {
+  auto* p = const_cast<FlameOffloadPool*>(pc);
+  if (!p || !out) return fail(FLAME_OFFLOAD_ERR_INVALID, "stats: null argument");
+  std::lock_guard<std::mutex> lk(p->mu);
+  *out = p->stats;
+  return FLAME_OFFLOAD_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,62 @@
+"""Bandwidth probe and recompute-vs-offload plan (flame_offload_probe / flame_offload_policy_plan).
+
+Takes the seat of ``CheckpointPolicy::Adaptive`` in the reference
+(src/gradient_checkpointing.rs:70-74, 201-232): the decision per saved tensor
+is made from measured link and HBM rates instead of a byte counter.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from dataclasses import dataclass
+
+from . import _lib
+from .errors import raise_for_status
+
+
+class Decision(enum.IntEnum):
+    RESIDENT = 0
+    OFFLOAD_BF16 = 1
+    OFFLOAD_INT8 = 2
+    OFFLOAD_FP8 = 3
+    RECOMPUTE = 4
+
+
+@dataclass
+class LinkProbe:
+    d2h_gbs: float
+    h2d_gbs: float
+    hbm_copy_gbs: float
+    quant_gbs: float
+    dequant_gbs: float
+
+
+def probe(nbytes: int = 256 << 20, reps: int = 5) -> LinkProbe:
+    """Measures, on the current CUDA device, pinned copy rates, a device copy and the int8 codec."""
+    out = _lib.LinkProbe()
+    raise_for_status(_lib.lib().flame_offload_probe(nbytes, reps, C.byref(out)), _lib.last_error())
+    return LinkProbe(*(getattr(out, n) for n, _ in _lib.LinkProbe._fields_))
+
+
+@dataclass
+class SavedTensor:
+    nbytes: int
+    group: int
+    recompute_ms: float = -1.0
+    allow_lossy: bool = True
+
+
+def plan(tensors: list[SavedTensor], *, d2h_gbs: float, h2d_gbs: float, fwd_ms: float, bwd_ms: float,
+         device_budget_bytes: int = 0, lossy_codec: Decision = Decision.OFFLOAD_INT8,
+         link_utilisation: float = 0.9) -> tuple[list[Decision], float]:
+    """Returns (decision per tensor, estimated exposed milliseconds per step)."""
+    n = len(tensors)
+    arr = (_lib.PolicyTensor * max(n, 1))()
+    for i, t in enumerate(tensors):
+        arr[i] = _lib.PolicyTensor(t.nbytes, t.recompute_ms, t.group, int(t.allow_lossy))
+    inp = _lib.PolicyInput(d2h_gbs, h2d_gbs, fwd_ms, bwd_ms, device_budget_bytes, int(lossy_codec), link_utilisation)
+    dec = (C.c_int32 * max(n, 1))()
+    est = C.c_double()
+    st = _lib.lib().flame_offload_policy_plan(C.byref(inp), arr, n, dec, C.byref(est))
+    raise_for_status(st, _lib.last_error())
+    return [Decision(dec[i]) for i in range(n)], est.value

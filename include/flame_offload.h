@@ -1,0 +1,276 @@
+/*
+ * flame_offload.h: C ABI of the B200 (sm_100a) activation offload/restore path.
+ *
+ * Plain C, no C++ or framework types: every argument is a pointer, a size or a
+ * scalar.  All device pointers are raw CUDA device addresses, every `stream`
+ * is a cudaStream_t passed as void* (NULL = the legacy default stream).  No
+ * entry point calls cudaDeviceSynchronize, throws, or aborts.
+ *
+ * Two return conventions coexist because the reference project has two:
+ *   - `int` that is 0 on success and otherwise the cudaError_t value
+ *     (the pinned_host.cu / fp8_quant.cu family);
+ *   - FlameOffloadStatus (the FlameCudaStatus family of
+ *     cuda/include/flame_cuda_status.h, extended by two codes).
+ *
+ * Each declaration names the reference interface (file:line inside the
+ * reference project) that it replaces or extends.
+ */
+#ifndef FLAME_OFFLOAD_H_
+#define FLAME_OFFLOAD_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Same numbering as FlameCudaStatus (cuda/include/flame_cuda_status.h:7-12,
+ * mapped to Rust errors at src/cuda_ops_ffi.rs:591-599); 4 and 5 are new.
+ * STATE corresponds to the reference's Error::InvalidOperation (pool full,
+ * stale epoch, slot out of range, slot not in the Pushed state:
+ * src/activation_offload.rs:494-499, 620-641). */
+typedef enum {
+  FLAME_OFFLOAD_OK = 0,
+  FLAME_OFFLOAD_ERR_INVALID = 1,
+  FLAME_OFFLOAD_ERR_UNSUPPORTED = 2,
+  FLAME_OFFLOAD_ERR_CUDA = 3,
+  FLAME_OFFLOAD_ERR_TIMEOUT = 4,
+  FLAME_OFFLOAD_ERR_STATE = 5
+} FlameOffloadStatus;
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* flame_offload_last_error(void);
+
+/* ------------------------------------------------------------------------
+ * 1. Pinned host memory and async copies: signatures kept exactly.
+ *    Replaces src/cuda/pinned_host.cu:4-45 (declared src/cuda/ffi.rs:83-94).
+ * ---------------------------------------------------------------------- */
+void* flame_cuda_alloc_pinned_host(size_t size, unsigned int flags); /* NULL on failure */
+int flame_cuda_free_pinned_host(void* ptr);
+/* kind: 1 = H2D, 2 = D2H, 3 = D2D, anything else = cudaMemcpyDefault */
+int flame_cuda_memcpy_async(void* dst, const void* src, size_t bytes, int kind, void* stream);
+int flame_cuda_host_register(void* ptr, size_t bytes, unsigned int flags);
+int flame_cuda_host_unregister(void* ptr);
+
+/* Replaces src/ffi/cuda_ffi.c:90-109 (impl cuda/src/flame_cuda_common.cu:131-165):
+ * NULL pointers or bytes == 0 give ERR_INVALID. */
+FlameOffloadStatus flame_h2d_async(void* dst_device, const void* src_host, uint64_t bytes, void* stream);
+FlameOffloadStatus flame_d2h_async(void* dst_host, const void* src_device, uint64_t bytes, void* stream);
+FlameOffloadStatus flame_d2d_async(void* dst_device, const void* src_device, uint64_t bytes, void* stream);
+
+/* ------------------------------------------------------------------------
+ * 2. Element-wise FP8 E4M3 with a caller-supplied scale: signatures kept.
+ *    Replaces src/cuda/fp8_quant.cu:74-93 and src/cuda/fp8_dequant.cu:41-59
+ *    (declared src/cuda/ffi.rs:546-564, src/activation_offload.rs:99-115).
+ *    out[i] = enc(bf16_to_f32(in[i]) * inv_scale);  out[i] = bf16(dec(in[i]) * scale)
+ *    with the reference's own encoder/decoder arithmetic, bit for bit, under
+ *    IEEE (non flush-to-zero) float semantics.  n == 0 returns 0 at once.
+ * ---------------------------------------------------------------------- */
+int flame_bf16_to_fp8(const void* input_bf16, void* output_u8, float inv_scale, size_t n_elements, void* stream);
+int flame_fp8_to_bf16(const void* input_u8, void* output_bf16, float scale, size_t n_elements, void* stream);
+
+/* ------------------------------------------------------------------------
+ * 3. Per-128-element-block codecs (new; they take the place of the two calls
+ *    above inside push/pull, src/activation_offload.rs:543-579 and 678-700).
+ *
+ *    Blocks are consecutive runs of 128 elements of the flat tensor; a short
+ *    last block uses only its real elements.  scales[b] is fp32.
+ *      int8: scale = absmax/127; code = rne(x / scale) in [-127,127]
+ *            (int8 formula of src/sage_attention.rs:524-541); absmax == 0
+ *            gives scale 0 and codes 0.
+ *      fp8 : scale = absmax/448; code = enc(x * (1/scale)) with the encoder of
+ *            src/cuda/fp8_quant.cu:19-57; absmax == 0 gives scale 0, codes 0.
+ *    Dequantise: out = bf16_rne(float(code) * scale) / bf16_rne(dec(code) * scale).
+ *    Returns 0 or a cudaError_t value; cudaErrorInvalidValue (1) for NULL
+ *    pointers with n > 0.  Any pointer alignment is accepted (16-byte aligned
+ *    pointers take the fast kernels).
+ * ---------------------------------------------------------------------- */
+#define FLAME_ACT_BLOCK 128
+#define FLAME_ACT_INT8_MUL_INV 1u /* int8: code = rne(x * (1/scale)) instead of the division */
+#define FLAME_ACT_FP8_OCP 1u      /* fp8: OCP round-to-nearest-even, saturating encoder (not the reference's) */
+
+int flame_act_quant_int8_b128(const void* in_bf16, void* codes_i8, void* scales_f32, size_t n, unsigned int flags, void* stream);
+int flame_act_dequant_int8_b128(const void* codes_i8, const void* scales_f32, void* out_bf16, size_t n, void* stream);
+int flame_act_quant_fp8_b128(const void* in_bf16, void* codes_u8, void* scales_f32, size_t n, unsigned int flags, void* stream);
+int flame_act_dequant_fp8_b128(const void* codes_u8, const void* scales_f32, void* out_bf16, size_t n, void* stream);
+
+/* Packed layout of one compressed tensor or chunk in one buffer:
+ * codes[n] | zero padding up to a 256-byte boundary | scales[ceil(n/128)]. */
+size_t flame_act_packed_scales_offset(size_t n);
+size_t flame_act_packed_bytes(size_t n);
+
+/* Limits the number of thread blocks the codec kernels launch on the current
+ * device (0 = default: a multiple of the SM count).  Returns the old value. */
+int flame_act_set_max_ctas(int max_ctas);
+
+/* ------------------------------------------------------------------------
+ * 4. Activation offload pool.
+ *    Mirrors ActivationOffloadPool (src/activation_offload.rs:323-760): same
+ *    slot state machine, LIFO free stack, epoch-stamped handles and error
+ *    cases.  Underneath: one pinned slab carved into chunks, a chunked
+ *    double-buffered pipeline on dedicated codec / D2H / H2D streams, and
+ *    restore straight into a caller-provided destination.
+ * ---------------------------------------------------------------------- */
+typedef struct FlameOffloadPool FlameOffloadPool;
+
+/* OffloadCompression (src/activation_offload.rs:89-96) plus the two block codecs. */
+enum {
+  FLAME_OFFLOAD_COMPRESSION_NONE = 0,
+  FLAME_OFFLOAD_COMPRESSION_FP8 = 1,       /* reference mode: fixed per-tensor scale 8/448 */
+  FLAME_OFFLOAD_COMPRESSION_INT8_B128 = 2,
+  FLAME_OFFLOAD_COMPRESSION_FP8_B128 = 3
+};
+
+/* DType tags accepted by push (src/activation_offload.rs:467-476). */
+enum { FLAME_OFFLOAD_DTYPE_BF16 = 0, FLAME_OFFLOAD_DTYPE_F32 = 1 };
+
+/* OffloadHandle (src/activation_offload.rs:292-303): a plain copyable value. */
+typedef struct {
+  uint64_t slot;
+  uint64_t epoch;
+} FlameOffloadHandle;
+
+typedef struct {
+  uint32_t struct_size;       /* sizeof(FlameOffloadPoolConfig); 0-filled fields take defaults */
+  int32_t device;             /* CUDA ordinal; -1 = current device */
+  uint64_t chunk_bytes;       /* pipeline chunk in source (BF16/F32) bytes; default 16 MiB; multiple of 64 KiB */
+  uint32_t staging_tiles;     /* device staging tiles per direction for the compressed modes; default 3 */
+  uint32_t codec_flags;       /* FLAME_ACT_* flags passed to the block codecs */
+  uint64_t host_budget_bytes; /* pinned bytes to hold; 0 = num_slots * stored size of max_bytes */
+  uint32_t host_alloc_flags;  /* cudaHostAlloc flags; default 0 (never write-combined: the host reads it back) */
+  int32_t codec_max_ctas;     /* thread blocks per codec launch; 0 = default */
+  int32_t numa_node;          /* bind the slab to this NUMA node with mbind(); -1 = leave to first touch */
+  uint32_t reserved;
+} FlameOffloadPoolConfig;
+
+typedef struct {
+  uint64_t pushes, pulls;
+  uint64_t bytes_logical_out, bytes_logical_in; /* BF16/F32 bytes offloaded / restored */
+  uint64_t bytes_link_out, bytes_link_in;       /* bytes that crossed the host link */
+  uint64_t chunks_out, chunks_in;
+  uint64_t codec_launches;                      /* compress + dequantise kernel launches */
+  uint64_t host_chunks_total, host_chunks_free;
+  uint64_t push_rejected_full;                  /* pushes refused: no slot or no pinned chunk left */
+} FlameOffloadStats;
+
+/* new(device, num_slots, max_bytes, compression): src/activation_offload.rs:365-427.
+ * cfg may be NULL.  Returns NULL on failure (see flame_offload_last_error). */
+FlameOffloadPool* flame_offload_pool_create(size_t num_slots, size_t max_bytes, int compression, const FlameOffloadPoolConfig* cfg);
+/* Waits (bounded, 30 s) for the pool's own streams, then frees everything. */
+void flame_offload_pool_destroy(FlameOffloadPool* pool);
+
+/* Accessors: src/activation_offload.rs:429-455. */
+size_t flame_offload_pool_num_slots(const FlameOffloadPool* pool);
+size_t flame_offload_pool_slot_bytes(const FlameOffloadPool* pool);
+size_t flame_offload_pool_host_bytes(const FlameOffloadPool* pool);
+size_t flame_offload_pool_in_flight(const FlameOffloadPool* pool);
+int flame_offload_pool_compression(const FlameOffloadPool* pool);
+
+/* push(&tensor): src/activation_offload.rs:465-611.  `src_device` must be the
+ * first element of a contiguous tensor of `numel` elements.  Work already
+ * submitted to `compute_stream` is ordered before the pool reads the source.
+ * Never blocks the host.  The caller must keep the source alive until
+ * flame_offload_pool_source_released() reports 1 (the reference holds it until
+ * pull; src/activation_offload.rs:600-605). */
+FlameOffloadStatus flame_offload_pool_push(FlameOffloadPool* pool, const void* src_device, size_t numel, int dtype, void* compute_stream, FlameOffloadHandle* out_handle);
+
+/* pull(handle): src/activation_offload.rs:619-731, but into the caller's
+ * buffer (`dst_bytes` >= the tensor's byte size).  Work already submitted to
+ * `compute_stream` is ordered before the first write into dst.  Unless
+ * FLAME_OFFLOAD_PULL_DEFER_WAIT is set, `compute_stream` is made to wait for
+ * the restore before returning (src/activation_offload.rs:714-715).  The slot
+ * returns to Idle and to the top of the free stack. */
+#define FLAME_OFFLOAD_PULL_DEFER_WAIT 1u
+FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* pool, FlameOffloadHandle handle, void* dst_device, size_t dst_bytes, void* compute_stream, unsigned int flags);
+/* Makes `stream` wait for the most recent restore issued from `slot`. */
+FlameOffloadStatus flame_offload_pool_wait_ready(FlameOffloadPool* pool, size_t slot, void* stream);
+
+/* clear(): src/activation_offload.rs:742-760.  Does not synchronise. */
+FlameOffloadStatus flame_offload_pool_clear(FlameOffloadPool* pool);
+
+/* 1 when the device-to-host copy of `handle` has finished reading the source
+ * tensor (it may be freed), 0 while it is still being read, negative
+ * FlameOffloadStatus on a stale or invalid handle. */
+int flame_offload_pool_source_released(FlameOffloadPool* pool, FlameOffloadHandle handle);
+
+/* Metadata captured at push (SlotMeta, src/activation_offload.rs:269-281). */
+typedef struct {
+  uint64_t numel;
+  int32_t dtype;
+  int32_t compression;
+  uint64_t bytes;        /* logical bytes */
+  uint64_t stored_bytes; /* pinned bytes used, scales and padding included */
+  uint64_t chunks;
+} FlameOffloadSlotInfo;
+FlameOffloadStatus flame_offload_pool_slot_info(FlameOffloadPool* pool, FlameOffloadHandle handle, FlameOffloadSlotInfo* out);
+
+/* Polls the pool's streams until idle or until timeout_s elapses
+ * (ERR_TIMEOUT).  Never waits unboundedly. */
+FlameOffloadStatus flame_offload_pool_synchronize(FlameOffloadPool* pool, double timeout_s);
+
+/* Test / inspection hook: after the offload of `handle` has completed, gather
+ * what is stored in pinned memory into host arrays in canonical order.
+ * Compressed modes: codes_out[numel] and scales_out[ceil(numel/128)] (legacy
+ * FP8: scales_out[0] = the fixed scale).  Uncompressed: codes_out[bytes]. */
+FlameOffloadStatus flame_offload_pool_read_slot(FlameOffloadPool* pool, FlameOffloadHandle handle, void* codes_out, void* scales_out, double timeout_s);
+
+FlameOffloadStatus flame_offload_pool_stats(const FlameOffloadPool* pool, FlameOffloadStats* out);
+
+/* Host-side fault injection for tests: the `countdown`-th next call of the
+ * named kind fails with an error code instead of reaching CUDA.  Nothing is
+ * ever injected on the device. */
+enum { FLAME_OFFLOAD_FAULT_NONE = 0, FLAME_OFFLOAD_FAULT_MEMCPY = 1, FLAME_OFFLOAD_FAULT_KERNEL = 2, FLAME_OFFLOAD_FAULT_HOST_ALLOC = 3 };
+void flame_offload_inject_fault(int kind, int countdown);
+
+/* ------------------------------------------------------------------------
+ * 5. PinnedPool: size-class cache of pinned buffers.
+ *    Mirrors src/pinned_pool.rs:21-99 (8 MiB classes, max_cached_bytes cap).
+ * ---------------------------------------------------------------------- */
+typedef struct FlamePinnedPool FlamePinnedPool;
+FlamePinnedPool* flame_pinned_pool_create(unsigned int alloc_flags, size_t max_cached_bytes);
+void flame_pinned_pool_destroy(FlamePinnedPool* pool);
+/* checkout(min_bytes): smallest cached buffer with capacity >= round_up(min_bytes), else a fresh one. */
+FlameOffloadStatus flame_pinned_pool_checkout(FlamePinnedPool* pool, size_t min_bytes, void** out_ptr, size_t* out_capacity);
+/* checkin(buf): cached if it fits under max_cached_bytes, otherwise freed. */
+FlameOffloadStatus flame_pinned_pool_checkin(FlamePinnedPool* pool, void* ptr, size_t capacity);
+void flame_pinned_pool_stats(const FlamePinnedPool* pool, size_t* cached_bytes, size_t* cached_buffers);
+
+/* ------------------------------------------------------------------------
+ * 6. Bandwidth probes and the recompute-vs-offload policy.
+ *    Takes the seat of CheckpointPolicy::Adaptive
+ *    (src/gradient_checkpointing.rs:70-74, 201-232) and of the fixed rule
+ *    "offload every BF16 requires_grad saved tensor" (src/autograd.rs:1721-1725).
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  double d2h_gbs, h2d_gbs;       /* pinned <-> device copy rate, GB/s */
+  double hbm_copy_gbs;           /* device-to-device copy, read+write bytes per second */
+  double quant_gbs, dequant_gbs; /* int8 block codec, algorithmic bytes per second */
+} FlameLinkProbe;
+/* Measures on the current device with CUDA events; `bytes` per transfer (0 = 256 MiB). */
+FlameOffloadStatus flame_offload_probe(size_t bytes, int reps, FlameLinkProbe* out);
+
+enum { FLAME_POLICY_RESIDENT = 0, FLAME_POLICY_OFFLOAD_BF16 = 1, FLAME_POLICY_OFFLOAD_INT8 = 2, FLAME_POLICY_OFFLOAD_FP8 = 3, FLAME_POLICY_RECOMPUTE = 4 };
+
+typedef struct {
+  uint64_t bytes;          /* BF16 bytes of the saved tensor */
+  double recompute_ms;     /* time to recompute it in backward; < 0 = cannot be recomputed */
+  int32_t group;           /* checkpoint block index in forward order */
+  int32_t allow_lossy;     /* 1 = int8/fp8 allowed */
+} FlamePolicyTensor;
+
+typedef struct {
+  double d2h_gbs, h2d_gbs;      /* from the probe, for this replica count */
+  double fwd_ms, bwd_ms;        /* compute time of one step that copies can hide behind */
+  uint64_t device_budget_bytes; /* activation bytes that may stay resident */
+  int32_t lossy_codec;          /* FLAME_POLICY_OFFLOAD_INT8 or _FP8 */
+  double link_utilisation;      /* fraction of fwd/bwd time the link may be busy; default 0.9 */
+} FlamePolicyInput;
+
+/* Deterministic for given inputs.  decisions[i] receives a FLAME_POLICY_* value. */
+FlameOffloadStatus flame_offload_policy_plan(const FlamePolicyInput* in, const FlamePolicyTensor* tensors, size_t n, int32_t* decisions, double* est_overhead_ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLAME_OFFLOAD_H_ */

@@ -1,0 +1,44 @@
+"""The recompute-vs-offload plan is a pure host function: tested here without a GPU."""
+import pytest
+
+from flame_b200.errors import InvalidInput
+from flame_b200.policy import Decision, SavedTensor, plan
+
+MB = 1 << 20
+
+
+def dit_tensors(blocks=20):
+    per_block = [28 * MB, 28 * MB, 85 * MB, 28 * MB, 170 * MB]
+    return [SavedTensor(nbytes=b, group=g, recompute_ms=0.02 * b / MB) for g in range(blocks) for b in per_block]
+
+
+def test_everything_fits_under_a_fast_link():
+    dec, est = plan(dit_tensors(), d2h_gbs=1000, h2d_gbs=1000, fwd_ms=60, bwd_ms=120)
+    assert set(dec) == {Decision.OFFLOAD_INT8} and est == 0.0
+
+
+def test_resident_budget_goes_to_the_last_blocks():
+    ts = dit_tensors()
+    dec, _ = plan(ts, d2h_gbs=1000, h2d_gbs=1000, fwd_ms=60, bwd_ms=120, device_budget_bytes=2 * 339 * MB)
+    resident_groups = {t.group for t, d in zip(ts, dec) if d == Decision.RESIDENT}
+    assert resident_groups == {18, 19}
+
+
+def test_slow_link_switches_cheap_tensors_to_recompute_and_reports_the_rest():
+    ts = dit_tensors()
+    dec, est = plan(ts, d2h_gbs=5, h2d_gbs=5, fwd_ms=60, bwd_ms=120)
+    assert Decision.RECOMPUTE in dec
+    dec2, est2 = plan([SavedTensor(t.nbytes, t.group, -1.0) for t in ts], d2h_gbs=5, h2d_gbs=5, fwd_ms=60, bwd_ms=120)
+    assert Decision.RECOMPUTE not in dec2 and est2 > est > 0
+
+
+def test_lossless_tensors_stay_bf16_and_plan_is_deterministic():
+    ts = [SavedTensor(100 * MB, 0, allow_lossy=False), SavedTensor(100 * MB, 1)]
+    a = plan(ts, d2h_gbs=50, h2d_gbs=50, fwd_ms=10, bwd_ms=20, lossy_codec=Decision.OFFLOAD_FP8)
+    assert a[0] == [Decision.OFFLOAD_BF16, Decision.OFFLOAD_FP8]
+    assert a == plan(ts, d2h_gbs=50, h2d_gbs=50, fwd_ms=10, bwd_ms=20, lossy_codec=Decision.OFFLOAD_FP8)
+
+
+def test_bad_rates_are_rejected():
+    with pytest.raises(InvalidInput):
+        plan(dit_tensors(1), d2h_gbs=0, h2d_gbs=10, fwd_ms=1, bwd_ms=1)
