@@ -26,7 +26,7 @@ class PoolConfig(C.Structure):
         ("struct_size", C.c_uint32), ("device", C.c_int32), ("chunk_bytes", C.c_uint64),
         ("staging_tiles", C.c_uint32), ("codec_flags", C.c_uint32), ("host_budget_bytes", C.c_uint64),
         ("host_alloc_flags", C.c_uint32), ("codec_max_ctas", C.c_int32), ("numa_node", C.c_int32),
-        ("reserved", C.c_uint32),
+        ("tile_chunks", C.c_uint32),
     ]
 
 

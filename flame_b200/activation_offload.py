@@ -66,7 +66,7 @@ class ActivationOffloadPool:
                  compression: OffloadCompression = OffloadCompression.NONE, *,
                  chunk_bytes: int = 0, staging_tiles: int = 0, codec_flags: int = 0,
                  host_budget_bytes: int = 0, host_alloc_flags: int = 0, codec_max_ctas: int = 0,
-                 numa_node: int = -2):
+                 numa_node: int = -2, tile_chunks: int = 0):
         import torch
 
         self._torch = torch
@@ -76,7 +76,7 @@ class ActivationOffloadPool:
         index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self.device = torch.device("cuda", index)
         cfg = _lib.PoolConfig(C.sizeof(_lib.PoolConfig), index, chunk_bytes, staging_tiles, codec_flags,
-                              host_budget_bytes, host_alloc_flags, codec_max_ctas, numa_node, 0)
+                              host_budget_bytes, host_alloc_flags, codec_max_ctas, numa_node, tile_chunks)
         self._lib = _lib.lib()
         with torch.cuda.device(index):
             self._h = self._lib.flame_offload_pool_create(num_slots, max_bytes, int(compression), C.byref(cfg))

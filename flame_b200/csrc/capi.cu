@@ -112,17 +112,28 @@ int flame_fp8_to_bf16(const void* input, void* output, float scale, size_t n, vo
 
 // ---- per-128-block codecs --------------------------------------------------------
 
+static int quant_entry(int codec, const void* in, void* codes, void* scales, size_t n, unsigned flags, void* stream) {
+  if (n == 0) return 0;
+  if (!in || !codes || !scales) return (int)cudaErrorInvalidValue;
+  return (int)launch_compress(codec, in, codes, n, single_chunk_layout(codes, scales, n), flags, (cudaStream_t)stream, 0);
+}
+static int dequant_entry(int codec, const void* codes, const void* scales, void* out, size_t n, void* stream) {
+  if (n == 0) return 0;
+  if (!codes || !scales || !out) return (int)cudaErrorInvalidValue;
+  return (int)launch_dequant(codec, codes, out, n, single_chunk_layout(codes, scales, n), (cudaStream_t)stream, 0);
+}
+
 int flame_act_quant_int8_b128(const void* in, void* codes, void* scales, size_t n, unsigned int flags, void* stream) {
-  return (int)launch_compress(kCodecInt8, in, codes, scales, n, flags, (cudaStream_t)stream, 0);
+  return quant_entry(kCodecInt8, in, codes, scales, n, flags, stream);
 }
 int flame_act_dequant_int8_b128(const void* codes, const void* scales, void* out, size_t n, void* stream) {
-  return (int)launch_dequant(kCodecInt8, codes, scales, out, n, (cudaStream_t)stream, 0);
+  return dequant_entry(kCodecInt8, codes, scales, out, n, stream);
 }
 int flame_act_quant_fp8_b128(const void* in, void* codes, void* scales, size_t n, unsigned int flags, void* stream) {
-  return (int)launch_compress(kCodecFp8, in, codes, scales, n, flags, (cudaStream_t)stream, 0);
+  return quant_entry(kCodecFp8, in, codes, scales, n, flags, stream);
 }
 int flame_act_dequant_fp8_b128(const void* codes, const void* scales, void* out, size_t n, void* stream) {
-  return (int)launch_dequant(kCodecFp8, codes, scales, out, n, (cudaStream_t)stream, 0);
+  return dequant_entry(kCodecFp8, codes, scales, out, n, stream);
 }
 
 size_t flame_act_packed_scales_offset(size_t n) { return (n + 255u) & ~(size_t)255u; }

@@ -8,21 +8,29 @@
 // All of this is HBM-bound byte work: 2 B read + 1 B + 4/128 B written per
 // element one way, the mirror image the other way.  There is no contraction,
 // so no tensor cores.  What matters is coalescing, bytes in flight per SM and
-// an instruction count per element that stays under the issue budget.
+// an instruction count per element that stays under the issue budget
+// (~18 lane-instructions per element at full HBM rate; in practice ~10).
 //
-// Compress tile: 256 threads x 4 x 16-byte loads = 8192 elements = 64 blocks of
-// 128.  Sixteen consecutive lanes hold one block, so the block's absmax is four
-// shuffles inside a half-warp.  Codes and scales are written into a shared
-// memory tile (double buffered) and leave the SM as two bulk asynchronous
-// copies (cp.async.bulk.global.shared::cta), so the store path costs one
-// instruction per tile instead of one per thread.  Cluster size is 1 and no
-// multicast is used anywhere.
+// Compress tile: 256 threads x 2 x 32-byte loads = 8192 elements = 64 blocks of
+// 128.  Eight consecutive lanes hold one block (16 elements each), so the
+// block's absmax is three shuffles and the per-block divisions are paid once
+// per 16 elements of a lane.  Codes and scales are written into a shared-memory
+// tile (double buffered) and leave the SM as two bulk asynchronous copies
+// (cp.async.bulk.global.shared::cta), so the store path costs one instruction
+// per tile instead of one per thread.  Cluster size is 1; no multicast.
+//
+// Output addressing is "packed chunks": chunk c of `chunk_elems` elements lives
+// at out + c*chunk_stride, codes first, its scales at a byte offset inside the
+// chunk.  One launch can therefore fill a staging tile made of several
+// self-contained chunks, each of which then crosses the host link as a single
+// copy.  The plain (codes*, scales*) entry points are the one-chunk case.
 //
 // Arithmetic is IEEE binary32 throughout: this file must be compiled WITHOUT
 // --use_fast_math and without -ftz; the operations whose rounding matters use
 // the explicit _rn intrinsics so that no FMA contraction can change a result.
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -32,11 +40,13 @@ namespace flame_b200 {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kVec = 8;                                   // BF16 per 16-byte load
-constexpr int kUnroll = 4;                                // loads in flight per thread
-constexpr int kTileElems = kThreads * kVec * kUnroll;     // 8192
-constexpr int kTileBlocks = kTileElems / 128;             // 64 scales per tile
-constexpr int kLanesPerBlock = 128 / kVec;                // 16
+constexpr int kLaneElems = 16;                               // BF16 per 32-byte load
+constexpr int kUnroll = 2;                                   // loads in flight per thread
+constexpr int kTileElems = kThreads * kLaneElems * kUnroll;  // 8192
+constexpr int kTileBlocks = kTileElems / 128;                // 64 scales per tile
+constexpr int kLanesPerBlock = 128 / kLaneElems;             // 8
+
+struct U32x8 { uint32_t v[8]; };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -55,99 +65,121 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 // Orders this thread's shared-memory writes before later async-proxy reads.
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__device__ __forceinline__ uint4 ld_stream16(const void* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
-__device__ __forceinline__ uint2 ld_stream8(const void* p) { return __ldcs(reinterpret_cast<const uint2*>(p)); }
+// 32-byte streaming load / store (256-bit accesses exist from sm_100 on).
+__device__ __forceinline__ U32x8 ld_stream32(const void* p) {
+  U32x8 r;
+  asm volatile("ld.global.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]),
+                 "=r"(r.v[4]), "=r"(r.v[5]), "=r"(r.v[6]), "=r"(r.v[7]) : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void st_stream32(void* p, const U32x8& r) {
+  asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               :: "l"(p), "r"(r.v[0]), "r"(r.v[1]), "r"(r.v[2]), "r"(r.v[3]),
+                  "r"(r.v[4]), "r"(r.v[5]), "r"(r.v[6]), "r"(r.v[7]) : "memory");
+}
 
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 
-__device__ __forceinline__ void unpack8(const uint4& r, float (&x)[8]) {
-  x[0] = bf16lo(r.x); x[1] = bf16hi(r.x);
-  x[2] = bf16lo(r.y); x[3] = bf16hi(r.y);
-  x[4] = bf16lo(r.z); x[5] = bf16hi(r.z);
-  x[6] = bf16lo(r.w); x[7] = bf16hi(r.w);
+__device__ __forceinline__ void unpack16(const U32x8& r, float (&x)[16]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { x[2 * i] = bf16lo(r.v[i]); x[2 * i + 1] = bf16hi(r.v[i]); }
 }
 
 // fmaxf ignores a NaN operand, so a NaN element never becomes the absmax.
-__device__ __forceinline__ float absmax8(const float (&x)[8]) {
-  float m = fmaxf(fabsf(x[0]), fabsf(x[1]));
-  m = fmaxf(m, fmaxf(fabsf(x[2]), fabsf(x[3])));
-  m = fmaxf(m, fmaxf(fabsf(x[4]), fabsf(x[5])));
-  m = fmaxf(m, fmaxf(fabsf(x[6]), fabsf(x[7])));
-  return m;
+template <int N>
+__device__ __forceinline__ float absmax_n(const float (&x)[N]) {
+  float m0 = fabsf(x[0]), m1 = fabsf(x[1]);
+#pragma unroll
+  for (int i = 2; i < N; i += 2) { m0 = fmaxf(m0, fabsf(x[i])); m1 = fmaxf(m1, fabsf(x[i + 1])); }
+  return fmaxf(m0, m1);
 }
 
-// Max over the 16 lanes that hold one 128-element block.
-__device__ __forceinline__ float absmax_halfwarp(float m) {
-  m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 8));
+// Max over the 8 lanes that hold one 128-element block.
+__device__ __forceinline__ float absmax_8lanes(float m) {
   m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 4));
   m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
   m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
   return m;
 }
 
-// ---- int8 -----------------------------------------------------------------
-
-// round-to-nearest-even to a saturated signed byte; NaN gives 0.
-__device__ __forceinline__ uint32_t f32_to_s8(float q) {
-  int r;
-  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(q));
-  return static_cast<uint32_t>(r) & 0xFFu;
+// ---- correctly rounded quotients without a division per element ----------------
+// Markstein's sequence: with r = RN(1/s), q0 = RN(x*r), e = x - q0*s (exact, one
+// FMA), q = RN(q0 + e*r) equals RN(x/s) provided s's significand is not all ones
+// and nothing underflows.  `safe_range` keeps every intermediate normal; the
+// rare scale outside it takes the IEEE division.  (Replayed against x/s on the
+// host for every BF16 x and thousands of scales by the test-suite.)
+__device__ __forceinline__ bool markstein_ok(float s) {
+  const uint32_t b = __float_as_uint(s);
+  const uint32_t ex = (b >> 23) & 0xFFu;
+  return (ex >= 64u) && (ex <= 190u) && ((b & 0x7FFFFFu) != 0x7FFFFFu);
 }
 
-// The quotient x/scale, correctly rounded, decides the code.  A full IEEE
-// division per element costs ~10 instructions; instead one correctly rounded
-// reciprocal per block plus a residual correction per element gives the same
-// correctly rounded quotient (Markstein: q0 = x*r, e = x - q0*s exactly by FMA,
-// q = q0 + e*r is RN(x/s) when r = RN(1/s) and s's significand is not all
-// ones).  Blocks whose scale is all-ones, tiny or huge (where e could
-// underflow) take the plain division.
-struct Int8Divider {
-  float scale, inv;
-  bool fast;
-  __device__ __forceinline__ explicit Int8Divider(float s) : scale(s) {
-    const uint32_t b = __float_as_uint(s);
-    const uint32_t ex = (b >> 23) & 0xFFu;
-    fast = (ex >= 64u) && (ex <= 190u) && ((b & 0x7FFFFFu) != 0x7FFFFFu);
-    inv = __frcp_rn(s);
+// amax / D for the two constants 127 and 448 (neither has an all-ones significand).
+template <int D>
+__device__ __forceinline__ float div_const(float amax) {
+  const uint32_t ex = (__float_as_uint(amax) >> 23) & 0xFFu;
+  if (ex >= 64u && ex <= 190u) {
+    const float r = 1.0f / (float)D;  // folded at compile time, correctly rounded
+    const float q0 = __fmul_rn(amax, r);
+    const float e = __fmaf_rn(-q0, (float)D, amax);
+    return __fmaf_rn(e, r, q0);
   }
-  __device__ __forceinline__ float quotient(float x) const {
-    if (fast) {
-      const float q0 = __fmul_rn(x, inv);
-      const float e = __fmaf_rn(-q0, scale, x);
-      return __fmaf_rn(e, inv, q0);
-    }
-    return __fdiv_rn(x, scale);
-  }
-};
+  return __fdiv_rn(amax, (float)D);
+}
 
-template <bool kMulInv>
-__device__ __forceinline__ uint2 encode8_int8(const float (&x)[8], float scale) {
-  uint32_t c[8];
+// ---- int8 -----------------------------------------------------------------
+
+__device__ __forceinline__ int f32_to_s32_rne(float q) {  // NaN -> 0
+  int r;
+  asm("cvt.rni.s32.f32 %0, %1;" : "=r"(r) : "f"(q));
+  return r;
+}
+
+// Saturate four ints to signed bytes and pack them, e0 in the lowest byte.
+__device__ __forceinline__ uint32_t pack_s8x4(int e0, int e1, int e2, int e3) {
+  uint32_t hi, d;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(e3), "r"(e2), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(e1), "r"(e0), "r"(hi));
+  return d;
+}
+
+template <int N, bool kMulInv>
+__device__ __forceinline__ void encode_int8(const float (&x)[N], float amax, float& scale, uint32_t (&out)[N / 4]) {
+  scale = div_const<127>(amax);
+  int r[N];
   if (kMulInv) {
     const float inv = __fdiv_rn(1.0f, scale);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) c[i] = f32_to_s8(__fmul_rn(x[i], inv));
-  } else {
-    const Int8Divider d(scale);
+    for (int i = 0; i < N; ++i) r[i] = max(f32_to_s32_rne(__fmul_rn(x[i], inv)), -127);  // -inf would pack as -128
+  } else if (markstein_ok(scale)) {
+    const float inv = __frcp_rn(scale);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) c[i] = f32_to_s8(d.quotient(x[i]));
+    for (int i = 0; i < N; ++i) {
+      const float q0 = __fmul_rn(x[i], inv);
+      const float e = __fmaf_rn(-q0, scale, x[i]);
+      r[i] = f32_to_s32_rne(__fmaf_rn(e, inv, q0));
+    }
+  } else {
+    // scale == 0 lands here: 0/0 is NaN, which converts to 0.
+#pragma unroll
+    for (int i = 0; i < N; ++i) r[i] = f32_to_s32_rne(__fdiv_rn(x[i], scale));
   }
-  // scale == 0 (all-zero block): 0/0 and 0*inf are NaN, which encodes as 0.
-  uint2 o;
-  o.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
-  o.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
-  return o;
+#pragma unroll
+  for (int i = 0; i < N / 4; ++i) out[i] = pack_s8x4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
 }
 
 // ---- FP8 E4M3, the reference's encoder (src/cuda/fp8_quant.cu:19-57) --------
-// Integer restatement: adding 1<<19 to the magnitude bits rounds the mantissa
-// half-up to 3 bits with carry into the exponent; >>20 leaves exponent*8+mant;
-// -960 re-biases (127-7)*8.  Anything that lands in exponent 15 (>= 248)
-// becomes 0x7F.  Magnitudes under 2^-6 use the reference's float formula
-// (int)(v*512 + 0.5f) clamped to 7.  The sign comes from `y < 0`, so -0.0
-// encodes as 0x00 while a negative value that rounds to zero encodes as 0x80.
-__device__ __forceinline__ uint32_t fp8_encode_ref(float y) {
+// Exact scalar restatement in integer arithmetic: adding 1<<19 to the magnitude
+// bits rounds the mantissa half-up to 3 bits with carry into the exponent; >>20
+// leaves exponent*8+mant; -960 re-biases (127-7)*8.  Anything that lands in
+// exponent 15 (>= 248) becomes 0x7F.  Magnitudes under 2^-6 use the reference's
+// float formula (int)(v*512 + 0.5f) clamped to 7.  The sign comes from `y < 0`,
+// so -0.0 encodes as 0x00 while a negative value that rounds to zero is 0x80.
+// `x` is the element before scaling: a NaN result takes x's sign bit (the
+// reference leaves NaN undefined; this is this library's definition).
+__device__ __forceinline__ uint32_t fp8_encode_ref(float y, float x) {
   const uint32_t b = __float_as_uint(y);
   const uint32_t a = b & 0x7FFFFFFFu;
   uint32_t c = ((a + 0x80000u) >> 20) - 960u;
@@ -158,59 +190,131 @@ __device__ __forceinline__ uint32_t fp8_encode_ref(float y) {
     c = min(__float_as_uint(__fadd_rd(w, 8388608.0f)) & 0xFu, 7u);
   }
   uint32_t s = (y < 0.0f) ? 0x80u : 0u;
-  if (a > 0x7F800000u) { s = (b >> 24) & 0x80u; c = 0x7Fu; }  // NaN (undefined in the reference)
+  if (a > 0x7F800000u) { s = (__float_as_uint(x) >> 24) & 0x80u; c = 0x7Fu; }
   return s | c;
 }
 
+// y = x * inv, except that a zero element stays zero even when inv is infinite.
+__device__ __forceinline__ float scaled(float x, float inv) { return x == 0.0f ? x : __fmul_rn(x, inv); }
+__device__ __forceinline__ uint32_t fp8_encode_ref_scaled(float x, float inv) { return fp8_encode_ref(scaled(x, inv), x); }
+
+// Fast form of the same encoder for a lane's worth of magnitudes, two at a time,
+// on the conversion hardware.  For 2^-6 <= |y| < 248 the reference rounds the
+// mantissa half-UP; the hardware converter rounds half-to-even.  Truncating |y|
+// to FP16 and setting the lowest mantissa bit moves every value strictly off
+// the rounding boundaries (they are FP16 numbers with a zero low bit) without
+// crossing one, and puts exact ties just above: round-to-nearest-even of that
+// equals round-half-up of |y|.  |y| >= 248 must give 0x7F: those lanes are made
+// NaN, which the converter encodes as 0x7F.  Zero gives 0.  Magnitudes in
+// (0, 2^-6) need the reference's float formula: the caller detects them from
+// `min_nz` (the smallest magnitude among elements whose source is not +-0) and
+// re-encodes the lane with fp8_encode_ref.  `xpair` is the two source BF16.
+__device__ __forceinline__ uint32_t fp8_encode_pair_fast(float ylo_abs, float yhi_abs, uint32_t xpair, __half2& min_nz) {
+  uint32_t h;
+  asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(yhi_abs), "f"(ylo_abs));
+  const __half2 hh = *reinterpret_cast<const __half2*>(&h);
+  const uint32_t sat = __hge2_mask(hh, __half2half2(__ushort_as_half((unsigned short)0x5BC0)));  // 248.0
+  const uint32_t zero = __heq2_mask(*reinterpret_cast<const __nv_bfloat162*>(&xpair), __float2bfloat162_rn(0.0f));
+  const uint32_t hz = h | zero;  // lanes whose source is zero become NaN, which __hmin2 ignores
+  min_nz = __hmin2(min_nz, *reinterpret_cast<const __half2*>(&hz));
+  const uint32_t h2 = h | 0x00010001u | sat;
+  uint16_t c;
+  asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(c) : "r"(h2));
+  return c;  // low byte = code(ylo), high byte = code(yhi); bit 7 may be set on saturated lanes
+}
+
 // OCP E4M3: round-to-nearest-even, saturate to +-448.  The hardware converter
-// does exactly this.
+// does exactly this (NaN -> 0x7F/0xFF).
 __device__ __forceinline__ uint32_t fp8_encode_ocp_pair(float lo, float hi) {
   uint16_t r;
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
   return r;
 }
 
-template <bool kOcp>
-__device__ __forceinline__ uint2 encode8_fp8(const float (&x)[8], float amax, float scale) {
-  uint2 o = make_uint2(0u, 0u);
-  if (amax == 0.0f) return o;  // all-zero block: codes 0, scale 0
-  const float inv = __fdiv_rn(1.0f, scale);
-  float y[8];
+// raw: the N/2 input words (two BF16 each), needed for the sign bits.
+template <int N, bool kOcp>
+__device__ __forceinline__ void encode_fp8(const float (&x)[N], const uint32_t* raw, float amax, float& scale,
+                                           uint32_t (&out)[N / 4]) {
+  scale = div_const<448>(amax);
+  if (amax == 0.0f) {  // all-zero block: codes 0, scale 0
 #pragma unroll
-  for (int i = 0; i < 8; ++i) y[i] = __fmul_rn(x[i], inv);
-  if (kOcp) {
-    o.x = fp8_encode_ocp_pair(y[0], y[1]) | (fp8_encode_ocp_pair(y[2], y[3]) << 16);
-    o.y = fp8_encode_ocp_pair(y[4], y[5]) | (fp8_encode_ocp_pair(y[6], y[7]) << 16);
-    // the converter turns NaN into 0x7F/0xFF already
-  } else {
-    uint32_t c[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) c[i] = fp8_encode_ref(y[i]);
-    o.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
-    o.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+    for (int i = 0; i < N / 4; ++i) out[i] = 0u;
+    return;
   }
-  return o;
+  const float inv = __frcp_rn(scale);  // == RN(1/scale)
+  if (!(inv < 3.0e38f)) {  // sub-normal scale: 1/scale overflowed; exact element-wise path
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) {
+      uint32_t w = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float xv = x[4 * i + k], y = scaled(xv, inv);
+        w |= (kOcp ? (fp8_encode_ocp_pair(y, 0.0f) & 0xFFu) : fp8_encode_ref(y, xv)) << (8 * k);
+      }
+      out[i] = w;
+    }
+    return;
+  }
+  if (kOcp) {
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i)
+      out[i] = fp8_encode_ocp_pair(__fmul_rn(x[4 * i], inv), __fmul_rn(x[4 * i + 1], inv)) |
+               (fp8_encode_ocp_pair(__fmul_rn(x[4 * i + 2], inv), __fmul_rn(x[4 * i + 3], inv)) << 16);
+    return;
+  }
+  __half2 min_nz = __half2half2(__ushort_as_half((unsigned short)0x7BFF));  // 65504
+#pragma unroll
+  for (int i = 0; i < N / 4; ++i) {
+    const uint32_t c01 = fp8_encode_pair_fast(__fmul_rn(fabsf(x[4 * i]), inv), __fmul_rn(fabsf(x[4 * i + 1]), inv), raw[2 * i], min_nz);
+    const uint32_t c23 = fp8_encode_pair_fast(__fmul_rn(fabsf(x[4 * i + 2]), inv), __fmul_rn(fabsf(x[4 * i + 3]), inv), raw[2 * i + 1], min_nz);
+    const uint32_t mag = (c01 | (c23 << 16)) & 0x7F7F7F7Fu;
+    // sign bytes of the four BF16 (their high bytes); a zero magnitude keeps sign 0,
+    // which is what `val < 0` gives for +-0.0
+    const uint32_t sgn = __byte_perm(raw[2 * i], raw[2 * i + 1], 0x7531);
+    const uint32_t nz = (mag + 0x7F7F7F7Fu) & 0x80808080u;
+    out[i] = mag | (sgn & nz);
+  }
+  // any magnitude in (0, 2^-6)?  (0x2400 = 2^-6 in FP16)
+  const __half lo = __low2half(min_nz), hi = __high2half(min_nz);
+  if (__hlt(__hmin(lo, hi), __ushort_as_half((unsigned short)0x2400))) {
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i)
+      out[i] = fp8_encode_ref_scaled(x[4 * i], inv) | (fp8_encode_ref_scaled(x[4 * i + 1], inv) << 8) |
+               (fp8_encode_ref_scaled(x[4 * i + 2], inv) << 16) | (fp8_encode_ref_scaled(x[4 * i + 3], inv) << 24);
+  }
 }
 
-template <int kCodec, bool kFlag>
-__device__ __forceinline__ uint2 encode8(const float (&x)[8], float amax, float& scale) {
-  if (kCodec == kCodecInt8) {
-    scale = __fdiv_rn(amax, 127.0f);
-    return encode8_int8<kFlag>(x, scale);
-  } else {
-    scale = __fdiv_rn(amax, 448.0f);
-    return encode8_fp8<kFlag>(x, amax, scale);
-  }
+template <int kCodec, bool kFlag, int N>
+__device__ __forceinline__ void encode_block_part(const float (&x)[N], const uint32_t* raw, float amax, float& scale,
+                                                  uint32_t (&out)[N / 4]) {
+  if (kCodec == kCodecInt8) encode_int8<N, kFlag>(x, amax, scale, out);
+  else encode_fp8<N, kFlag>(x, raw, amax, scale, out);
+}
+
+// Where a block's output goes (see the header comment on packed chunks).
+struct OutAddr {
+  uint8_t* codes;
+  float* scales;
+};
+__device__ __forceinline__ OutAddr locate(uint8_t* base, const PackedLayout& L, size_t elem0) {
+  size_t c = 0, within = elem0;
+  if (elem0 >= L.chunk_elems) { c = elem0 / L.chunk_elems; within = elem0 - c * L.chunk_elems; }
+  uint8_t* cb = base + (int64_t)c * L.chunk_stride;
+  const int64_t so = (c == L.last_chunk) ? L.scales_off_last : L.scales_off;
+  return {cb + within, reinterpret_cast<float*>(cb + so) + within / 128};
+}
+__device__ __forceinline__ OutAddr locate(const uint8_t* base, const PackedLayout& L, size_t elem0) {
+  return locate(const_cast<uint8_t*>(base), L, elem0);
 }
 
 // ---- compress kernel --------------------------------------------------------
-// Requires: in 16-byte aligned, codes 16-byte aligned, scales 16-byte aligned.
-// Full tiles go through the shared-memory tiles and bulk stores; the last,
-// partial tile uses predicated loads and direct stores.
+// Requires: in 32-byte aligned; every chunk's codes and scales 16-byte aligned;
+// chunk_elems a multiple of 8192 (or >= n).  Full tiles go through the shared
+// memory tiles and bulk stores; the last, partial tile uses predicated loads and
+// direct stores.
 template <int kCodec, bool kFlag>
 __global__ void __launch_bounds__(kThreads)
-compress_b128_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ codes,
-                     float* __restrict__ scales, size_t n) {
+compress_b128_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ out, size_t n, PackedLayout L) {
   __shared__ __align__(128) uint8_t s_codes[2][kTileElems];
   __shared__ __align__(128) float s_scales[2][kTileBlocks];
 
@@ -220,9 +324,9 @@ compress_b128_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ code
 
   for (size_t tile = blockIdx.x; tile < full_tiles; tile += gridDim.x) {
     const uint16_t* tin = in + tile * kTileElems;
-    uint4 raw[kUnroll];
+    U32x8 raw[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) raw[u] = ld_stream16(tin + (size_t)(u * kThreads + tid) * kVec);
+    for (int u = 0; u < kUnroll; ++u) raw[u] = ld_stream32(tin + (size_t)(u * kThreads + tid) * kLaneElems);
 
     // The bulk store issued two tiles ago read this buffer; it must be done.
     if (tid == 0) bulk_wait_read<1>();
@@ -230,20 +334,22 @@ compress_b128_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ code
 
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      float x[8];
-      unpack8(raw[u], x);
-      const float amax = absmax_halfwarp(absmax8(x));
+      float x[kLaneElems];
+      unpack16(raw[u], x);
+      const float amax = absmax_8lanes(absmax_n<kLaneElems>(x));
       float scale;
-      const uint2 c = encode8<kCodec, kFlag>(x, amax, scale);
+      uint32_t c[kLaneElems / 4];
+      encode_block_part<kCodec, kFlag, kLaneElems>(x, raw[u].v, amax, scale, c);
       const int v = u * kThreads + tid;
-      *reinterpret_cast<uint2*>(&s_codes[buf][v * kVec]) = c;
+      *reinterpret_cast<uint4*>(&s_codes[buf][v * kLaneElems]) = make_uint4(c[0], c[1], c[2], c[3]);
       if ((tid & (kLanesPerBlock - 1)) == 0) s_scales[buf][v / kLanesPerBlock] = scale;
     }
     fence_async_smem();
     __syncthreads();
     if (tid == 0) {
-      bulk_store(codes + tile * kTileElems, s_codes[buf], kTileElems);
-      bulk_store(scales + tile * kTileBlocks, s_scales[buf], kTileBlocks * sizeof(float));
+      const OutAddr o = locate(out, L, tile * kTileElems);
+      bulk_store(o.codes, s_codes[buf], kTileElems);
+      bulk_store(o.scales, s_scales[buf], kTileBlocks * sizeof(float));
       bulk_commit();
     }
     buf ^= 1;
@@ -254,32 +360,35 @@ compress_b128_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ code
   if (tail0 < n && (full_tiles % gridDim.x) == blockIdx.x) {
     const uint16_t* tin = in + tail0;
     const size_t rem = n - tail0;
+    const OutAddr o = locate(out, L, tail0);
 #pragma unroll 1
     for (int u = 0; u < kUnroll; ++u) {
-      const size_t e0 = (size_t)(u * kThreads + tid) * kVec;
+      const size_t e0 = (size_t)(u * kThreads + tid) * kLaneElems;
       // whole warps enter together so the shuffles stay converged
-      if (((size_t)(u * kThreads + (tid & ~31)) * kVec) >= rem) break;
-      uint4 r = make_uint4(0u, 0u, 0u, 0u);
-      if (e0 + kVec <= rem) {
-        r = ld_stream16(tin + e0);
+      if (((size_t)(u * kThreads + (tid & ~31)) * kLaneElems) >= rem) break;
+      U32x8 r;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) r.v[i] = 0u;
+      if (e0 + kLaneElems <= rem) {
+        r = ld_stream32(tin + e0);
       } else if (e0 < rem) {
-        uint16_t tmp[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (size_t i = 0; e0 + i < rem; ++i) tmp[i] = tin[e0 + i];
-        r.x = tmp[0] | ((uint32_t)tmp[1] << 16); r.y = tmp[2] | ((uint32_t)tmp[3] << 16);
-        r.z = tmp[4] | ((uint32_t)tmp[5] << 16); r.w = tmp[6] | ((uint32_t)tmp[7] << 16);
+        for (size_t i = 0; e0 + i < rem; ++i) {
+          const uint32_t h = tin[e0 + i];
+          r.v[i >> 1] |= (i & 1) ? (h << 16) : h;
+        }
       }
-      float x[8];
-      unpack8(r, x);
-      const float amax = absmax_halfwarp(absmax8(x));
+      float x[kLaneElems];
+      unpack16(r, x);
+      const float amax = absmax_8lanes(absmax_n<kLaneElems>(x));
       float scale;
-      const uint2 c = encode8<kCodec, kFlag>(x, amax, scale);
-      if (e0 + kVec <= rem) {
-        *reinterpret_cast<uint2*>(codes + tail0 + e0) = c;
+      uint32_t c[kLaneElems / 4];
+      encode_block_part<kCodec, kFlag, kLaneElems>(x, r.v, amax, scale, c);
+      if (e0 + kLaneElems <= rem) {
+        *reinterpret_cast<uint4*>(o.codes + e0) = make_uint4(c[0], c[1], c[2], c[3]);
       } else if (e0 < rem) {
-        const uint64_t cc = ((uint64_t)c.y << 32) | c.x;
-        for (size_t i = 0; e0 + i < rem; ++i) codes[tail0 + e0 + i] = (uint8_t)(cc >> (8 * i));
+        for (size_t i = 0; e0 + i < rem; ++i) o.codes[e0 + i] = (uint8_t)(c[i >> 2] >> (8 * (i & 3)));
       }
-      if ((tid & (kLanesPerBlock - 1)) == 0 && e0 < rem) scales[(tail0 + e0) / 128] = scale;
+      if ((tid & (kLanesPerBlock - 1)) == 0 && e0 < rem) o.scales[e0 / 128] = scale;
     }
   }
 
@@ -289,25 +398,28 @@ compress_b128_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ code
 // Any alignment, any n: one warp per 128-element block, scalar accesses.
 template <int kCodec, bool kFlag>
 __global__ void __launch_bounds__(kThreads)
-compress_b128_generic_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ codes,
-                             float* __restrict__ scales, size_t n) {
+compress_b128_generic_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ out, size_t n, PackedLayout L) {
   const size_t nblocks = (n + 127) / 128;
   const int lane = threadIdx.x & 31;
   const size_t warp0 = (size_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
   const size_t nwarps = (size_t)gridDim.x * (kThreads / 32);
   for (size_t blk = warp0; blk < nblocks; blk += nwarps) {
     const size_t e0 = blk * 128 + (size_t)lane * 4;
-    float x[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint32_t raw[2] = {0u, 0u};
     for (int i = 0; i < 4; ++i)
-      if (e0 + i < n) x[i] = __uint_as_float((uint32_t)in[e0 + i] << 16);
-    float m = absmax8(x);
+      if (e0 + i < n) raw[i >> 1] |= (uint32_t)in[e0 + i] << (16 * (i & 1));
+    float x[4] = {bf16lo(raw[0]), bf16hi(raw[0]), bf16lo(raw[1]), bf16hi(raw[1])};
+    float m = absmax_n<4>(x);
     m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 16));
-    const float amax = absmax_halfwarp(m);
+    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 8));
+    const float amax = absmax_8lanes(m);
     float scale;
-    const uint2 c = encode8<kCodec, kFlag>(x, amax, scale);
+    uint32_t c[1];
+    encode_block_part<kCodec, kFlag, 4>(x, raw, amax, scale, c);
+    const OutAddr o = locate(out, L, blk * 128);
     for (int i = 0; i < 4; ++i)
-      if (e0 + i < n) codes[e0 + i] = (uint8_t)(c.x >> (8 * i));
-    if (lane == 0) scales[blk] = scale;
+      if (e0 + i < n) o.codes[(size_t)lane * 4 + i] = (uint8_t)(c[0] >> (8 * i));
+    if (lane == 0) o.scales[0] = scale;
   }
 }
 
@@ -322,7 +434,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // Signed byte k of w as a float, exactly: 2^23 + (code ^ 0x80) - (2^23 + 128).
 template <int k>
 __device__ __forceinline__ float s8_to_f32(uint32_t w_flipped) {
-  const uint32_t bits = __byte_perm(w_flipped, 0x4B000000u, 0x7650 | k) ;
+  const uint32_t bits = __byte_perm(w_flipped, 0x4B000000u, 0x7650 | k);
   return __fsub_rn(__uint_as_float(bits), 8388736.0f);
 }
 
@@ -336,97 +448,121 @@ __device__ __forceinline__ float fp8_to_f32_scaled(uint32_t w) {
   return __fmul_rn(__uint_as_float(bits), 1.329227995784916e36f);  // * 2^120, exact
 }
 
+// Four codes in one word -> two words of BF16.
 template <int kCodec>
-__device__ __forceinline__ uint4 decode8(uint2 c, float scale) {
-  float v[8];
+__device__ __forceinline__ void decode4(uint32_t c, float scale, uint32_t& o0, uint32_t& o1) {
+  float v0, v1, v2, v3;
   if (kCodec == kCodecInt8) {
-    const uint32_t a = c.x ^ 0x80808080u, b = c.y ^ 0x80808080u;
-    v[0] = s8_to_f32<0>(a); v[1] = s8_to_f32<1>(a); v[2] = s8_to_f32<2>(a); v[3] = s8_to_f32<3>(a);
-    v[4] = s8_to_f32<0>(b); v[5] = s8_to_f32<1>(b); v[6] = s8_to_f32<2>(b); v[7] = s8_to_f32<3>(b);
+    const uint32_t a = c ^ 0x80808080u;
+    v0 = s8_to_f32<0>(a); v1 = s8_to_f32<1>(a); v2 = s8_to_f32<2>(a); v3 = s8_to_f32<3>(a);
   } else {
-    v[0] = fp8_to_f32_scaled<0>(c.x); v[1] = fp8_to_f32_scaled<1>(c.x);
-    v[2] = fp8_to_f32_scaled<2>(c.x); v[3] = fp8_to_f32_scaled<3>(c.x);
-    v[4] = fp8_to_f32_scaled<0>(c.y); v[5] = fp8_to_f32_scaled<1>(c.y);
-    v[6] = fp8_to_f32_scaled<2>(c.y); v[7] = fp8_to_f32_scaled<3>(c.y);
+    v0 = fp8_to_f32_scaled<0>(c); v1 = fp8_to_f32_scaled<1>(c); v2 = fp8_to_f32_scaled<2>(c); v3 = fp8_to_f32_scaled<3>(c);
   }
-#pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], scale);
-  uint4 o;
-  o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-  o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-  return o;
+  o0 = pack_bf16x2(__fmul_rn(v0, scale), __fmul_rn(v1, scale));
+  o1 = pack_bf16x2(__fmul_rn(v2, scale), __fmul_rn(v3, scale));
 }
 
-// Requires: codes 8-byte aligned, out 16-byte aligned.  Each thread turns 8
-// codes (one 8-byte load) into 8 BF16 (one 16-byte store); the 16 lanes of a
-// block read the same scale, which the L1 serves.
+template <int kCodec>
+__device__ __forceinline__ uint16_t decode1(uint8_t c, float scale) {
+  uint32_t o0, o1;
+  decode4<kCodec>(c, scale, o0, o1);
+  return (uint16_t)(o0 & 0xFFFFu);
+}
+
+// Requires: every chunk's codes 16-byte aligned, out 32-byte aligned.  Each
+// thread turns 16 codes (one 16-byte load) into 16 BF16 (one 32-byte store);
+// the 8 lanes of a block read the same scale, which the L1 serves.
 template <int kCodec>
 __global__ void __launch_bounds__(kThreads)
-dequant_b128_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ scales,
-                    uint16_t* __restrict__ out, size_t n) {
+dequant_b128_kernel(const uint8_t* __restrict__ in, uint16_t* __restrict__ out, size_t n, PackedLayout L) {
+  constexpr int kDU = 4;  // 16-byte loads in flight per thread
   const int tid = threadIdx.x;
-  const size_t nvec = n / kVec;  // whole 8-element vectors
-  const size_t tiles = (nvec + kThreads * kUnroll - 1) / (kThreads * kUnroll);
+  const size_t nvec = n / kLaneElems;  // whole 16-element vectors
+  const size_t tiles = (nvec + kThreads * kDU - 1) / (kThreads * kDU);
   for (size_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-    const size_t v0 = tile * (kThreads * kUnroll);
-    uint2 c[kUnroll];
-    float s[kUnroll];
+    const size_t v0 = tile * (kThreads * kDU);
+    const OutAddr A = locate(in, L, v0 * kLaneElems);  // a tile never straddles chunks
+    uint4 c[kDU];
+    float s[kDU];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < kDU; ++u) {
       const size_t v = v0 + (size_t)(u * kThreads + tid);
       if (v < nvec) {
-        c[u] = ld_stream8(codes + v * kVec);
-        s[u] = __ldg(scales + v / kLanesPerBlock);
+        const int lv = u * kThreads + tid;
+        c[u] = __ldcs(reinterpret_cast<const uint4*>(A.codes + (size_t)lv * kLaneElems));
+        s[u] = __ldg(A.scales + lv / kLanesPerBlock);
       }
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < kDU; ++u) {
       const size_t v = v0 + (size_t)(u * kThreads + tid);
-      if (v < nvec) __stcs(reinterpret_cast<uint4*>(out + v * kVec), decode8<kCodec>(c[u], s[u]));
+      if (v < nvec) {
+        U32x8 o;
+        decode4<kCodec>(c[u].x, s[u], o.v[0], o.v[1]);
+        decode4<kCodec>(c[u].y, s[u], o.v[2], o.v[3]);
+        decode4<kCodec>(c[u].z, s[u], o.v[4], o.v[5]);
+        decode4<kCodec>(c[u].w, s[u], o.v[6], o.v[7]);
+        st_stream32(out + v * kLaneElems, o);
+      }
     }
   }
-  // up to 7 trailing elements
-  const size_t t0 = nvec * kVec;
+  // up to 15 trailing elements
+  const size_t t0 = nvec * kLaneElems;
   if (blockIdx.x == 0 && tid < (int)(n - t0)) {
     const size_t e = t0 + tid;
-    uint2 c = make_uint2(codes[e], 0u);
-    const uint4 o = decode8<kCodec>(c, scales[e / 128]);
-    out[e] = (uint16_t)(o.x & 0xFFFFu);
+    const OutAddr a = locate(in, L, e & ~(size_t)127);
+    out[e] = decode1<kCodec>(a.codes[e & 127], a.scales[0]);
   }
 }
 
 template <int kCodec>
 __global__ void __launch_bounds__(kThreads)
-dequant_b128_generic_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ scales,
-                            uint16_t* __restrict__ out, size_t n) {
+dequant_b128_generic_kernel(const uint8_t* __restrict__ in, uint16_t* __restrict__ out, size_t n, PackedLayout L) {
   const size_t stride = (size_t)gridDim.x * kThreads;
   for (size_t e = (size_t)blockIdx.x * kThreads + threadIdx.x; e < n; e += stride) {
-    const uint4 o = decode8<kCodec>(make_uint2(codes[e], 0u), scales[e / 128]);
-    out[e] = (uint16_t)(o.x & 0xFFFFu);
+    const OutAddr a = locate(in, L, e & ~(size_t)127);
+    out[e] = decode1<kCodec>(a.codes[e & 127], a.scales[0]);
   }
 }
 
 // ---- element-wise FP8 with a caller-supplied scale --------------------------
+// Same arithmetic as flame_bf16_to_fp8 / flame_fp8_to_bf16 in the reference; 16
+// elements per thread per iteration with the fast encoder where it applies.
 
 __global__ void __launch_bounds__(kThreads)
 bf16_to_fp8_vec_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ out, float inv_scale, size_t n) {
-  const size_t nvec = n / kVec;
+  const size_t nvec = n / kLaneElems;
   const size_t stride = (size_t)gridDim.x * kThreads;
   for (size_t v = (size_t)blockIdx.x * kThreads + threadIdx.x; v < nvec; v += stride) {
-    float x[8];
-    unpack8(ld_stream16(in + v * kVec), x);
-    uint32_t c[8];
+    const U32x8 r = ld_stream32(in + v * kLaneElems);
+    float x[kLaneElems];
+    unpack16(r, x);
+    uint32_t c[4];
+    bool slow = !(inv_scale > 0.0f) || !(inv_scale < 3.0e38f);  // sign of y must equal sign of x
+    if (!slow) {
+      __half2 min_nz = __half2half2(__ushort_as_half((unsigned short)0x7BFF));
 #pragma unroll
-    for (int i = 0; i < 8; ++i) c[i] = fp8_encode_ref(__fmul_rn(x[i], inv_scale));
-    uint2 o;
-    o.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
-    o.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
-    __stcs(reinterpret_cast<uint2*>(out + v * kVec), o);
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t c01 = fp8_encode_pair_fast(__fmul_rn(fabsf(x[4 * i]), inv_scale), __fmul_rn(fabsf(x[4 * i + 1]), inv_scale), r.v[2 * i], min_nz);
+        const uint32_t c23 = fp8_encode_pair_fast(__fmul_rn(fabsf(x[4 * i + 2]), inv_scale), __fmul_rn(fabsf(x[4 * i + 3]), inv_scale), r.v[2 * i + 1], min_nz);
+        const uint32_t mag = (c01 | (c23 << 16)) & 0x7F7F7F7Fu;
+        const uint32_t sgn = __byte_perm(r.v[2 * i], r.v[2 * i + 1], 0x7531);
+        c[i] = mag | (sgn & ((mag + 0x7F7F7F7Fu) & 0x80808080u));
+      }
+      slow = __hlt(__hmin(__low2half(min_nz), __high2half(min_nz)), __ushort_as_half((unsigned short)0x2400));
+    }
+    if (slow) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        c[i] = fp8_encode_ref_scaled(x[4 * i], inv_scale) | (fp8_encode_ref_scaled(x[4 * i + 1], inv_scale) << 8) |
+               (fp8_encode_ref_scaled(x[4 * i + 2], inv_scale) << 16) | (fp8_encode_ref_scaled(x[4 * i + 3], inv_scale) << 24);
+    }
+    __stcs(reinterpret_cast<uint4*>(out + v * kLaneElems), make_uint4(c[0], c[1], c[2], c[3]));
   }
-  const size_t t0 = nvec * kVec;
+  const size_t t0 = nvec * kLaneElems;
   if (blockIdx.x == 0 && threadIdx.x < (unsigned)(n - t0)) {
     const size_t e = t0 + threadIdx.x;
-    out[e] = (uint8_t)fp8_encode_ref(__fmul_rn(__uint_as_float((uint32_t)in[e] << 16), inv_scale));
+    out[e] = (uint8_t)fp8_encode_ref_scaled(__uint_as_float((uint32_t)in[e] << 16), inv_scale);
   }
 }
 
@@ -434,19 +570,26 @@ __global__ void __launch_bounds__(kThreads)
 bf16_to_fp8_scalar_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ out, float inv_scale, size_t n) {
   const size_t stride = (size_t)gridDim.x * kThreads;
   for (size_t e = (size_t)blockIdx.x * kThreads + threadIdx.x; e < n; e += stride)
-    out[e] = (uint8_t)fp8_encode_ref(__fmul_rn(__uint_as_float((uint32_t)in[e] << 16), inv_scale));
+    out[e] = (uint8_t)fp8_encode_ref_scaled(__uint_as_float((uint32_t)in[e] << 16), inv_scale);
 }
 
 __global__ void __launch_bounds__(kThreads)
 fp8_to_bf16_vec_kernel(const uint8_t* __restrict__ in, uint16_t* __restrict__ out, float scale, size_t n) {
-  const size_t nvec = n / kVec;
+  const size_t nvec = n / kLaneElems;
   const size_t stride = (size_t)gridDim.x * kThreads;
-  for (size_t v = (size_t)blockIdx.x * kThreads + threadIdx.x; v < nvec; v += stride)
-    __stcs(reinterpret_cast<uint4*>(out + v * kVec), decode8<kCodecFp8>(ld_stream8(in + v * kVec), scale));
-  const size_t t0 = nvec * kVec;
+  for (size_t v = (size_t)blockIdx.x * kThreads + threadIdx.x; v < nvec; v += stride) {
+    const uint4 c = __ldcs(reinterpret_cast<const uint4*>(in + v * kLaneElems));
+    U32x8 o;
+    decode4<kCodecFp8>(c.x, scale, o.v[0], o.v[1]);
+    decode4<kCodecFp8>(c.y, scale, o.v[2], o.v[3]);
+    decode4<kCodecFp8>(c.z, scale, o.v[4], o.v[5]);
+    decode4<kCodecFp8>(c.w, scale, o.v[6], o.v[7]);
+    st_stream32(out + v * kLaneElems, o);
+  }
+  const size_t t0 = nvec * kLaneElems;
   if (blockIdx.x == 0 && threadIdx.x < (unsigned)(n - t0)) {
     const size_t e = t0 + threadIdx.x;
-    out[e] = (uint16_t)(decode8<kCodecFp8>(make_uint2(in[e], 0u), scale).x & 0xFFFFu);
+    out[e] = decode1<kCodecFp8>(in[e], scale);
   }
 }
 
@@ -454,7 +597,7 @@ __global__ void __launch_bounds__(kThreads)
 fp8_to_bf16_scalar_kernel(const uint8_t* __restrict__ in, uint16_t* __restrict__ out, float scale, size_t n) {
   const size_t stride = (size_t)gridDim.x * kThreads;
   for (size_t e = (size_t)blockIdx.x * kThreads + threadIdx.x; e < n; e += stride)
-    out[e] = (uint16_t)(decode8<kCodecFp8>(make_uint2(in[e], 0u), scale).x & 0xFFFFu);
+    out[e] = decode1<kCodecFp8>(in[e], scale);
 }
 
 // ---- launch helpers ---------------------------------------------------------
@@ -483,59 +626,84 @@ int grid_for(size_t work_items, int ctas_per_sm, int max_ctas) {
 }
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+inline bool aligned(int64_t v, int64_t a) { return (v & (a - 1)) == 0; }
+
+bool layout_fast(const void* base, const PackedLayout& L, size_t n) {
+  if (!aligned(base, 16) || !aligned(L.scales_off, 16) || !aligned(L.scales_off_last, 16)) return false;
+  if (L.chunk_elems >= n) return true;
+  return (L.chunk_elems % (2 * kTileElems)) == 0 && aligned(L.chunk_stride, 16);  // 16384: the dequantise tile
+}
 
 }  // namespace
 
 int set_max_ctas(int v) { const int old = g_max_ctas; g_max_ctas = v < 0 ? 0 : v; return old; }
 
-cudaError_t launch_compress(int codec, const void* in, void* codes, void* scales, size_t n,
+PackedLayout single_chunk_layout(const void* codes, const void* scales, size_t n) {
+  PackedLayout L;
+  L.chunk_elems = n ? n : 1;
+  L.chunk_stride = 0;
+  L.scales_off = L.scales_off_last = static_cast<const uint8_t*>(scales) - static_cast<const uint8_t*>(codes);
+  L.last_chunk = 0;
+  return L;
+}
+
+PackedLayout packed_chunks_layout(size_t n, size_t chunk_elems, size_t chunk_stride) {
+  PackedLayout L;
+  L.chunk_elems = chunk_elems;
+  L.chunk_stride = (int64_t)chunk_stride;
+  L.last_chunk = n ? (n - 1) / chunk_elems : 0;
+  const size_t last_elems = n - L.last_chunk * chunk_elems;
+  L.scales_off = (int64_t)((chunk_elems + 255u) & ~(size_t)255u);
+  L.scales_off_last = (int64_t)((last_elems + 255u) & ~(size_t)255u);
+  return L;
+}
+
+cudaError_t launch_compress(int codec, const void* in, void* out, size_t n, const PackedLayout& L,
                             unsigned flags, cudaStream_t stream, int max_ctas) {
   if (n == 0) return cudaSuccess;
-  if (!in || !codes || !scales) return cudaErrorInvalidValue;
+  if (!in || !out) return cudaErrorInvalidValue;
   const bool flag = (flags & 1u) != 0;
   auto* i = static_cast<const uint16_t*>(in);
-  auto* c = static_cast<uint8_t*>(codes);
-  auto* s = static_cast<float*>(scales);
-  if (aligned(in, 16) && aligned(codes, 16) && aligned(scales, 16)) {
+  auto* o = static_cast<uint8_t*>(out);
+  if (aligned(in, 32) && layout_fast(out, L, n)) {
     const size_t tiles = (n + kTileElems - 1) / kTileElems;
     const int grid = grid_for(tiles, 6, max_ctas);
     if (codec == kCodecInt8) {
-      if (flag) compress_b128_kernel<kCodecInt8, true><<<grid, kThreads, 0, stream>>>(i, c, s, n);
-      else compress_b128_kernel<kCodecInt8, false><<<grid, kThreads, 0, stream>>>(i, c, s, n);
+      if (flag) compress_b128_kernel<kCodecInt8, true><<<grid, kThreads, 0, stream>>>(i, o, n, L);
+      else compress_b128_kernel<kCodecInt8, false><<<grid, kThreads, 0, stream>>>(i, o, n, L);
     } else {
-      if (flag) compress_b128_kernel<kCodecFp8, true><<<grid, kThreads, 0, stream>>>(i, c, s, n);
-      else compress_b128_kernel<kCodecFp8, false><<<grid, kThreads, 0, stream>>>(i, c, s, n);
+      if (flag) compress_b128_kernel<kCodecFp8, true><<<grid, kThreads, 0, stream>>>(i, o, n, L);
+      else compress_b128_kernel<kCodecFp8, false><<<grid, kThreads, 0, stream>>>(i, o, n, L);
     }
   } else {
     const size_t warps = (n + 127) / 128;
     const int grid = grid_for((warps + 7) / 8, 8, max_ctas);
     if (codec == kCodecInt8) {
-      if (flag) compress_b128_generic_kernel<kCodecInt8, true><<<grid, kThreads, 0, stream>>>(i, c, s, n);
-      else compress_b128_generic_kernel<kCodecInt8, false><<<grid, kThreads, 0, stream>>>(i, c, s, n);
+      if (flag) compress_b128_generic_kernel<kCodecInt8, true><<<grid, kThreads, 0, stream>>>(i, o, n, L);
+      else compress_b128_generic_kernel<kCodecInt8, false><<<grid, kThreads, 0, stream>>>(i, o, n, L);
     } else {
-      if (flag) compress_b128_generic_kernel<kCodecFp8, true><<<grid, kThreads, 0, stream>>>(i, c, s, n);
-      else compress_b128_generic_kernel<kCodecFp8, false><<<grid, kThreads, 0, stream>>>(i, c, s, n);
+      if (flag) compress_b128_generic_kernel<kCodecFp8, true><<<grid, kThreads, 0, stream>>>(i, o, n, L);
+      else compress_b128_generic_kernel<kCodecFp8, false><<<grid, kThreads, 0, stream>>>(i, o, n, L);
     }
   }
   return cudaGetLastError();
 }
 
-cudaError_t launch_dequant(int codec, const void* codes, const void* scales, void* out, size_t n,
+cudaError_t launch_dequant(int codec, const void* in, void* out, size_t n, const PackedLayout& L,
                            cudaStream_t stream, int max_ctas) {
   if (n == 0) return cudaSuccess;
-  if (!codes || !scales || !out) return cudaErrorInvalidValue;
-  auto* c = static_cast<const uint8_t*>(codes);
-  auto* s = static_cast<const float*>(scales);
+  if (!in || !out) return cudaErrorInvalidValue;
+  auto* c = static_cast<const uint8_t*>(in);
   auto* o = static_cast<uint16_t*>(out);
-  if (aligned(codes, 8) && aligned(out, 16) && aligned(scales, 4)) {
-    const size_t tiles = (n / kVec + kThreads * kUnroll - 1) / (kThreads * kUnroll);
+  if (aligned(out, 32) && layout_fast(in, L, n)) {
+    const size_t tiles = (n / kLaneElems + kThreads * 4 - 1) / (kThreads * 4);
     const int grid = grid_for(tiles ? tiles : 1, 8, max_ctas);
-    if (codec == kCodecInt8) dequant_b128_kernel<kCodecInt8><<<grid, kThreads, 0, stream>>>(c, s, o, n);
-    else dequant_b128_kernel<kCodecFp8><<<grid, kThreads, 0, stream>>>(c, s, o, n);
+    if (codec == kCodecInt8) dequant_b128_kernel<kCodecInt8><<<grid, kThreads, 0, stream>>>(c, o, n, L);
+    else dequant_b128_kernel<kCodecFp8><<<grid, kThreads, 0, stream>>>(c, o, n, L);
   } else {
     const int grid = grid_for((n + kThreads - 1) / kThreads, 8, max_ctas);
-    if (codec == kCodecInt8) dequant_b128_generic_kernel<kCodecInt8><<<grid, kThreads, 0, stream>>>(c, s, o, n);
-    else dequant_b128_generic_kernel<kCodecFp8><<<grid, kThreads, 0, stream>>>(c, s, o, n);
+    if (codec == kCodecInt8) dequant_b128_generic_kernel<kCodecInt8><<<grid, kThreads, 0, stream>>>(c, o, n, L);
+    else dequant_b128_generic_kernel<kCodecFp8><<<grid, kThreads, 0, stream>>>(c, o, n, L);
   }
   return cudaGetLastError();
 }
@@ -544,8 +712,8 @@ cudaError_t launch_bf16_to_fp8(const void* in, void* out, float inv_scale, size_
   if (n == 0) return cudaSuccess;
   auto* i = static_cast<const uint16_t*>(in);
   auto* o = static_cast<uint8_t*>(out);
-  if (aligned(in, 16) && aligned(out, 8)) {
-    const int grid = grid_for((n / kVec + kThreads - 1) / kThreads + 1, 8, max_ctas);
+  if (aligned(in, 32) && aligned(out, 16)) {
+    const int grid = grid_for((n / kLaneElems + kThreads - 1) / kThreads + 1, 8, max_ctas);
     bf16_to_fp8_vec_kernel<<<grid, kThreads, 0, stream>>>(i, o, inv_scale, n);
   } else {
     const int grid = grid_for((n + kThreads - 1) / kThreads, 8, max_ctas);
@@ -558,8 +726,8 @@ cudaError_t launch_fp8_to_bf16(const void* in, void* out, float scale, size_t n,
   if (n == 0) return cudaSuccess;
   auto* i = static_cast<const uint8_t*>(in);
   auto* o = static_cast<uint16_t*>(out);
-  if (aligned(in, 8) && aligned(out, 16)) {
-    const int grid = grid_for((n / kVec + kThreads - 1) / kThreads + 1, 8, max_ctas);
+  if (aligned(in, 16) && aligned(out, 32)) {
+    const int grid = grid_for((n / kLaneElems + kThreads - 1) / kThreads + 1, 8, max_ctas);
     fp8_to_bf16_vec_kernel<<<grid, kThreads, 0, stream>>>(i, o, scale, n);
   } else {
     const int grid = grid_for((n + kThreads - 1) / kThreads, 8, max_ctas);

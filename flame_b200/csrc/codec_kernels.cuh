@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stddef.h>
+#include <stdint.h>
 
 namespace flame_b200 {
 
@@ -9,10 +10,28 @@ namespace flame_b200 {
 constexpr int kCodecInt8 = 2;
 constexpr int kCodecFp8 = 3;
 
+// Addressing of compressed data as a run of self-contained chunks: chunk c holds
+// elements [c*chunk_elems, (c+1)*chunk_elems) and starts at base + c*chunk_stride
+// with its codes; its fp32 scales start scales_off bytes into the chunk
+// (scales_off_last for the final, possibly shorter chunk).
+struct PackedLayout {
+  size_t chunk_elems;
+  int64_t chunk_stride;
+  int64_t scales_off;
+  int64_t scales_off_last;
+  size_t last_chunk;
+};
+
+// One chunk: codes at `codes`, scales at `scales` (any two buffers).
+PackedLayout single_chunk_layout(const void* codes, const void* scales, size_t n);
+// Chunks of `chunk_elems` (a multiple of 16384) every `chunk_stride` bytes, each
+// in the packed layout codes | pad to 256 B | scales.
+PackedLayout packed_chunks_layout(size_t n, size_t chunk_elems, size_t chunk_stride);
+
 // max_ctas: 0 = process default (see set_max_ctas), otherwise a cap on the grid.
-cudaError_t launch_compress(int codec, const void* in_bf16, void* codes, void* scales, size_t n,
+cudaError_t launch_compress(int codec, const void* in_bf16, void* out_base, size_t n, const PackedLayout& layout,
                             unsigned flags, cudaStream_t stream, int max_ctas);
-cudaError_t launch_dequant(int codec, const void* codes, const void* scales, void* out_bf16, size_t n,
+cudaError_t launch_dequant(int codec, const void* in_base, void* out_bf16, size_t n, const PackedLayout& layout,
                            cudaStream_t stream, int max_ctas);
 cudaError_t launch_bf16_to_fp8(const void* in, void* out, float inv_scale, size_t n, cudaStream_t stream, int max_ctas);
 cudaError_t launch_fp8_to_bf16(const void* in, void* out, float scale, size_t n, cudaStream_t stream, int max_ctas);

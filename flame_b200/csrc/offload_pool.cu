@@ -39,7 +39,8 @@ namespace flame_b200 {
 namespace {
 
 constexpr uint64_t kDefaultChunkBytes = 16ull << 20;
-constexpr uint32_t kDefaultTiles = 3;
+constexpr uint32_t kDefaultTiles = 2;
+constexpr uint32_t kDefaultTileChunks = 8;
 constexpr float kLegacyFp8Scale = 8.0f / 448.0f;  // src/activation_offload.rs:548
 
 size_t packed_scales_offset(size_t n) { return (n + 255u) & ~(size_t)255u; }
@@ -120,6 +121,7 @@ struct FlameOffloadPool {
   uint64_t chunk_src_bytes = 0;   // source bytes covered by one chunk
   uint64_t chunk_elems = 0;       // BF16 elements per chunk (compressed modes)
   uint64_t host_chunk_bytes = 0;  // pinned bytes per chunk
+  uint32_t tile_chunks = 1;       // chunks per device staging tile = per codec launch
   uint32_t codec_flags = 0;
   int codec_max_ctas = 0;
 
@@ -207,28 +209,32 @@ cudaError_t enqueue_push(FlameOffloadPool& p, Slot& s, const uint8_t* src, cudaS
     }
   } else {
     POOL_TRY(s.producer.make_wait(p.s_quant), "push: wait(producer)");
-    for (size_t k = 0; k < nchunks; ++k) {
-      const uint64_t e0 = k * p.chunk_elems;
-      const uint64_t e = std::min<uint64_t>(p.chunk_elems, s.numel - e0);
+    // One codec launch fills a staging tile of up to tile_chunks self-contained
+    // chunks; each chunk then crosses the link as one copy.
+    for (size_t k0 = 0; k0 < nchunks; k0 += p.tile_chunks) {
+      const size_t kn = std::min<size_t>(p.tile_chunks, nchunks - k0);
+      const uint64_t e0 = k0 * p.chunk_elems;
+      const uint64_t e = std::min<uint64_t>(kn * p.chunk_elems, s.numel - e0);
       Tile& t = p.out_tiles[p.out_next++ % p.out_tiles.size()];
       POOL_TRY(t.free_.make_wait(p.s_quant), "push: wait(tile free)");
       POOL_TRY(kernel_guard(), "push: compress kernel");
       const void* in = src + 2 * e0;
-      size_t link = 0;
-      if (p.compression == FLAME_OFFLOAD_COMPRESSION_FP8) {
+      if (p.compression == FLAME_OFFLOAD_COMPRESSION_FP8)
         POOL_TRY(launch_bf16_to_fp8(in, t.dev, 1.0f / s.fp8_scale, e, p.s_quant, p.codec_max_ctas), "push: bf16_to_fp8");
-        link = e;
-      } else {
-        POOL_TRY(launch_compress(p.compression, in, t.dev, t.dev + packed_scales_offset(e), e, p.codec_flags,
-                                 p.s_quant, p.codec_max_ctas), "push: compress");
-        link = packed_bytes(e);
-      }
+      else
+        POOL_TRY(launch_compress(p.compression, in, t.dev, e, packed_chunks_layout(e, p.chunk_elems, p.host_chunk_bytes),
+                                 p.codec_flags, p.s_quant, p.codec_max_ctas), "push: compress");
       p.stats.codec_launches++;
       POOL_TRY(t.full.record(p.s_quant), "push: record(tile full)");
       POOL_TRY(t.full.make_wait(p.s_d2h), "push: wait(tile full)");
-      POOL_TRY(memcpy_async_checked(p.chunk_ptr(s.chunks[k]), t.dev, link, cudaMemcpyDeviceToHost, p.s_d2h), "push: D2H");
+      for (size_t j = 0; j < kn; ++j) {
+        const uint64_t ec = std::min<uint64_t>(p.chunk_elems, e - j * p.chunk_elems);
+        const size_t link = p.stored_for(ec);
+        POOL_TRY(memcpy_async_checked(p.chunk_ptr(s.chunks[k0 + j]), t.dev + j * p.host_chunk_bytes, link,
+                                      cudaMemcpyDeviceToHost, p.s_d2h), "push: D2H");
+        p.stats.bytes_link_out += link;
+      }
       POOL_TRY(t.free_.record(p.s_d2h), "push: record(tile free)");
-      p.stats.bytes_link_out += link;
     }
   }
   POOL_TRY(s.d2h_done.record(p.s_d2h), "push: record(d2h_done)");
@@ -252,13 +258,19 @@ cudaError_t enqueue_pull(FlameOffloadPool& p, Slot& s, uint8_t* dst, cudaStream_
     POOL_TRY(s.ready.record(p.s_h2d), "pull: record(ready)");
   } else {
     POOL_TRY(s.consumer.make_wait(p.s_dequant), "pull: wait(consumer)");
-    for (size_t k = 0; k < nchunks; ++k) {
-      const uint64_t e0 = k * p.chunk_elems;
-      const uint64_t e = std::min<uint64_t>(p.chunk_elems, s.numel - e0);
+    for (size_t k0 = 0; k0 < nchunks; k0 += p.tile_chunks) {
+      const size_t kn = std::min<size_t>(p.tile_chunks, nchunks - k0);
+      const uint64_t e0 = k0 * p.chunk_elems;
+      const uint64_t e = std::min<uint64_t>(kn * p.chunk_elems, s.numel - e0);
       Tile& t = p.in_tiles[p.in_next++ % p.in_tiles.size()];
-      const size_t link = p.compression == FLAME_OFFLOAD_COMPRESSION_FP8 ? (size_t)e : packed_bytes(e);
       POOL_TRY(t.free_.make_wait(p.s_h2d), "pull: wait(tile free)");
-      POOL_TRY(memcpy_async_checked(t.dev, p.chunk_ptr(s.chunks[k]), link, cudaMemcpyHostToDevice, p.s_h2d), "pull: H2D");
+      for (size_t j = 0; j < kn; ++j) {
+        const uint64_t ec = std::min<uint64_t>(p.chunk_elems, e - j * p.chunk_elems);
+        const size_t link = p.stored_for(ec);
+        POOL_TRY(memcpy_async_checked(t.dev + j * p.host_chunk_bytes, p.chunk_ptr(s.chunks[k0 + j]), link,
+                                      cudaMemcpyHostToDevice, p.s_h2d), "pull: H2D");
+        p.stats.bytes_link_in += link;
+      }
       POOL_TRY(t.full.record(p.s_h2d), "pull: record(tile full)");
       POOL_TRY(t.full.make_wait(p.s_dequant), "pull: wait(tile full)");
       POOL_TRY(kernel_guard(), "pull: dequantise kernel");
@@ -266,11 +278,10 @@ cudaError_t enqueue_pull(FlameOffloadPool& p, Slot& s, uint8_t* dst, cudaStream_
       if (p.compression == FLAME_OFFLOAD_COMPRESSION_FP8)
         POOL_TRY(launch_fp8_to_bf16(t.dev, out, s.fp8_scale, e, p.s_dequant, p.codec_max_ctas), "pull: fp8_to_bf16");
       else
-        POOL_TRY(launch_dequant(p.compression, t.dev, t.dev + packed_scales_offset(e), out, e, p.s_dequant,
-                                p.codec_max_ctas), "pull: dequantise");
+        POOL_TRY(launch_dequant(p.compression, t.dev, out, e, packed_chunks_layout(e, p.chunk_elems, p.host_chunk_bytes),
+                                p.s_dequant, p.codec_max_ctas), "pull: dequantise");
       p.stats.codec_launches++;
       POOL_TRY(t.free_.record(p.s_dequant), "pull: record(tile free)");
-      p.stats.bytes_link_in += link;
     }
     POOL_TRY(s.h2d_done.record(p.s_h2d), "pull: record(h2d_done)");
     POOL_TRY(s.ready.record(p.s_dequant), "pull: record(ready)");
@@ -374,6 +385,8 @@ FlameOffloadPool* flame_offload_pool_create(size_t num_slots, size_t max_bytes, 
     p->chunk_elems = single ? (max_bytes + 1) / 2 : chunk / 2;
     p->host_chunk_bytes = p->stored_for(p->chunk_elems);
   }
+  p->tile_chunks = single ? 1 : std::max<uint32_t>(1, cfg.tile_chunks ? cfg.tile_chunks : kDefaultTileChunks);
+  p->tile_chunks = (uint32_t)std::min<size_t>(p->tile_chunks, chunks_per_slot);
   size_t total = num_slots * chunks_per_slot;
   if (cfg.host_budget_bytes) total = std::max<size_t>(1, cfg.host_budget_bytes / p->host_chunk_bytes);
   p->total_chunks = total;
@@ -420,7 +433,7 @@ FlameOffloadPool* flame_offload_pool_create(size_t num_slots, size_t max_bytes, 
       ring->resize(tiles);
       for (auto& t : *ring) {
         void* d = nullptr;
-        chk(cudaMalloc(&d, p->host_chunk_bytes), "cudaMalloc(staging tile)");
+        chk(cudaMalloc(&d, p->host_chunk_bytes * p->tile_chunks), "cudaMalloc(staging tile)");
         t.dev = static_cast<uint8_t*>(d);
         chk(t.full.create(), "cudaEventCreate"); chk(t.free_.create(), "cudaEventCreate");
       }

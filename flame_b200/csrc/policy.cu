@@ -78,9 +78,9 @@ FlameOffloadStatus flame_offload_probe(size_t bytes, int reps, FlameLinkProbe* o
   const size_t n = (bytes / 2) & ~(size_t)8191;
   auto* packed = static_cast<uint8_t*>(b.dev_b);
   const size_t so = (n + 255u) & ~(size_t)255u;
-  PROBE_TRY(timed([&] { return launch_compress(kCodecInt8, b.dev_a, packed, packed + so, n, 0, b.s, 0); }, ms));
+  PROBE_TRY(timed([&] { return launch_compress(kCodecInt8, b.dev_a, packed, n, single_chunk_layout(packed, packed + so, n), 0, b.s, 0); }, ms));
   out->quant_gbs = (3.03125 * n) / ms * 1e-6;
-  PROBE_TRY(timed([&] { return launch_dequant(kCodecInt8, packed, packed + so, b.dev_a, n, b.s, 0); }, ms));
+  PROBE_TRY(timed([&] { return launch_dequant(kCodecInt8, packed, b.dev_a, n, single_chunk_layout(packed, packed + so, n), b.s, 0); }, ms));
   out->dequant_gbs = (3.03125 * n) / ms * 1e-6;
 #undef PROBE_TRY
   return FLAME_OFFLOAD_OK;

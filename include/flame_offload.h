@@ -135,13 +135,13 @@ typedef struct {
   uint32_t struct_size;       /* sizeof(FlameOffloadPoolConfig); 0-filled fields take defaults */
   int32_t device;             /* CUDA ordinal; -1 = current device */
   uint64_t chunk_bytes;       /* pipeline chunk in source (BF16/F32) bytes; default 16 MiB; multiple of 64 KiB */
-  uint32_t staging_tiles;     /* device staging tiles per direction for the compressed modes; default 3 */
+  uint32_t staging_tiles;     /* device staging tiles per direction for the compressed modes; default 2 */
   uint32_t codec_flags;       /* FLAME_ACT_* flags passed to the block codecs */
   uint64_t host_budget_bytes; /* pinned bytes to hold; 0 = num_slots * stored size of max_bytes */
   uint32_t host_alloc_flags;  /* cudaHostAlloc flags; default 0 (never write-combined: the host reads it back) */
   int32_t codec_max_ctas;     /* thread blocks per codec launch; 0 = default */
   int32_t numa_node;          /* bind the slab to this NUMA node with mbind(); -1 = leave to first touch */
-  uint32_t reserved;
+  uint32_t tile_chunks;       /* chunks per staging tile = per codec kernel launch; default 8 */
 } FlameOffloadPoolConfig;
 
 typedef struct {

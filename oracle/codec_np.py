@@ -54,6 +54,16 @@ def fp8_decode(c) -> np.ndarray:
     return np.where((c >> 7) == 1, -mag, mag).astype(F32)
 
 
+def _fp8_code_of(x, inv) -> np.ndarray:
+    """enc(x*inv); a zero element stays zero when inv is infinite; a NaN result takes x's sign bit."""
+    x = np.asarray(x, F32)
+    with np.errstate(all="ignore"):
+        y = np.where(x == 0, x, (x * inv).astype(F32)).astype(F32)
+    c = fp8_encode_ref(np.where(np.isnan(y), F32(0), y))
+    nan_code = ((x.view(np.uint32) >> 24) & 0x80 | 0x7F).astype(np.uint8)
+    return np.where(np.isnan(y), nan_code, c).astype(np.uint8)
+
+
 def _blocks(x: np.ndarray) -> np.ndarray:
     n = x.size
     pad = (-n) % 128
@@ -95,8 +105,7 @@ def quant_fp8_b128(bits):
     scale = (amax / F32(448.0)).astype(F32)
     with np.errstate(all="ignore"):
         inv = (F32(1.0) / scale).astype(F32)
-        y = (xb * inv[:, None]).astype(F32)
-    c = fp8_encode_ref(y)
+    c = _fp8_code_of(xb, inv[:, None])
     c = np.where((amax == 0)[:, None], 0, c).astype(np.uint8)
     return c.reshape(-1)[:n], scale
 
@@ -109,8 +118,7 @@ def dequant_fp8_b128(codes, scales):
 
 
 def bf16_to_fp8(bits, inv_scale):
-    with np.errstate(all="ignore"):
-        return fp8_encode_ref(bf16_to_f32(bits) * F32(inv_scale))
+    return _fp8_code_of(bf16_to_f32(bits), F32(inv_scale))
 
 
 def fp8_to_bf16(codes, scale):

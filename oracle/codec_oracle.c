@@ -172,9 +172,18 @@ void oracle_fp8_encode_many(const float* y, uint8_t* out, size_t n, int form) {
 
 /* ---- element-wise fixed-scale entry points (legacy mode) ---------------- */
 
+/* code of x scaled by inv.  Two cases the reference leaves undefined are pinned
+ * here so that every platform gives the same byte: a zero element stays zero
+ * even when inv is infinite (0*inf would be NaN), and a NaN result takes the
+ * sign bit of the source element x. */
+static inline uint8_t fp8_code_of(float x, float inv, int ocp) {
+    float y = (x == 0.0f) ? x : x * inv;
+    if (y != y) return (uint8_t)(((f32_to_bits(x) >> 24) & 0x80u) | 0x7Fu);
+    return ocp ? oracle_fp8_e4m3_encode_ocp(y) : oracle_fp8_e4m3_encode_bits(y);
+}
+
 void oracle_bf16_to_fp8(const uint16_t* in, uint8_t* out, float inv_scale, size_t n) {
-    for (size_t i = 0; i < n; ++i)
-        out[i] = oracle_fp8_e4m3_encode_bits(oracle_bf16_to_f32(in[i]) * inv_scale);
+    for (size_t i = 0; i < n; ++i) out[i] = fp8_code_of(oracle_bf16_to_f32(in[i]), inv_scale, 0);
 }
 
 void oracle_fp8_to_bf16(const uint8_t* in, uint16_t* out, float scale, size_t n) {
@@ -230,11 +239,8 @@ void oracle_quant_fp8_b128(const uint16_t* in, uint8_t* codes, float* scales, si
         scales[blk] = scale;
         if (amax == 0.0f) { memset(codes + b0, 0, len); continue; }
         float inv = 1.0f / scale;
-        for (size_t i = 0; i < len; ++i) {
-            float y = oracle_bf16_to_f32(in[b0 + i]) * inv;
-            codes[b0 + i] = (flags & ORACLE_FLAG_FP8_OCP) ? oracle_fp8_e4m3_encode_ocp(y)
-                                                         : oracle_fp8_e4m3_encode_bits(y);
-        }
+        for (size_t i = 0; i < len; ++i)
+            codes[b0 + i] = fp8_code_of(oracle_bf16_to_f32(in[b0 + i]), inv, (flags & ORACLE_FLAG_FP8_OCP) != 0);
     }
 }
 

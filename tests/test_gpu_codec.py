@@ -1,0 +1,206 @@
+"""Parity of the CUDA codec kernels with the CPU oracle, through the C ABI.  Bit exact."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from flame_b200 import _lib, synthetic
+from oracle import capi
+from tests import gpu_util as G
+
+pytestmark = pytest.mark.gpu
+
+SIZES = [1, 7, 8, 9, 127, 128, 129, 1000, 8191, 8192, 8193, 3 * 8192 + 77, (1 << 20) + 13]
+
+
+def _check_int8(x_bits, dev, flags=0, **offs):
+    x = G.to_dev(x_bits, dev, offs.pop("in_offset", 0))
+    codes, scales = G.quant("int8", x, flags, **offs)
+    want_c, want_s = capi.quant_int8_b128(x_bits, flags)
+    assert np.array_equal(codes.cpu().numpy().view(np.int8), want_c)
+    assert np.array_equal(scales.cpu().numpy().view(np.uint32), want_s.view(np.uint32))
+    out = G.dequant("int8", codes, scales, x.numel())
+    assert np.array_equal(G.bits_of(out), capi.dequant_int8_b128(want_c, want_s))
+    return codes, scales, out
+
+
+def _check_fp8(x_bits, dev, flags=0, **offs):
+    x = G.to_dev(x_bits, dev, offs.pop("in_offset", 0))
+    codes, scales = G.quant("fp8", x, flags, **offs)
+    want_c, want_s = capi.quant_fp8_b128(x_bits, flags)
+    assert np.array_equal(codes.cpu().numpy(), want_c)
+    assert np.array_equal(scales.cpu().numpy().view(np.uint32), want_s.view(np.uint32))
+    out = G.dequant("fp8", codes, scales, x.numel())
+    assert np.array_equal(G.bits_of(out), capi.dequant_fp8_b128(want_c, want_s))
+    return codes, scales, out
+
+
+@pytest.mark.parametrize("n", SIZES)
+def test_int8_sizes(cuda_device, n):
+    _check_int8(synthetic.normal_with_outliers(n, seed=n), cuda_device)
+
+
+@pytest.mark.parametrize("n", SIZES)
+def test_fp8_sizes(cuda_device, n):
+    _check_fp8(synthetic.normal_with_outliers(n, seed=n + 1), cuda_device)
+
+
+def test_empty_input_is_a_no_op(cuda_device):
+    lib = _lib.lib()
+    assert lib.flame_act_quant_int8_b128(None, None, None, 0, 0, None) == 0
+    assert lib.flame_act_dequant_fp8_b128(None, None, None, 0, None) == 0
+    assert lib.flame_act_quant_fp8_b128(None, None, None, 5, 0, None) == 1  # cudaErrorInvalidValue
+
+
+@pytest.mark.parametrize("n", [129, 8192 + 9, 50001])
+def test_unaligned_pointers_take_the_generic_kernels(cuda_device, n):
+    bits = synthetic.normal(n, seed=7)
+    _check_int8(bits, cuda_device, in_offset=1, code_offset=3, scale_offset=1)
+    _check_fp8(bits, cuda_device, in_offset=3, code_offset=1, scale_offset=3)
+    # dequantise into an odd destination
+    x = G.to_dev(bits, cuda_device)
+    codes, scales = G.quant("int8", x, code_offset=5)
+    out = G.dequant("int8", codes, scales, n, out_offset=1)
+    wc, ws = capi.quant_int8_b128(bits)
+    assert np.array_equal(G.bits_of(out), capi.dequant_int8_b128(wc, ws))
+
+
+def test_every_finite_bf16_value(cuda_device):
+    """All 65,280 finite BF16 patterns, in blocks that mix magnitudes and in blocks of similar magnitude."""
+    vals = synthetic.edge_values()
+    rng = np.random.default_rng(0)
+    for bits in (vals, rng.permutation(vals), np.sort(vals.view(np.int16)).view(np.uint16)):
+        _check_int8(bits, cuda_device)
+        _check_int8(bits, cuda_device, flags=1)  # MUL_INV form
+        _check_fp8(bits, cuda_device)
+
+
+def test_scale_edge_blocks(cuda_device):
+    """Zero blocks, -0.0, one-hot blocks, sub-normal magnitudes, huge magnitudes, all-ones scale significands."""
+    x = np.zeros(128 * 12, np.uint16)
+    x[128 + 5] = 0x8000                                     # block 1: only a -0.0
+    x[256 + 17] = 0x3F80                                    # block 2: one-hot 1.0
+    x[384:512] = 0x0001                                     # block 3: smallest BF16 sub-normal
+    x[512:640] = np.arange(128, dtype=np.uint16) + 0x0001   # block 4: sub-normal ramp
+    x[640:768] = 0x7F7F                                     # block 5: BF16 max
+    x[768:896] = (np.arange(128) % 2 * 0x8000 + 0x7F00).astype(np.uint16)  # block 6: huge, mixed sign
+    x[896:1024] = synthetic.normal(128, 1)
+    x[896] = 0x42FE                                         # 127.0 -> scale 1.0 exactly
+    x[1024:1152] = synthetic.normal(128, 2)
+    x[1152:1280] = (synthetic.normal(128, 3) & 0x807F) | 0x0080  # tiny normals
+    _check_int8(x, cuda_device)
+    _check_int8(x, cuda_device, flags=1)
+    _check_fp8(x, cuda_device)
+
+
+def test_nan_elements_do_not_poison_a_block(cuda_device):
+    x = synthetic.normal(512, 4)
+    x[3] = 0x7FC0
+    x[200] = 0xFFC1
+    _check_int8(x, cuda_device)
+    _check_fp8(x, cuda_device)
+
+
+def test_ocp_encoder_flag(cuda_device):
+    bits = synthetic.student_t3_times2(100000 + 3, 5)
+    _check_fp8(bits, cuda_device, flags=1)
+    _check_fp8(synthetic.edge_values(), cuda_device, flags=1)
+
+
+def test_block_codec_goldens(cuda_device, golden_dir):
+    from tests.golden.make_golden import BLOCK_CASES
+
+    g = np.load(os.path.join(golden_dir, "block_codec_cases.npz"))
+    for name, (gen, n, seed) in BLOCK_CASES.items():
+        bits = getattr(synthetic, gen)(n, seed)
+        codes, scales, out = _check_int8(bits, cuda_device)
+        assert np.array_equal(codes.cpu().numpy().view(np.int8), g[f"{name}.int8_codes"])
+        assert np.array_equal(G.bits_of(out), g[f"{name}.int8_out"])
+        codes, scales, out = _check_fp8(bits, cuda_device)
+        assert np.array_equal(codes.cpu().numpy(), g[f"{name}.fp8_codes"])
+        assert np.array_equal(scales.cpu().numpy(), g[f"{name}.fp8_scales"])
+        assert np.array_equal(G.bits_of(out), g[f"{name}.fp8_out"])
+
+
+def test_config1_full_tensor_int8(cuda_device):
+    """[1,4096,3072] BF16, N(0,1) with 0.1 % +-U(20,60) outliers, seed 0: codes, scales and values bit exact;
+    every dequantised value within absmax/127 of its source."""
+    bits = synthetic.normal_with_outliers(4096 * 3072, 0)
+    codes, scales, out = _check_int8(bits, cuda_device)
+    xf = G.to_dev(bits, cuda_device).float()
+    err = (out.float() - xf).abs().view(-1, 128).amax(dim=1)
+    assert bool((err <= scales).all())
+
+
+def test_config3_mixed_activations_fp8(cuda_device):
+    """GELU outputs, 2*t(3) attention outputs and a SwiGLU hidden state [1,4608,9216]."""
+    _check_fp8(synthetic.gelu_of_normal(4608 * 3072, 0), cuda_device)
+    _check_fp8(synthetic.student_t3_times2(4608 * 3072, 0), cuda_device)
+    _check_fp8(synthetic.swiglu_hidden(4608 * 9216, 0), cuda_device)
+    _check_int8(synthetic.student_t3_times2(4608 * 3072, 1), cuda_device)
+
+
+# ---- element-wise FP8 with a caller-supplied scale (the reference's two entry points) --------
+
+@pytest.mark.parametrize("n", [1, 5, 8, 1000, 65536 + 3])
+@pytest.mark.parametrize("offset", [0, 1])
+def test_flame_bf16_to_fp8_and_back(cuda_device, n, offset):
+    lib = _lib.lib()
+    bits = synthetic.normal_with_outliers(n, seed=n)
+    x = G.to_dev(bits, cuda_device, offset)
+    scale = np.float32(8.0) / np.float32(448.0)      # the reference pool's fixed scale
+    inv = np.float32(1.0) / scale
+    codes = torch.empty(n + offset, dtype=torch.uint8, device=cuda_device)[offset:]
+    assert lib.flame_bf16_to_fp8(x.data_ptr(), codes.data_ptr(), float(inv), n, G.stream_ptr(cuda_device)) == 0
+    out = torch.empty(n + offset, dtype=torch.bfloat16, device=cuda_device)[offset:]
+    assert lib.flame_fp8_to_bf16(codes.data_ptr(), out.data_ptr(), float(scale), n, G.stream_ptr(cuda_device)) == 0
+    torch.cuda.synchronize()
+    want = capi.bf16_to_fp8(bits, inv)
+    assert np.array_equal(codes.cpu().numpy(), want)
+    assert np.array_equal(G.bits_of(out), capi.fp8_to_bf16(want, scale))
+
+
+def test_elementwise_encoder_against_reference_golden(cuda_device, golden_dir):
+    """The codes the reference's own encoder gave for every finite BF16 value (committed fixture)."""
+    lib = _lib.lib()
+    g = np.load(os.path.join(golden_dir, "fp8_reference_encoder.npz"))
+    bits = synthetic.edge_values()
+    x = G.to_dev(bits, cuda_device)
+    for k, inv in enumerate(g["inv_scales"]):
+        codes = torch.empty(bits.size, dtype=torch.uint8, device=cuda_device)
+        assert lib.flame_bf16_to_fp8(x.data_ptr(), codes.data_ptr(), float(inv), bits.size, None) == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(codes.cpu().numpy(), g[f"codes_{k}"])
+    dec = np.load(os.path.join(golden_dir, "fp8_reference_decoder.npy"))
+    all_codes = torch.arange(256, dtype=torch.int16, device=cuda_device).to(torch.uint8)
+    out = torch.empty(256, dtype=torch.bfloat16, device=cuda_device)
+    assert lib.flame_fp8_to_bf16(all_codes.data_ptr(), out.data_ptr(), 1.0, 256, None) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(out.float().cpu().numpy().view(np.uint32), dec.view(np.uint32))  # every decoded value is a BF16
+
+
+# ---- size-independent properties at benchmark sizes -------------------------------------------
+
+def test_large_tensor_properties(cuda_device):
+    """512 MiB of BF16: round trip within one step per block, max |code| == 127 in every non-zero block,
+    and chunk invariance: quantising two halves separately gives the same codes as one launch."""
+    n = 1 << 28
+    g = torch.Generator(device=cuda_device).manual_seed(0)
+    x = torch.randn(n, device=cuda_device, dtype=torch.float32, generator=g).to(torch.bfloat16)
+    codes, scales = G.quant("int8", x)
+    out = G.dequant("int8", codes, scales, n)
+    blk_err = (out.float() - x.float()).abs().view(-1, 128).amax(dim=1)
+    assert bool((blk_err <= scales).all())
+    assert bool((codes.view(torch.int8).abs().view(-1, 128).amax(dim=1) == 127).all())
+    half = n // 2
+    c0, s0 = G.quant("int8", x[:half])
+    c1, s1 = G.quant("int8", x[half:])
+    assert torch.equal(codes[:half], c0) and torch.equal(codes[half:], c1)
+    assert torch.equal(scales[: half // 128], s0) and torch.equal(scales[half // 128:], s1)
+    # spot check against the oracle on a slice that straddles tile boundaries
+    lo, hi = 8192 * 1000 - 300, 8192 * 1000 + 128 * 200
+    lo -= lo % 128
+    want_c, want_s = capi.quant_int8_b128(G.bits_of(x[lo:hi]))
+    assert np.array_equal(codes[lo:hi].cpu().numpy().view(np.int8), want_c)
+    assert np.array_equal(scales[lo // 128: hi // 128].cpu().numpy(), want_s)
