@@ -1,0 +1,405 @@
+"""Benchmark of the activation offload+restore path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--codec int8|fp8|none] [--impl reference]
+
+One *step* is one pass of the hot path over the saved activations of one DiT
+training step (20 blocks x {2 norm outputs, QKV, attention output, SwiGLU
+gate+up} at 4608 tokens, hidden 3072; 6.79 GB of BF16): every tensor is
+offloaded in forward order, then every tensor is restored in reverse order.
+
+Reported, for the whole job (all N replicas):
+
+* ``value``  BF16-equivalent GB/s (bytes offloaded + bytes restored, per second)
+  of the device-resident part: compress into packed device buffers and
+  dequantise back, inputs and outputs in HBM, no host link.
+* ``e2e``    the same metric through ``ActivationOffloadPool.push`` /
+  ``pull_into``: compress, D2H into the pinned slab, H2D, dequantise into the
+  destination tensor.  The host<->device copies are inside the timed region.
+* ``roofline``  achieved algorithmic GB/s of the compress kernel (3.03125 B per
+  element) against the measured HBM copy rate; ``roofline_dequant`` likewise.
+* ``link``   achieved D2H / H2D GB/s against the PCIe Gen5 x16 bound (63.0 GB/s).
+* ``cpu_baseline``  the CPU oracle's quantise+pack / unpack+dequantise on this
+  box's host cores over a bounded sample (rank 0, N=1 only).
+* ``overhead``  (N=1, unless --no-dit) step time of a 20-block DiT training step
+  with activations offloaded / recomputed, relative to keeping them resident.
+
+``--impl reference`` times the reference's CPU arm instead: the reference crate
+is GPU-only Rust and has no CPU quantise/pack path of its own, so the timed code
+is the C oracle (a port), on all host threads, over a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "activation offload+restore GB/s per GPU (BF16-equiv), whole job"
+UNIT = "GB/s"
+ALG_BYTES_PER_ELEM = 3.03125  # 2 B read + 1 B code + 4/128 B scale (and the mirror image for dequantise)
+PCIE_GEN5_X16_GBS = 63.0      # 32 GT/s x 16 lanes x 128/130 / 8
+TOKENS, HIDDEN, BLOCKS = 4608, 3072, 20
+# saved set of one block, as last dims: norm1 out, QKV, attention out, norm2 out, SwiGLU gate+up
+BLOCK_SAVED = (HIDDEN, 3 * HIDDEN, HIDDEN, HIDDEN, 6 * HIDDEN)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        sm = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": int(self.rows[0][1]) if self.rows[0][1].isdigit() else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+def make_workload(torch, dev, seed: int, blocks: int = BLOCKS):
+    """The saved activations of one step: N(0,1) with 0.1 % of entries replaced by +-U(20,60), BF16."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    tensors = []
+    for _ in range(blocks):
+        for last in BLOCK_SAVED:
+            x = torch.randn(1, TOKENS, last, device=dev, dtype=torch.float32, generator=g)
+            mask = torch.rand(x.shape, device=dev, generator=g) < 1e-3
+            mag = torch.empty_like(x).uniform_(20.0, 60.0, generator=g) * torch.where(torch.rand(x.shape, device=dev, generator=g) < 0.5, -1.0, 1.0)
+            tensors.append(torch.where(mask, mag, x).to(torch.bfloat16).contiguous())
+            del x, mask, mag
+    return tensors
+
+
+def verify_against_oracle(torch, lib, x, codec: str) -> bool:
+    """One tensor through the C ABI, compared bit for bit with the CPU oracle (the checker, not the product)."""
+    import numpy as np
+    from oracle import capi
+
+    n = min(x.numel(), 1 << 22)
+    xs = x.reshape(-1)[:n].contiguous()
+    codes = torch.empty(n, dtype=torch.uint8, device=x.device)
+    scales = torch.empty((n + 127) // 128, dtype=torch.float32, device=x.device)
+    out = torch.empty(n, dtype=torch.bfloat16, device=x.device)
+    s = torch.cuda.current_stream().cuda_stream
+    q, d = (lib.flame_act_quant_int8_b128, lib.flame_act_dequant_int8_b128) if codec == "int8" else \
+           (lib.flame_act_quant_fp8_b128, lib.flame_act_dequant_fp8_b128)
+    assert q(xs.data_ptr(), codes.data_ptr(), scales.data_ptr(), n, 0, s) == 0
+    assert d(codes.data_ptr(), scales.data_ptr(), out.data_ptr(), n, s) == 0
+    torch.cuda.synchronize()
+    bits = xs.view(torch.int16).cpu().numpy().view(np.uint16)
+    wc, ws = (capi.quant_int8_b128 if codec == "int8" else capi.quant_fp8_b128)(bits)
+    wo = (capi.dequant_int8_b128 if codec == "int8" else capi.dequant_fp8_b128)(wc, ws)
+    return (np.array_equal(codes.cpu().numpy(), wc.view(np.uint8)) and np.array_equal(scales.cpu().numpy().view(np.uint32), ws.view(np.uint32))
+            and np.array_equal(out.view(torch.int16).cpu().numpy().view(np.uint16), wo))
+
+
+def cpu_leg(seconds_target: float = 12.0, codec_name: str = "int8"):
+    """CPU oracle pack+unpack on all host threads over a bounded sample of the workload. Returns (GB/s bf16-equiv, cores, sample)."""
+    import numpy as np
+    from flame_b200 import synthetic
+    from oracle import capi
+
+    codec = {"int8": capi.CODEC_INT8, "fp8": capi.CODEC_FP8, "none": capi.CODEC_NONE}[codec_name]
+    cores = os.cpu_count() or 1
+    n = TOKENS * HIDDEN  # one [1,4608,3072] norm output
+    x = synthetic.normal_with_outliers(n, seed=0)
+    capi.roundtrip_mt(x, codec, cores)  # warm-up, page in
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        capi.roundtrip_mt(x, codec, cores)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds_target or reps >= 400:
+            break
+    gbs = (2 * 2 * n * reps) / dt * 1e-9  # bytes offloaded + bytes restored
+    return gbs, cores, f"{reps} x one [1,{TOKENS},{HIDDEN}] BF16 tensor ({2 * n / 1e6:.1f} MB), quantise+pack then unpack+dequantise, {cores} threads, {dt:.1f} s", dt / reps
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps_rates, cores, sample, step_s = [], 0, "", []
+    per = max(2.0, min(20.0, 150.0 / max(1, args.steps + args.warmup)))
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        gbs, cores, sample, _ = cpu_leg(per, args.codec)
+        if i >= args.warmup:
+            steps_rates.append(gbs)
+            step_s.append(time.perf_counter() - t0)
+    value = sum(steps_rates) / len(steps_rates)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(sum(step_s) / len(step_s) * 1e3, 1), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 codes + f32 scales" if args.codec == "int8" else args.codec, "data": "synthetic",
+        "config": workload_config(args, 1),
+        "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": cores, "kind": "port", "sample": "each step: " + sample},
+        "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference crate is GPU-only Rust with no CPU quantise/pack path; this arm times the C oracle (a port of its formulas) on the host cores",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, world):
+    return {"workload": f"DiT saved activations: {BLOCKS} blocks x [norm1 3072, QKV 9216, attn 3072, norm2 3072, gate+up 18432] x {TOKENS} tokens, BF16, "
+                        f"{BLOCKS * sum(BLOCK_SAVED) * TOKENS * 2 / 1e9:.2f} GB per step per GPU; offload all in forward order, restore all in reverse",
+            "codec": args.codec + ("-b128" if args.codec != "none" else ""), "chunk_bytes": args.chunk_mb << 20, "tile_chunks": args.tile_chunks,
+            "l2": "inputs larger than L2 (6.79 GB of distinct tensors per step)", "replicas": world, "parallelism": f"dp{world} independent replicas, no collective"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--codec", choices=["int8", "fp8", "none"], default="int8")
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--chunk-mb", type=int, default=16)
+    ap.add_argument("--tile-chunks", type=int, default=8)
+    ap.add_argument("--blocks", type=int, default=BLOCKS, help="fewer blocks = smaller case (profiling only)")
+    ap.add_argument("--no-dit", action="store_true", help="skip the DiT training-step overhead measurement")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--only", choices=["all", "value", "e2e"], default="all", help="profiling: run only one timed region")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from flame_b200 import ActivationOffloadPool, OffloadCompression, _lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.lib()  # raises if the CUDA library is missing: there is no fallback
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    tensors = make_workload(torch, dev, seed=rank, blocks=args.blocks)
+    step_bytes = sum(t.numel() * 2 for t in tensors)
+    step_elems = sum(t.numel() for t in tensors)
+    max_bytes = max(t.numel() * 2 for t in tensors)
+    mode = {"int8": OffloadCompression.INT8_B128, "fp8": OffloadCompression.FP8_B128, "none": OffloadCompression.NONE}[args.codec]
+    stream = torch.cuda.current_stream()
+    sp = stream.cuda_stream
+    verified = verify_against_oracle(torch, lib, tensors[1], args.codec) if args.codec != "none" else True
+
+    # ---- device-resident leg: compress + dequantise, HBM in, HBM out ---------------------------------
+    value_ms = quant_ms = dequant_ms = None
+    launches = 0
+    dst = [torch.empty_like(t) for t in tensors]
+    if args.only in ("all", "value"):
+        if args.codec == "none":
+            def offload_all():
+                for t, d in zip(tensors, packed):
+                    lib.flame_d2d_async(d.data_ptr(), t.data_ptr(), t.numel() * 2, sp)
+
+            def restore_all():
+                for d, p in zip(reversed(dst), reversed(packed)):
+                    lib.flame_d2d_async(d.data_ptr(), p.data_ptr(), d.numel() * 2, sp)
+            packed = [torch.empty(t.numel() * 2, dtype=torch.uint8, device=dev) for t in tensors]
+            per_step_launches = 0
+        else:
+            q, dq = (lib.flame_act_quant_int8_b128, lib.flame_act_dequant_int8_b128) if args.codec == "int8" else \
+                    (lib.flame_act_quant_fp8_b128, lib.flame_act_dequant_fp8_b128)
+            packed = [torch.empty(lib.flame_act_packed_bytes(t.numel()), dtype=torch.uint8, device=dev) for t in tensors]
+            so = [lib.flame_act_packed_scales_offset(t.numel()) for t in tensors]
+
+            def offload_all():
+                for t, p, o in zip(tensors, packed, so):
+                    rc = q(t.data_ptr(), p.data_ptr(), p.data_ptr() + o, t.numel(), 0, sp)
+                    assert rc == 0, rc
+
+            def restore_all():
+                for d, p, o in zip(reversed(dst), reversed(packed), reversed(so)):
+                    rc = dq(p.data_ptr(), p.data_ptr() + o, d.data_ptr(), d.numel(), sp)
+                    assert rc == 0, rc
+            per_step_launches = 2 * len(tensors)
+
+        for _ in range(max(args.warmup, 1)):
+            offload_all(); restore_all()
+        barrier()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3 * args.steps + 1)]
+        with ClockSampler(local) as clk_value:
+            ev[0].record(stream)
+            for k in range(args.steps):
+                offload_all(); ev[3 * k + 1].record(stream)
+                restore_all(); ev[3 * k + 2].record(stream)
+                ev[3 * k + 3].record(stream)
+            barrier()
+        quant_ms = sum(ev[3 * k].elapsed_time(ev[3 * k + 1]) for k in range(args.steps)) / args.steps
+        dequant_ms = sum(ev[3 * k + 1].elapsed_time(ev[3 * k + 2]) for k in range(args.steps)) / args.steps
+        value_ms = max_over_ranks(ev[0].elapsed_time(ev[-1]) / args.steps)
+        launches += per_step_launches * args.steps
+        del packed
+
+    # ---- end-to-end leg: the pool, through pinned host memory --------------------------------------------
+    e2e = link = None
+    e2e_ms = None
+    if args.only in ("all", "e2e"):
+        pool = ActivationOffloadPool(dev, len(tensors), max_bytes, mode, chunk_bytes=args.chunk_mb << 20,
+                                     tile_chunks=args.tile_chunks,
+                                     host_budget_bytes=ActivationOffloadPool.host_bytes_needed(
+                                         [t.numel() * 2 for t in tensors], mode, args.chunk_mb << 20))
+
+        def e2e_step():
+            handles = [pool.push(t) for t in tensors]
+            for h, d in zip(reversed(handles), reversed(dst)):
+                pool.pull_into(h, d)
+
+        for _ in range(max(args.warmup, 1)):
+            e2e_step()
+        barrier()
+        st0 = pool.stats()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clk_e2e:
+            wall0 = time.perf_counter()
+            e0.record(stream)
+            for _ in range(args.steps):
+                e2e_step()
+            e1.record(stream)
+            barrier()
+            wall = (time.perf_counter() - wall0) / args.steps
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+        st1 = pool.stats()
+        d2h_b = (st1["bytes_link_out"] - st0["bytes_link_out"]) // args.steps
+        h2d_b = (st1["bytes_link_in"] - st0["bytes_link_in"]) // args.steps
+        launches += st1["codec_launches"] - st0["codec_launches"]
+        # restored values must equal the device-resident result (same kernels) and, for none, the source
+        if args.codec == "none":
+            assert all(torch.equal(a.view(torch.int16), b.view(torch.int16)) for a, b in zip(tensors[:3], dst[:3])), "BF16 round trip not bit exact"
+
+        # per-direction link rate, measured apart from the headline: all offloads, wait, then all restores
+        barrier()
+        w0 = time.perf_counter()
+        handles = [pool.push(t) for t in tensors]
+        pool.synchronize(120.0)          # bounded wait for the pool's own streams
+        d2h_s = time.perf_counter() - w0
+        a1, a2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a1.record(stream)
+        for h, d in zip(reversed(handles), reversed(dst)):
+            pool.pull_into(h, d)          # the compute stream waits for each restore
+        a2.record(stream)
+        torch.cuda.synchronize()
+        link = {"bound_gbs": PCIE_GEN5_X16_GBS, "d2h_gbs": round(d2h_b / d2h_s * 1e-9, 2),
+                "h2d_gbs": round(h2d_b / (a1.elapsed_time(a2) * 1e-3) * 1e-9, 2)}
+        link["d2h_frac_of_bound"] = round(link["d2h_gbs"] / PCIE_GEN5_X16_GBS, 3)
+        link["h2d_frac_of_bound"] = round(link["h2d_gbs"] / PCIE_GEN5_X16_GBS, 3)
+        pool.clear()
+        e2e_value = world * 2 * step_bytes / (e2e_ms * 1e-3) * 1e-9
+        e2e = {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": int(h2d_b), "d2h_bytes_per_step": int(d2h_b),
+               "ms_per_step": round(e2e_ms, 3), "wall_ms_per_step": round(wall * 1e3, 3), "pinned_bytes": pool.host_bytes(),
+               "api": "ActivationOffloadPool.push / pull_into over flame_offload_pool_push / _pull_into"}
+        pool.close()
+
+    hbm_peak, peak_kind = measured_peaks()
+    line = {
+        "metric": METRIC, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": {"int8": "int8 codes + f32 scales", "fp8": "fp8-e4m3 codes + f32 scales", "none": "bf16"}[args.codec],
+        "data": "synthetic", "config": workload_config(args, world), "verified_against_oracle": bool(verified),
+        "gpu_launches": int(launches),
+    }
+    if value_ms is not None:
+        line["value"] = round(world * 2 * step_bytes / (value_ms * 1e-3) * 1e-9, 1)
+        line["ms_per_step"] = round(value_ms, 4)
+        if args.codec != "none":
+            alg = ALG_BYTES_PER_ELEM * step_elems
+            qa, da = alg / (quant_ms * 1e-3) * 1e-9, alg / (dequant_ms * 1e-3) * 1e-9
+            n_l = len(tensors)
+            line["roofline"] = {"bound": "hbm", "kernel": "compress_b128_kernel", "achieved": round(qa, 1), "peak": hbm_peak, "unit": "GB/s",
+                                "frac": round(qa / hbm_peak, 4), "peak_kind": f"of {peak_kind}", "traffic": None,
+                                "alg_bytes_per_launch": int(alg / n_l), "avg_launch_us": round(quant_ms * 1e3 / n_l, 2), "launches_per_step": n_l}
+            line["roofline_dequant"] = {"bound": "hbm", "kernel": "dequant_b128_kernel", "achieved": round(da, 1), "peak": hbm_peak, "unit": "GB/s",
+                                        "frac": round(da / hbm_peak, 4), "peak_kind": f"of {peak_kind}", "traffic": None,
+                                        "alg_bytes_per_launch": int(alg / n_l), "avg_launch_us": round(dequant_ms * 1e3 / n_l, 2)}
+        line["clocks"] = clk_value.summary()
+    else:
+        line["value"] = e2e["value"]
+        line["ms_per_step"] = e2e["ms_per_step"]
+    if e2e is not None:
+        line["e2e"] = e2e
+        line["link"] = link
+        line["clocks_e2e"] = clk_e2e.summary()
+        if "clocks" not in line:
+            line["clocks"] = line["clocks_e2e"]
+
+    if rank == 0 and world == 1 and not args.no_cpu:
+        gbs, cores, sample, _ = cpu_leg(12.0, args.codec)
+        line["cpu_baseline"] = {"value": round(gbs, 3), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+    if rank == 0 and world == 1 and not args.no_dit and args.only == "all":
+        try:
+            from flame_b200.dit_workload import measure_overhead
+            del tensors, dst
+            torch.cuda.empty_cache()
+            line["overhead"] = measure_overhead(dev, steps=max(3, min(args.steps, 5)), warmup=3)
+        except Exception as exc:  # the headline numbers above stand on their own
+            line["overhead"] = {"error": f"{type(exc).__name__}: {exc}"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -89,6 +89,21 @@ class ActivationOffloadPool:
         self._meta: dict[int, tuple] = {}        # slot -> (shape, dtype)
         self._keep_alive: dict[int, tuple] = {}  # slot -> (handle, tensor)
 
+    @staticmethod
+    def host_bytes_needed(tensor_bytes, compression: OffloadCompression, chunk_bytes: int = 0) -> int:
+        """Pinned bytes that hold all of `tensor_bytes` (BF16 byte sizes) at once: a value for `host_budget_bytes`.
+
+        Every tensor occupies whole chunks, so the last chunk of each is partly empty.
+        """
+        chunk = chunk_bytes or (16 << 20)
+        if compression == OffloadCompression.NONE:
+            per_chunk = chunk
+        elif compression == OffloadCompression.FP8:
+            per_chunk = chunk // 2
+        else:
+            per_chunk = _lib.lib().flame_act_packed_bytes(chunk // 2)
+        return sum(-(-int(b) // chunk) for b in tensor_bytes) * per_chunk
+
     # -- accessors (src/activation_offload.rs:429-455) ---------------------------------
     def num_slots(self) -> int:
         return self._lib.flame_offload_pool_num_slots(self._h)

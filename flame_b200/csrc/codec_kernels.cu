@@ -45,6 +45,8 @@ constexpr int kUnroll = 2;                                   // loads in flight 
 constexpr int kTileElems = kThreads * kLaneElems * kUnroll;  // 8192
 constexpr int kTileBlocks = kTileElems / 128;                // 64 scales per tile
 constexpr int kLanesPerBlock = 128 / kLaneElems;             // 8
+constexpr int kDequantUnroll = 4;                            // 16-byte code loads in flight per thread
+constexpr int kDequantTileElems = kThreads * kLaneElems * kDequantUnroll;  // 16384
 
 struct U32x8 { uint32_t v[8]; };
 
@@ -313,16 +315,56 @@ __device__ __forceinline__ OutAddr locate(const uint8_t* base, const PackedLayou
 // memory tiles and bulk stores; the last, partial tile uses predicated loads and
 // direct stores.
 template <int kCodec, bool kFlag>
-__global__ void __launch_bounds__(kThreads)
-compress_b128_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ out, size_t n, PackedLayout L) {
-  __shared__ __align__(128) uint8_t s_codes[2][kTileElems];
-  __shared__ __align__(128) float s_scales[2][kTileBlocks];
+__device__ __forceinline__ void compress_tail(const uint16_t* __restrict__ in, uint8_t* __restrict__ out, size_t n,
+                                              const PackedLayout& L, size_t full_tiles, int tid);
 
+// kStaged = true : codes and scales of a tile are collected in shared memory and
+//                  leave as two bulk asynchronous copies issued by one thread.
+// kStaged = false: every lane stores its 16 codes with one 16-byte store and one
+//                  lane in eight stores the scale; no shared memory, no barrier.
+template <int kCodec, bool kFlag, bool kStaged>
+__global__ void __launch_bounds__(kThreads)
+compress_b128_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ out, size_t n, PackedLayout L,
+                     unsigned tiles_per_cta) {
   const int tid = threadIdx.x;
   const size_t full_tiles = n / kTileElems;
+  // Round k of every thread block works on the window [k*grid, (k+1)*grid) of tiles;
+  // the host sizes the grid so that all blocks run the same number of rounds
+  // (see grid_balanced) and all are resident at once.
+
+  if (!kStaged) {
+    for (unsigned k = 0; k < tiles_per_cta; ++k) {
+      const size_t tile = (size_t)k * gridDim.x + blockIdx.x;
+      if (tile >= full_tiles) break;
+      const uint16_t* tin = in + tile * kTileElems;
+      U32x8 raw[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) raw[u] = ld_stream32(tin + (size_t)(u * kThreads + tid) * kLaneElems);
+      const OutAddr o = locate(out, L, tile * kTileElems);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        float x[kLaneElems];
+        unpack16(raw[u], x);
+        const float amax = absmax_8lanes(absmax_n<kLaneElems>(x));
+        float scale;
+        uint32_t c[kLaneElems / 4];
+        encode_block_part<kCodec, kFlag, kLaneElems>(x, raw[u].v, amax, scale, c);
+        const int v = u * kThreads + tid;
+        __stcs(reinterpret_cast<uint4*>(o.codes + v * kLaneElems), make_uint4(c[0], c[1], c[2], c[3]));
+        if ((tid & (kLanesPerBlock - 1)) == 0) o.scales[v / kLanesPerBlock] = scale;
+      }
+    }
+    compress_tail<kCodec, kFlag>(in, out, n, L, full_tiles, tid);
+    return;
+  }
+
+  __shared__ __align__(128) uint8_t s_codes[2][kTileElems];
+  __shared__ __align__(128) float s_scales[2][kTileBlocks];
   int buf = 0;
 
-  for (size_t tile = blockIdx.x; tile < full_tiles; tile += gridDim.x) {
+  for (unsigned k = 0; k < tiles_per_cta; ++k) {
+    const size_t tile = (size_t)k * gridDim.x + blockIdx.x;
+    if (tile >= full_tiles) break;
     const uint16_t* tin = in + tile * kTileElems;
     U32x8 raw[kUnroll];
 #pragma unroll
@@ -355,9 +397,17 @@ compress_b128_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ out,
     buf ^= 1;
   }
 
-  // Ragged tail: owned by the block that would have taken tile `full_tiles`.
+  compress_tail<kCodec, kFlag>(in, out, n, L, full_tiles, tid);
+  if (tid == 0) bulk_wait_all<0>();
+}
+
+// Ragged tail (n not a multiple of 8192): handled by the last thread block with
+// predicated loads and direct stores.
+template <int kCodec, bool kFlag>
+__device__ __forceinline__ void compress_tail(const uint16_t* __restrict__ in, uint8_t* __restrict__ out, size_t n,
+                                              const PackedLayout& L, size_t full_tiles, int tid) {
   const size_t tail0 = full_tiles * kTileElems;
-  if (tail0 < n && (full_tiles % gridDim.x) == blockIdx.x) {
+  if (tail0 < n && blockIdx.x == gridDim.x - 1) {
     const uint16_t* tin = in + tail0;
     const size_t rem = n - tail0;
     const OutAddr o = locate(out, L, tail0);
@@ -392,8 +442,8 @@ compress_b128_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ out,
     }
   }
 
-  if (tid == 0) bulk_wait_all<0>();
 }
+
 
 // Any alignment, any n: one warp per 128-element block, scalar accesses.
 template <int kCodec, bool kFlag>
@@ -474,12 +524,15 @@ __device__ __forceinline__ uint16_t decode1(uint8_t c, float scale) {
 // the 8 lanes of a block read the same scale, which the L1 serves.
 template <int kCodec>
 __global__ void __launch_bounds__(kThreads)
-dequant_b128_kernel(const uint8_t* __restrict__ in, uint16_t* __restrict__ out, size_t n, PackedLayout L) {
-  constexpr int kDU = 4;  // 16-byte loads in flight per thread
+dequant_b128_kernel(const uint8_t* __restrict__ in, uint16_t* __restrict__ out, size_t n, PackedLayout L,
+                    unsigned tiles_per_cta) {
+  constexpr int kDU = kDequantUnroll;  // 16-byte loads in flight per thread
   const int tid = threadIdx.x;
   const size_t nvec = n / kLaneElems;  // whole 16-element vectors
   const size_t tiles = (nvec + kThreads * kDU - 1) / (kThreads * kDU);
-  for (size_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+  for (unsigned k = 0; k < tiles_per_cta; ++k) {
+    const size_t tile = (size_t)k * gridDim.x + blockIdx.x;
+    if (tile >= tiles) break;
     const size_t v0 = tile * (kThreads * kDU);
     const OutAddr A = locate(in, L, v0 * kLaneElems);  // a tile never straddles chunks
     uint4 c[kDU];
@@ -508,7 +561,7 @@ dequant_b128_kernel(const uint8_t* __restrict__ in, uint16_t* __restrict__ out, 
   }
   // up to 15 trailing elements
   const size_t t0 = nvec * kLaneElems;
-  if (blockIdx.x == 0 && tid < (int)(n - t0)) {
+  if (blockIdx.x == gridDim.x - 1 && tid < (int)(n - t0)) {
     const size_t e = t0 + tid;
     const OutAddr a = locate(in, L, e & ~(size_t)127);
     out[e] = decode1<kCodec>(a.codes[e & 127], a.scales[0]);
@@ -625,13 +678,37 @@ int grid_for(size_t work_items, int ctas_per_sm, int max_ctas) {
   return (int)g;
 }
 
+// Resident thread blocks per SM of a kernel (queried once per kernel).
+template <typename K>
+int resident_ctas_per_sm(K kernel) {
+  static int cached = 0;
+  if (cached == 0) {
+    int v = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, kernel, kThreads, 0) != cudaSuccess || v <= 0) v = 4;
+    cached = v;
+  }
+  return cached;
+}
+
+// A grid in which every thread block takes the same number of consecutive tiles
+// and all blocks are resident at once: no second wave, no ragged last round.
+struct Grid { int ctas; unsigned tiles_per_cta; };
+Grid grid_balanced(size_t tiles, int ctas_per_sm, int max_ctas) {
+  if (tiles == 0) tiles = 1;
+  size_t cap = (size_t)sm_count() * (size_t)ctas_per_sm;
+  const int lim = max_ctas > 0 ? max_ctas : g_max_ctas;
+  if (lim > 0 && cap > (size_t)lim) cap = (size_t)lim;
+  const size_t per = (tiles + cap - 1) / cap;
+  return {(int)((tiles + per - 1) / per), (unsigned)per};
+}
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 inline bool aligned(int64_t v, int64_t a) { return (v & (a - 1)) == 0; }
 
 bool layout_fast(const void* base, const PackedLayout& L, size_t n) {
   if (!aligned(base, 16) || !aligned(L.scales_off, 16) || !aligned(L.scales_off_last, 16)) return false;
   if (L.chunk_elems >= n) return true;
-  return (L.chunk_elems % (2 * kTileElems)) == 0 && aligned(L.chunk_stride, 16);  // 16384: the dequantise tile
+  return (L.chunk_elems % kDequantTileElems) == 0 && aligned(L.chunk_stride, 16);  // 16384 covers both tile sizes
 }
 
 }  // namespace
@@ -666,15 +743,22 @@ cudaError_t launch_compress(int codec, const void* in, void* out, size_t n, cons
   auto* i = static_cast<const uint16_t*>(in);
   auto* o = static_cast<uint8_t*>(out);
   if (aligned(in, 32) && layout_fast(out, L, n)) {
-    const size_t tiles = (n + kTileElems - 1) / kTileElems;
-    const int grid = grid_for(tiles, 6, max_ctas);
+    const size_t tiles = (n + kTileElems - 1) / kTileElems;  // the ragged tail rides with the last block
+    const bool staged = (flags & kFlagStagedStores) != 0;
+#define FLAME_LAUNCH_COMPRESS(C, F, S)                                                          \
+    do {                                                                                          \
+      auto kern = compress_b128_kernel<C, F, S>;                                                  \
+      const Grid g = grid_balanced(tiles, resident_ctas_per_sm(kern), max_ctas);                  \
+      kern<<<g.ctas, kThreads, 0, stream>>>(i, o, n, L, g.tiles_per_cta);                         \
+    } while (0)
     if (codec == kCodecInt8) {
-      if (flag) compress_b128_kernel<kCodecInt8, true><<<grid, kThreads, 0, stream>>>(i, o, n, L);
-      else compress_b128_kernel<kCodecInt8, false><<<grid, kThreads, 0, stream>>>(i, o, n, L);
+      if (flag) { if (staged) FLAME_LAUNCH_COMPRESS(kCodecInt8, true, true); else FLAME_LAUNCH_COMPRESS(kCodecInt8, true, false); }
+      else { if (staged) FLAME_LAUNCH_COMPRESS(kCodecInt8, false, true); else FLAME_LAUNCH_COMPRESS(kCodecInt8, false, false); }
     } else {
-      if (flag) compress_b128_kernel<kCodecFp8, true><<<grid, kThreads, 0, stream>>>(i, o, n, L);
-      else compress_b128_kernel<kCodecFp8, false><<<grid, kThreads, 0, stream>>>(i, o, n, L);
+      if (flag) { if (staged) FLAME_LAUNCH_COMPRESS(kCodecFp8, true, true); else FLAME_LAUNCH_COMPRESS(kCodecFp8, true, false); }
+      else { if (staged) FLAME_LAUNCH_COMPRESS(kCodecFp8, false, true); else FLAME_LAUNCH_COMPRESS(kCodecFp8, false, false); }
     }
+#undef FLAME_LAUNCH_COMPRESS
   } else {
     const size_t warps = (n + 127) / 128;
     const int grid = grid_for((warps + 7) / 8, 8, max_ctas);
@@ -696,10 +780,16 @@ cudaError_t launch_dequant(int codec, const void* in, void* out, size_t n, const
   auto* c = static_cast<const uint8_t*>(in);
   auto* o = static_cast<uint16_t*>(out);
   if (aligned(out, 32) && layout_fast(in, L, n)) {
-    const size_t tiles = (n / kLaneElems + kThreads * 4 - 1) / (kThreads * 4);
-    const int grid = grid_for(tiles ? tiles : 1, 8, max_ctas);
-    if (codec == kCodecInt8) dequant_b128_kernel<kCodecInt8><<<grid, kThreads, 0, stream>>>(c, o, n, L);
-    else dequant_b128_kernel<kCodecFp8><<<grid, kThreads, 0, stream>>>(c, o, n, L);
+    const size_t tiles = (n + kDequantTileElems - 1) / kDequantTileElems;
+    if (codec == kCodecInt8) {
+      auto kern = dequant_b128_kernel<kCodecInt8>;
+      const Grid g = grid_balanced(tiles, resident_ctas_per_sm(kern), max_ctas);
+      kern<<<g.ctas, kThreads, 0, stream>>>(c, o, n, L, g.tiles_per_cta);
+    } else {
+      auto kern = dequant_b128_kernel<kCodecFp8>;
+      const Grid g = grid_balanced(tiles, resident_ctas_per_sm(kern), max_ctas);
+      kern<<<g.ctas, kThreads, 0, stream>>>(c, o, n, L, g.tiles_per_cta);
+    }
   } else {
     const int grid = grid_for((n + kThreads - 1) / kThreads, 8, max_ctas);
     if (codec == kCodecInt8) dequant_b128_generic_kernel<kCodecInt8><<<grid, kThreads, 0, stream>>>(c, o, n, L);

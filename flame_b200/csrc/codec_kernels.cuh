@@ -10,6 +10,10 @@ namespace flame_b200 {
 constexpr int kCodecInt8 = 2;
 constexpr int kCodecFp8 = 3;
 
+// Bits of `flags` for launch_compress.  Bit 0 is the public codec flag
+// (FLAME_ACT_INT8_MUL_INV / FLAME_ACT_FP8_OCP); bit 1 picks the store path.
+constexpr unsigned kFlagStagedStores = 2u;
+
 // Addressing of compressed data as a run of self-contained chunks: chunk c holds
 // elements [c*chunk_elems, (c+1)*chunk_elems) and starts at base + c*chunk_stride
 // with its codes; its fp32 scales start scales_off bytes into the chunk

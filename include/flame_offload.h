@@ -83,12 +83,14 @@ int flame_fp8_to_bf16(const void* input_u8, void* output_bf16, float scale, size
  *            src/cuda/fp8_quant.cu:19-57; absmax == 0 gives scale 0, codes 0.
  *    Dequantise: out = bf16_rne(float(code) * scale) / bf16_rne(dec(code) * scale).
  *    Returns 0 or a cudaError_t value; cudaErrorInvalidValue (1) for NULL
- *    pointers with n > 0.  Any pointer alignment is accepted (16-byte aligned
- *    pointers take the fast kernels).
+ *    pointers with n > 0.  Any pointer alignment is accepted (32-byte aligned
+ *    BF16 buffers and 16-byte aligned code/scale buffers take the fast kernels).
  * ---------------------------------------------------------------------- */
 #define FLAME_ACT_BLOCK 128
 #define FLAME_ACT_INT8_MUL_INV 1u /* int8: code = rne(x * (1/scale)) instead of the division */
 #define FLAME_ACT_FP8_OCP 1u      /* fp8: OCP round-to-nearest-even, saturating encoder (not the reference's) */
+#define FLAME_ACT_STAGED_STORES 2u /* compress: collect each tile's codes and scales in shared memory and write them
+                                      with bulk asynchronous copies instead of per-lane stores; same results */
 
 int flame_act_quant_int8_b128(const void* in_bf16, void* codes_i8, void* scales_f32, size_t n, unsigned int flags, void* stream);
 int flame_act_dequant_int8_b128(const void* codes_i8, const void* scales_f32, void* out_bf16, size_t n, void* stream);

@@ -17,7 +17,7 @@ SIZES = [1, 7, 8, 9, 127, 128, 129, 1000, 8191, 8192, 8193, 3 * 8192 + 77, (1 <<
 def _check_int8(x_bits, dev, flags=0, **offs):
     x = G.to_dev(x_bits, dev, offs.pop("in_offset", 0))
     codes, scales = G.quant("int8", x, flags, **offs)
-    want_c, want_s = capi.quant_int8_b128(x_bits, flags)
+    want_c, want_s = capi.quant_int8_b128(x_bits, flags & 1)
     assert np.array_equal(codes.cpu().numpy().view(np.int8), want_c)
     assert np.array_equal(scales.cpu().numpy().view(np.uint32), want_s.view(np.uint32))
     out = G.dequant("int8", codes, scales, x.numel())
@@ -28,7 +28,7 @@ def _check_int8(x_bits, dev, flags=0, **offs):
 def _check_fp8(x_bits, dev, flags=0, **offs):
     x = G.to_dev(x_bits, dev, offs.pop("in_offset", 0))
     codes, scales = G.quant("fp8", x, flags, **offs)
-    want_c, want_s = capi.quant_fp8_b128(x_bits, flags)
+    want_c, want_s = capi.quant_fp8_b128(x_bits, flags & 1)
     assert np.array_equal(codes.cpu().numpy(), want_c)
     assert np.array_equal(scales.cpu().numpy().view(np.uint32), want_s.view(np.uint32))
     out = G.dequant("fp8", codes, scales, x.numel())
@@ -44,6 +44,16 @@ def test_int8_sizes(cuda_device, n):
 @pytest.mark.parametrize("n", SIZES)
 def test_fp8_sizes(cuda_device, n):
     _check_fp8(synthetic.normal_with_outliers(n, seed=n + 1), cuda_device)
+
+
+@pytest.mark.parametrize("n", [8192, 8193, 5 * 8192 + 4000, (1 << 22) + 8192 * 3 + 9])
+def test_staged_store_path_gives_the_same_bytes(cuda_device, n):
+    """FLAME_ACT_STAGED_STORES: shared-memory tiles drained by bulk asynchronous copies."""
+    bits = synthetic.normal_with_outliers(n, seed=n + 2)
+    _check_int8(bits, cuda_device, flags=2)
+    _check_int8(bits, cuda_device, flags=3)
+    _check_fp8(bits, cuda_device, flags=2)
+    _check_fp8(bits, cuda_device, flags=3)
 
 
 def test_empty_input_is_a_no_op(cuda_device):
