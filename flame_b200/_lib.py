@@ -76,6 +76,7 @@ SIGNATURES = {
     "flame_act_packed_scales_offset": (_sz, [_sz]),
     "flame_act_packed_bytes": (_sz, [_sz]),
     "flame_act_set_max_ctas": (_i, [_i]),
+    "flame_act_offload_packed_noalloc": (_i, [_vp, _vp, _sz, _i, _u, _vp]),
     "flame_offload_pool_create": (_vp, [_sz, _sz, _i, C.POINTER(PoolConfig)]),
     "flame_offload_pool_destroy": (None, [_vp]),
     "flame_offload_pool_num_slots": (_sz, [_vp]),

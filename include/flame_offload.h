@@ -102,6 +102,34 @@ int flame_act_dequant_fp8_b128(const void* codes_u8, const void* scales_f32, voi
 size_t flame_act_packed_scales_offset(size_t n);
 size_t flame_act_packed_bytes(size_t n);
 
+/* Compress `n` BF16 elements on the device and deliver the packed result
+ * (layout above, flame_act_packed_bytes(n) bytes) to `packed_out`, which may be
+ * pinned host memory or device memory, WITHOUT allocating anything: no
+ * cudaMalloc, cudaFree or other allocating call is made.  (No counterpart in the
+ * reference, whose pool allocates its staging buffers up front,
+ * src/activation_offload.rs:401-407.)
+ *
+ * For callers that cannot allocate at the moment they need to spill: an
+ * out-of-memory handler freeing device memory by moving an activation out, or
+ * a step loop with a fixed memory plan in which cudaMalloc/cudaFree would stall
+ * the device or fail.  The device staging it needs is a fixed array inside the
+ * library: every GPU that loads the library holds about 8.3 MiB of it until the
+ * process exits.
+ *
+ *   - n may be at most FLAME_ACT_NOALLOC_MAX_ELEMS; larger tensors are refused
+ *     with cudaErrorInvalidValue (1) and a message in flame_offload_last_error().
+ *   - codec is FLAME_OFFLOAD_COMPRESSION_INT8_B128 or _FP8_B128; flags as for
+ *     the quantise entry points.  Results are identical to those entry points.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call before starting any stream
+ *     capture on that device.
+ *   - All calls share the one array.  Calls on the same stream are ordered;
+ *     calls whose GPU work can overlap (different streams) race on it and must
+ *     be ordered by the caller.  The result is complete when `stream` reaches
+ *     the end of the call's work. */
+#define FLAME_ACT_NOALLOC_MAX_ELEMS ((size_t)8 << 20)
+int flame_act_offload_packed_noalloc(const void* in_bf16, void* packed_out, size_t n, int codec, unsigned int flags, void* stream);
+
 /* Limits the number of thread blocks the codec kernels launch on the current
  * device (0 = default: a multiple of the SM count).  Returns the old value. */
 int flame_act_set_max_ctas(int max_ctas);
