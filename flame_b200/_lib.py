@@ -26,7 +26,7 @@ class PoolConfig(C.Structure):
         ("struct_size", C.c_uint32), ("device", C.c_int32), ("chunk_bytes", C.c_uint64),
         ("staging_tiles", C.c_uint32), ("codec_flags", C.c_uint32), ("host_budget_bytes", C.c_uint64),
         ("host_alloc_flags", C.c_uint32), ("codec_max_ctas", C.c_int32), ("numa_node", C.c_int32),
-        ("tile_chunks", C.c_uint32),
+        ("tile_chunks", C.c_uint32), ("d2h_piece_bytes", C.c_uint64), ("h2d_piece_bytes", C.c_uint64),
     ]
 
 
@@ -52,6 +52,14 @@ class PolicyTensor(C.Structure):
 class PolicyInput(C.Structure):
     _fields_ = [("d2h_gbs", C.c_double), ("h2d_gbs", C.c_double), ("fwd_ms", C.c_double), ("bwd_ms", C.c_double),
                 ("device_budget_bytes", C.c_uint64), ("lossy_codec", C.c_int32), ("link_utilisation", C.c_double)]
+
+
+class PolicyBlock(C.Structure):
+    _fields_ = [("saved_bytes", C.c_uint64), ("fwd_ms", C.c_double), ("bwd_ms", C.c_double)]
+
+
+class PolicyBlockPlan(C.Structure):
+    _fields_ = [("est_stall_ms", C.c_double), ("est_recompute_ms", C.c_double), ("resident_bytes", C.c_uint64), ("link_bytes", C.c_uint64)]
 
 
 _vp, _sz, _i, _u, _f, _d = C.c_void_p, C.c_size_t, C.c_int, C.c_uint, C.c_float, C.c_double
@@ -88,6 +96,7 @@ SIGNATURES = {
     "flame_offload_pool_pull_into": (_i, [_vp, Handle, _vp, _sz, _vp, _u]),
     "flame_offload_pool_wait_ready": (_i, [_vp, _sz, _vp]),
     "flame_offload_pool_clear": (_i, [_vp]),
+    "flame_offload_pool_discard": (_i, [_vp, Handle]),
     "flame_offload_pool_source_released": (_i, [_vp, Handle]),
     "flame_offload_pool_slot_info": (_i, [_vp, Handle, C.POINTER(SlotInfo)]),
     "flame_offload_pool_synchronize": (_i, [_vp, _d]),
@@ -100,6 +109,7 @@ SIGNATURES = {
     "flame_pinned_pool_checkin": (_i, [_vp, _vp, _sz]),
     "flame_pinned_pool_stats": (None, [_vp, C.POINTER(_sz), C.POINTER(_sz)]),
     "flame_offload_probe": (_i, [_sz, _i, C.POINTER(LinkProbe)]),
+    "flame_offload_policy_plan_blocks": (_i, [C.POINTER(PolicyInput), C.POINTER(PolicyBlock), _sz, _i, C.POINTER(C.c_int32), C.POINTER(PolicyBlockPlan)]),
     "flame_offload_policy_plan": (_i, [C.POINTER(PolicyInput), C.POINTER(PolicyTensor), _sz, C.POINTER(C.c_int32), C.POINTER(_d)]),
 }
 

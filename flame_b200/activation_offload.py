@@ -66,7 +66,7 @@ class ActivationOffloadPool:
                  compression: OffloadCompression = OffloadCompression.NONE, *,
                  chunk_bytes: int = 0, staging_tiles: int = 0, codec_flags: int = 0,
                  host_budget_bytes: int = 0, host_alloc_flags: int = 0, codec_max_ctas: int = 0,
-                 numa_node: int = -2, tile_chunks: int = 0):
+                 numa_node: int = -2, tile_chunks: int = 0, d2h_piece_bytes: int = 0, h2d_piece_bytes: int = 0):
         import torch
 
         self._torch = torch
@@ -76,7 +76,8 @@ class ActivationOffloadPool:
         index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self.device = torch.device("cuda", index)
         cfg = _lib.PoolConfig(C.sizeof(_lib.PoolConfig), index, chunk_bytes, staging_tiles, codec_flags,
-                              host_budget_bytes, host_alloc_flags, codec_max_ctas, numa_node, tile_chunks)
+                              host_budget_bytes, host_alloc_flags, codec_max_ctas, numa_node, tile_chunks,
+                              d2h_piece_bytes, h2d_piece_bytes)
         self._lib = _lib.lib()
         with torch.cuda.device(index):
             self._h = self._lib.flame_offload_pool_create(num_slots, max_bytes, int(compression), C.byref(cfg))
@@ -122,11 +123,17 @@ class ActivationOffloadPool:
         return self._torch.cuda.current_stream(self.device).cuda_stream
 
     def _sweep_keep_alive(self) -> None:
-        """Drops source tensors whose device-to-host copy has completed."""
-        for slot in list(self._keep_alive):
-            handle, _ = self._keep_alive[slot]
-            if self._lib.flame_offload_pool_source_released(self._h, handle._c()) != 0:
-                del self._keep_alive[slot]
+        """Drops source tensors whose device-to-host copy has completed.
+
+        Offloads complete in the order they were pushed (one D2H stream), so the sweep walks from the
+        oldest entry and stops at the first one that is still being read.
+        """
+        ka = self._keep_alive
+        while ka:
+            slot = next(iter(ka))
+            if self._lib.flame_offload_pool_source_released(self._h, ka[slot][0]) == 0:
+                break
+            del ka[slot]
 
     def push(self, tensor) -> OffloadHandle:
         """Asynchronously offload `tensor`; never blocks the host (activation_offload.rs:465-611)."""
@@ -139,10 +146,12 @@ class ActivationOffloadPool:
         h = _lib.Handle()
         st = self._lib.flame_offload_pool_push(self._h, tensor.data_ptr() if tensor.numel() else None,
                                               tensor.numel(), tag, self._stream(), C.byref(h))
-        raise_for_status(st, _lib.last_error())
+        if st != 0:
+            raise_for_status(st, _lib.last_error())
         handle = OffloadHandle(h.slot, h.epoch)
         self._meta[h.slot] = (tuple(tensor.shape), tensor.dtype)
-        self._keep_alive[h.slot] = (handle, tensor.detach())
+        self._keep_alive.pop(h.slot, None)          # re-inserted at the young end
+        self._keep_alive[h.slot] = (h, tensor.detach())
         return handle
 
     def pull_into(self, handle: OffloadHandle, dst, defer_wait: bool = False) -> None:
@@ -151,7 +160,8 @@ class ActivationOffloadPool:
             raise InvalidInput("ActivationOffloadPool::pull_into: destination must be a contiguous tensor on the pool's device")
         st = self._lib.flame_offload_pool_pull_into(self._h, handle._c(), dst.data_ptr(), dst.numel() * dst.element_size(),
                                                    self._stream(), 1 if defer_wait else 0)
-        raise_for_status(st, _lib.last_error())
+        if st != 0:
+            raise_for_status(st, _lib.last_error())
         if not defer_wait:
             self._keep_alive.pop(handle.slot, None)
         self._meta.pop(handle.slot, None)
@@ -165,9 +175,18 @@ class ActivationOffloadPool:
         self.pull_into(handle, out)
         return out
 
+    def discard(self, handle: OffloadHandle) -> None:
+        """Frees the slot of `handle` without restoring it (an abandoned block, src/autograd.rs:1742-1769)."""
+        raise_for_status(self._lib.flame_offload_pool_discard(self._h, handle._c()), _lib.last_error())
+        self._meta.pop(handle.slot, None)
+        # the source stays referenced until its device-to-host copy, already queued, has finished
+        self._sweep_keep_alive()
+
     def wait_ready(self, slot: int) -> None:
         """Makes the current stream wait for the latest restore issued from `slot`."""
-        raise_for_status(self._lib.flame_offload_pool_wait_ready(self._h, slot, self._stream()), _lib.last_error())
+        st = self._lib.flame_offload_pool_wait_ready(self._h, slot, self._stream())
+        if st != 0:
+            raise_for_status(st, _lib.last_error())
         self._keep_alive.pop(slot, None)
 
     def clear(self) -> None:

@@ -1,0 +1,282 @@
+"""Save / restore hooks: ``checkpoint`` and ``checkpoint_offload``.
+
+Mirror of the hooks in the reference's tape engine:
+
+* ``set_activation_offload_pool``      <- src/autograd.rs:63-74 (global pool, set once)
+* ``checkpoint(inputs, f)``            <- src/autograd.rs:1584-1647 + the ``Op::Checkpoint`` arm, 2271-2435
+  (forward without a tape, recompute in backward)
+* ``checkpoint_offload(inputs, f)``    <- src/autograd.rs:1659-1798 + the ``Op::CheckpointOffload`` arm, 2437-2510
+  (forward once with the tape on, every saved BF16 activation pushed to the pool,
+  pulled back in reverse during backward; no pool -> ``checkpoint``; pool full
+  mid-block -> handles given back and the block falls back to ``checkpoint``)
+
+The tape here is PyTorch's: ``torch.autograd.graph.saved_tensors_hooks`` sees
+every tensor an op saves for backward, which is what the reference walks in
+``sub_tape[*].saved_tensors``.  Because a Python closure cannot be re-run on
+detached inputs the way the Rust closure is re-run on tensor ids, ``f`` takes the
+inputs as arguments: ``f(*inputs)``.
+
+One thing is added on top of the reference's just-in-time pulls (its restore sits
+on the critical path, src/autograd.rs:2470-2479): blocks register in forward
+order, and when backward first touches block k the restores of block k-1 are
+issued into freshly allocated destinations (``pull_into`` with a deferred wait),
+so the host link works one block ahead of the VJPs.
+"""
+from __future__ import annotations
+
+import logging
+import weakref
+from typing import Callable, Optional, Sequence
+
+import torch
+from torch.utils.checkpoint import checkpoint as _torch_checkpoint
+
+from .activation_offload import ActivationOffloadPool
+from .errors import InvalidInput, InvalidOperation, OffloadError
+from .policy import Decision
+
+log = logging.getLogger("flame_b200.checkpoint")
+
+_ACTIVATION_POOL: Optional[ActivationOffloadPool] = None
+
+
+def set_activation_offload_pool(pool: ActivationOffloadPool) -> None:
+    """Install the pool ``checkpoint_offload`` uses.  Once; a second call is an error (autograd.rs:70-74)."""
+    global _ACTIVATION_POOL
+    if _ACTIVATION_POOL is not None:
+        raise InvalidOperation("Activation offload pool already set")
+    _ACTIVATION_POOL = pool
+
+
+def clear_activation_offload_pool() -> None:
+    """Uninstall the pool (the reference's OnceLock cannot be reset; tests and benchmarks need to)."""
+    global _ACTIVATION_POOL
+    _ACTIVATION_POOL = None
+    _SCHEDULER.reset()
+
+
+def activation_offload_pool() -> Optional[ActivationOffloadPool]:
+    return _ACTIVATION_POOL
+
+
+def checkpoint(inputs: Sequence[torch.Tensor], f: Callable[..., torch.Tensor]) -> torch.Tensor:
+    """Recompute arm: run ``f(*inputs)`` without saving activations, re-run it in backward."""
+    if not inputs:
+        raise InvalidInput("checkpoint requires at least one input")
+    if not torch.is_grad_enabled():
+        return f(*inputs)
+    return _torch_checkpoint(f, *inputs, use_reentrant=False)
+
+
+def dense_permutation(t: torch.Tensor):
+    """Permutation p with ``t.permute(p)`` contiguous, or None.
+
+    A saved tensor is often a transposed view of dense memory (attention inputs in [B,H,T,D]
+    order over [B,T,H,D] storage).  The pool moves flat contiguous memory, so such a view is
+    offloaded through its contiguous permutation and re-viewed after the restore.
+    """
+    if t.is_contiguous():
+        return tuple(range(t.dim()))
+    perm = tuple(sorted(range(t.dim()), key=lambda d: (-t.stride(d), d)))
+    return perm if t.permute(perm).is_contiguous() else None
+
+
+def offloadable(t: torch.Tensor, min_bytes: int) -> bool:
+    """The rule of src/autograd.rs:1721-1725 (BF16 activations that require grad), plus: on the GPU,
+    not a parameter, not tiny, and backed by dense memory."""
+    if isinstance(t, torch.nn.Parameter) or isinstance(getattr(t, "_base", None), torch.nn.Parameter):
+        return False  # weights and views of weights (a linear saves weight.t()) are not activations
+    return (t.is_cuda and t.dtype == torch.bfloat16 and t.requires_grad
+            and t.numel() * 2 >= min_bytes and dense_permutation(t) is not None)
+
+
+def saved_bytes_of(f: Callable[..., torch.Tensor], inputs: Sequence[torch.Tensor], min_bytes: int = 1 << 20) -> int:
+    """BF16 bytes ``checkpoint_offload(inputs, f)`` would push: a dry run of ``f`` with counting hooks."""
+    seen, total = set(), 0
+
+    def pack(t):
+        nonlocal total
+        if offloadable(t, min_bytes):
+            key = (t.data_ptr(), t.numel(), t._version)
+            if key not in seen:
+                seen.add(key)
+                total += t.numel() * 2
+        return t
+
+    with torch.enable_grad(), torch.autograd.graph.saved_tensors_hooks(pack, lambda t: t):
+        f(*inputs)
+    return total
+
+
+class _Entry:
+    """One offloaded saved tensor (OffloadedTapeEntry's handle plus what restore needs)."""
+
+    __slots__ = ("handle", "shape", "dtype", "restored", "waited", "block", "__weakref__")
+
+    def __init__(self, handle, shape, dtype, block):
+        self.handle, self.shape, self.dtype, self.block = handle, shape, dtype, block
+        self.restored = None
+        self.waited = False
+
+
+class _View:
+    """A saved tensor that is a reshaped and/or permuted view of an offloaded entry's flat memory."""
+
+    __slots__ = ("entry", "shape", "inverse")
+
+    def __init__(self, entry, shape, inverse):
+        self.entry, self.shape, self.inverse = entry, shape, inverse
+
+
+class _Block:
+    """The offloaded sub-tape of one ``checkpoint_offload`` call."""
+
+    def __init__(self, pool: ActivationOffloadPool, index: int, min_bytes: int):
+        self.pool, self.index, self.min_bytes = pool, index, min_bytes
+        # weak: an entry, and the restored tensor it caches, must die as soon as the last
+        # graph node that saved it has run its backward
+        self.entries: list = []
+        self._by_key: dict = {}
+        self._handles: list = []
+        self.failed = False
+        self.bytes_offloaded = 0
+        self.restores_issued = False
+
+    # -- forward -----------------------------------------------------------------------------
+    def pack(self, t: torch.Tensor):
+        # Only BF16 activations that take part in the gradient are offloaded; weights, non-BF16
+        # tensors and small tensors stay resident (autograd.rs:1721-1739).
+        if self.failed or not offloadable(t, self.min_bytes):
+            return t
+        perm = dense_permutation(t)
+        inverse = tuple(perm.index(d) for d in range(t.dim()))
+        base = t.permute(perm)  # contiguous view of the same memory
+        # the same memory is often saved several times under different shapes (a norm output
+        # and its 2-D view in the following linear): one offload, many views
+        key = (t.data_ptr(), t.numel(), t._version)
+        e = self._by_key.get(key)
+        if e is not None:
+            return _View(e, tuple(base.shape), inverse)
+        try:
+            h = self.pool.push(base)
+        except OffloadError as exc:  # pool exhausted: abandon offload for this block
+            log.warning("checkpoint_offload: pool push failed (%s), falling back to recompute; %d handles already pushed",
+                        exc, len(self.entries))
+            self.failed = True
+            return t
+        e = _Entry(h, (t.numel(),), t.dtype, self)
+        self.entries.append(weakref.ref(e))
+        self._by_key[key] = e
+        self._handles.append(h)
+        self.bytes_offloaded += t.numel() * 2
+        return _View(e, tuple(base.shape), inverse)
+
+    def finish_forward(self) -> None:
+        self._by_key.clear()
+
+    def abandon(self) -> None:
+        handles, self._handles = self._handles, []
+        for h in handles:
+            try:
+                self.pool.discard(h)
+            except OffloadError:
+                pass
+        self.entries.clear()
+
+    # -- backward ------------------------------------------------------------------------------
+    def issue_restores(self) -> None:
+        """Start the restore of every entry that has not been started yet (deferred wait)."""
+        self.restores_issued = True
+        for ref in reversed(self.entries):
+            e = ref()
+            if e is not None and e.restored is None:
+                dst = torch.empty(e.shape, dtype=e.dtype, device=self.pool.device)
+                self.pool.pull_into(e.handle, dst, defer_wait=True)
+                e.restored = dst
+
+    def unpack(self, obj):
+        if isinstance(obj, _View):
+            return self.unpack(obj.entry).view(obj.shape).permute(obj.inverse)
+        if not isinstance(obj, _Entry):
+            return obj
+        if not self.restores_issued:   # the output-gradient hook normally got here first
+            _SCHEDULER.on_backward_reach(self.index)
+            if not self.restores_issued:
+                self.issue_restores()
+        if obj.restored is None:  # pushed after the block's restores were issued: cannot happen, but stay correct
+            dst = torch.empty(obj.shape, dtype=obj.dtype, device=self.pool.device)
+            self.pool.pull_into(obj.handle, dst, defer_wait=True)
+            obj.restored = dst
+        if not obj.waited:
+            self.pool.wait_ready(obj.handle.slot)
+            obj.waited = True
+        return obj.restored
+
+
+class _Scheduler:
+    """Keeps the checkpointed blocks of the current step in forward order and, as backward walks them in
+    reverse, issues the restores of the offloaded blocks a few positions ahead of the VJPs."""
+
+    def __init__(self):
+        self.blocks: list = []      # per checkpoint_offload call of the step: weakref to its _Block, or None (resident / recompute)
+        self.prefetch_blocks = 2
+        self._backward_seen = False
+
+    def reset(self):
+        self.blocks.clear()
+        self._backward_seen = False
+
+    def register(self, block: Optional[_Block]) -> int:
+        if self._backward_seen:     # first forward call after a backward: a new step begins
+            self.reset()
+        self.blocks.append(weakref.ref(block) if block is not None else None)
+        return len(self.blocks) - 1
+
+    def on_backward_reach(self, position: int) -> None:
+        """Backward is about to run the block registered at `position`."""
+        self._backward_seen = True
+        for j in range(min(position, len(self.blocks) - 1), max(-1, position - 1 - self.prefetch_blocks), -1):
+            ref = self.blocks[j]
+            blk = ref() if ref is not None else None
+            if blk is not None and not blk.restores_issued:
+                blk.issue_restores()
+
+
+_SCHEDULER = _Scheduler()
+
+
+def set_prefetch_blocks(n: int) -> None:
+    """How many block positions ahead of the VJPs restores are issued (0 = just in time, as the reference)."""
+    _SCHEDULER.prefetch_blocks = max(0, int(n))
+
+
+def checkpoint_offload(inputs: Sequence[torch.Tensor], f: Callable[..., torch.Tensor], *,
+                       decision: Decision = Decision.OFFLOAD_INT8, min_bytes: int = 1 << 20) -> torch.Tensor:
+    """Offload arm.  ``decision`` comes from the policy: RESIDENT runs ``f`` plainly, RECOMPUTE uses ``checkpoint``,
+    any OFFLOAD_* value pushes the block's saved activations to the installed pool (whose own compression applies)."""
+    if not inputs:
+        raise InvalidInput("checkpoint_offload requires at least one input")
+    pool = _ACTIVATION_POOL
+    if pool is None or decision == Decision.RECOMPUTE:
+        return checkpoint(inputs, f)
+    if not torch.is_grad_enabled():
+        return f(*inputs)
+    if decision == Decision.RESIDENT:
+        out = f(*inputs)
+        if out.requires_grad:  # a resident block still tells the scheduler where backward is
+            pos = _SCHEDULER.register(None)
+            out.register_hook(lambda g, pos=pos: _SCHEDULER.on_backward_reach(pos))
+        return out
+    block = _Block(pool, len(_SCHEDULER.blocks), min_bytes)
+    with torch.autograd.graph.saved_tensors_hooks(block.pack, block.unpack):
+        out = f(*inputs)
+    block.finish_forward()
+    if block.failed:
+        log.warning("checkpoint_offload: falling back to recompute checkpoint (pool exhausted after %d tensors)", len(block.entries))
+        block.abandon()
+        del out
+        return checkpoint(inputs, f)
+    block.index = _SCHEDULER.register(block)  # the autograd graph keeps the block alive through the unpack hook
+    if out.requires_grad:
+        out.register_hook(lambda g, pos=block.index: _SCHEDULER.on_backward_reach(pos))
+    return out

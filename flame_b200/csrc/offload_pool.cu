@@ -122,6 +122,7 @@ struct FlameOffloadPool {
   uint64_t chunk_elems = 0;       // BF16 elements per chunk (compressed modes)
   uint64_t host_chunk_bytes = 0;  // pinned bytes per chunk
   uint32_t tile_chunks = 1;       // chunks per device staging tile = per codec launch
+  uint64_t d2h_piece = 0, h2d_piece = 0;  // copies are issued in pieces of this size (0 = whole chunk)
   uint32_t codec_flags = 0;
   int codec_max_ctas = 0;
 
@@ -183,6 +184,17 @@ namespace {
     if (_e != cudaSuccess) { fail_cuda(_e, what); return _e; } \
   } while (0)
 
+// One chunk's copy, optionally cut into pieces so that the copy engine leaves gaps on the link.
+cudaError_t copy_in_pieces(void* dst, const void* src, size_t bytes, cudaMemcpyKind kind, cudaStream_t st, uint64_t piece) {
+  if (piece == 0 || piece >= bytes) return memcpy_async_checked(dst, src, bytes, kind, st);
+  for (size_t off = 0; off < bytes; off += piece) {
+    cudaError_t e = memcpy_async_checked(static_cast<uint8_t*>(dst) + off, static_cast<const uint8_t*>(src) + off,
+                                         std::min<size_t>(piece, bytes - off), kind, st);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
 cudaError_t kernel_guard() { return fault_fires(FLAME_OFFLOAD_FAULT_KERNEL) ? cudaErrorLaunchFailure : cudaSuccess; }
 
 // Enqueue the offload of one tensor.  Returns the first CUDA error.
@@ -204,7 +216,7 @@ cudaError_t enqueue_push(FlameOffloadPool& p, Slot& s, const uint8_t* src, cudaS
     for (size_t k = 0; k < nchunks; ++k) {
       const uint64_t off = k * p.chunk_src_bytes;
       const uint64_t len = std::min<uint64_t>(p.chunk_src_bytes, s.bytes - off);
-      POOL_TRY(memcpy_async_checked(p.chunk_ptr(s.chunks[k]), src + off, len, cudaMemcpyDeviceToHost, p.s_d2h), "push: D2H");
+      POOL_TRY(copy_in_pieces(p.chunk_ptr(s.chunks[k]), src + off, len, cudaMemcpyDeviceToHost, p.s_d2h, p.d2h_piece), "push: D2H");
       p.stats.bytes_link_out += len;
     }
   } else {
@@ -230,8 +242,8 @@ cudaError_t enqueue_push(FlameOffloadPool& p, Slot& s, const uint8_t* src, cudaS
       for (size_t j = 0; j < kn; ++j) {
         const uint64_t ec = std::min<uint64_t>(p.chunk_elems, e - j * p.chunk_elems);
         const size_t link = p.stored_for(ec);
-        POOL_TRY(memcpy_async_checked(p.chunk_ptr(s.chunks[k0 + j]), t.dev + j * p.host_chunk_bytes, link,
-                                      cudaMemcpyDeviceToHost, p.s_d2h), "push: D2H");
+        POOL_TRY(copy_in_pieces(p.chunk_ptr(s.chunks[k0 + j]), t.dev + j * p.host_chunk_bytes, link,
+                                cudaMemcpyDeviceToHost, p.s_d2h, p.d2h_piece), "push: D2H");
         p.stats.bytes_link_out += link;
       }
       POOL_TRY(t.free_.record(p.s_d2h), "push: record(tile free)");
@@ -251,7 +263,7 @@ cudaError_t enqueue_pull(FlameOffloadPool& p, Slot& s, uint8_t* dst, cudaStream_
     for (size_t k = 0; k < nchunks; ++k) {
       const uint64_t off = k * p.chunk_src_bytes;
       const uint64_t len = std::min<uint64_t>(p.chunk_src_bytes, s.bytes - off);
-      POOL_TRY(memcpy_async_checked(dst + off, p.chunk_ptr(s.chunks[k]), len, cudaMemcpyHostToDevice, p.s_h2d), "pull: H2D");
+      POOL_TRY(copy_in_pieces(dst + off, p.chunk_ptr(s.chunks[k]), len, cudaMemcpyHostToDevice, p.s_h2d, p.h2d_piece), "pull: H2D");
       p.stats.bytes_link_in += len;
     }
     POOL_TRY(s.h2d_done.record(p.s_h2d), "pull: record(h2d_done)");
@@ -267,8 +279,8 @@ cudaError_t enqueue_pull(FlameOffloadPool& p, Slot& s, uint8_t* dst, cudaStream_
       for (size_t j = 0; j < kn; ++j) {
         const uint64_t ec = std::min<uint64_t>(p.chunk_elems, e - j * p.chunk_elems);
         const size_t link = p.stored_for(ec);
-        POOL_TRY(memcpy_async_checked(t.dev + j * p.host_chunk_bytes, p.chunk_ptr(s.chunks[k0 + j]), link,
-                                      cudaMemcpyHostToDevice, p.s_h2d), "pull: H2D");
+        POOL_TRY(copy_in_pieces(t.dev + j * p.host_chunk_bytes, p.chunk_ptr(s.chunks[k0 + j]), link,
+                                cudaMemcpyHostToDevice, p.s_h2d, p.h2d_piece), "pull: H2D");
         p.stats.bytes_link_in += link;
       }
       POOL_TRY(t.full.record(p.s_h2d), "pull: record(tile full)");
@@ -372,6 +384,8 @@ FlameOffloadPool* flame_offload_pool_create(size_t num_slots, size_t max_bytes, 
   p->slot_bytes = max_bytes;
   p->codec_flags = cfg.codec_flags;
   p->codec_max_ctas = cfg.codec_max_ctas;
+  p->d2h_piece = cfg.d2h_piece_bytes;
+  p->h2d_piece = cfg.h2d_piece_bytes;
 
   // A slot that fits in one chunk gets a chunk of exactly its stored size, so a
   // pool of small slots holds num_slots * stored(max_bytes) pinned bytes like
@@ -544,6 +558,21 @@ FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* p, FlameOffloa
   p->free_stack.push_back(h.slot);
   p->stats.pulls++;
   p->stats.bytes_logical_in += s.bytes;
+  p->stats.host_chunks_free = p->free_chunks.size();
+  return FLAME_OFFLOAD_OK;
+}
+
+FlameOffloadStatus flame_offload_pool_discard(FlameOffloadPool* p, FlameOffloadHandle h) {
+  if (!p) return fail(FLAME_OFFLOAD_ERR_INVALID, "discard: null pool");
+  std::lock_guard<std::mutex> lk(p->mu);
+  FlameOffloadStatus st = p->check_handle(h, "ActivationOffloadPool::discard");
+  if (st != FLAME_OFFLOAD_OK) return st;
+  Slot& s = p->slots[h.slot];
+  s.state = SlotState::Idle;
+  // An offload that is still writing these chunks runs on the D2H stream, the
+  // stream every later offload into them is queued on, so reuse stays ordered.
+  p->release_chunks(s, -1);
+  p->free_stack.push_back(h.slot);
   p->stats.host_chunks_free = p->free_chunks.size();
   return FLAME_OFFLOAD_OK;
 }

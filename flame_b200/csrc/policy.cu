@@ -153,3 +153,77 @@ FlameOffloadStatus flame_offload_policy_plan(const FlamePolicyInput* in, const F
 }
 
 }  // extern "C"
+
+namespace {
+
+struct SimResult { double stall_ms, recompute_ms; uint64_t resident, link; };
+
+// Timeline of one step under a given plan (see the header comment).
+SimResult simulate(const FlamePolicyInput& in, const FlamePolicyBlock* b, size_t n, const std::vector<int32_t>& dec, double payload_ratio) {
+  const double out_rate = in.d2h_gbs * 1e6, in_rate = in.h2d_gbs * 1e6;  // bytes per ms
+  SimResult r{0.0, 0.0, 0, 0};
+  std::vector<double> d2h_done(n, 0.0);
+  double t = 0.0, q_out = 0.0;
+  for (size_t g = 0; g < n; ++g) {  // forward
+    t += b[g].fwd_ms;
+    if (dec[g] == FLAME_POLICY_RESIDENT) { r.resident += b[g].saved_bytes; continue; }
+    if (dec[g] == FLAME_POLICY_RECOMPUTE) continue;
+    const double payload = (double)b[g].saved_bytes * (dec[g] == FLAME_POLICY_OFFLOAD_BF16 ? 1.0 : payload_ratio);
+    r.link += (uint64_t)payload;
+    q_out = std::max(q_out, t) + payload / out_rate;
+    d2h_done[g] = q_out;
+  }
+  // backward: restores are issued one block ahead of their consumer, in reverse order
+  double q_in = t;
+  std::vector<double> ready(n, 0.0);
+  auto issue = [&](size_t g, double now) {
+    if (dec[g] != FLAME_POLICY_OFFLOAD_BF16 && dec[g] != FLAME_POLICY_OFFLOAD_INT8 && dec[g] != FLAME_POLICY_OFFLOAD_FP8) return;
+    const double payload = (double)b[g].saved_bytes * (dec[g] == FLAME_POLICY_OFFLOAD_BF16 ? 1.0 : payload_ratio);
+    q_in = std::max(std::max(q_in, now), d2h_done[g]) + payload / in_rate;
+    ready[g] = q_in;
+  };
+  if (n) issue(n - 1, t);
+  for (size_t k = 0; k < n; ++k) {
+    const size_t g = n - 1 - k;
+    if (g > 0) issue(g - 1, t);  // prefetch the next block to be consumed
+    if (ready[g] > t) { r.stall_ms += ready[g] - t; t = ready[g]; }
+    if (dec[g] == FLAME_POLICY_RECOMPUTE) { t += b[g].fwd_ms; r.recompute_ms += b[g].fwd_ms; }
+    t += b[g].bwd_ms;
+  }
+  return r;
+}
+
+}  // namespace
+
+extern "C" {
+
+FlameOffloadStatus flame_offload_policy_plan_blocks(const FlamePolicyInput* in, const FlamePolicyBlock* blocks, size_t n,
+                                                              int offload_decision, int32_t* decisions, FlamePolicyBlockPlan* out) {
+  if (!in || (!blocks && n) || (!decisions && n)) return fail(FLAME_OFFLOAD_ERR_INVALID, "policy_plan_blocks: null argument");
+  if (in->d2h_gbs <= 0 || in->h2d_gbs <= 0) return fail(FLAME_OFFLOAD_ERR_INVALID, "policy_plan_blocks: link rates must be positive");
+  if (offload_decision != FLAME_POLICY_OFFLOAD_BF16 && offload_decision != FLAME_POLICY_OFFLOAD_INT8 && offload_decision != FLAME_POLICY_OFFLOAD_FP8)
+    return fail(FLAME_OFFLOAD_ERR_INVALID, "policy_plan_blocks: offload_decision must be one of the OFFLOAD_* values");
+  const double ratio = 0.5 + 1.0 / 64.0;
+  std::vector<int32_t> best;
+  SimResult best_r{};
+  double best_cost = 0.0;
+  std::vector<int32_t> dec(n);
+  for (size_t resident = 0; resident <= n; ++resident) {
+    uint64_t res_bytes = 0;
+    for (size_t g = n - resident; g < n; ++g) res_bytes += blocks[g].saved_bytes;
+    if (res_bytes > in->device_budget_bytes) break;  // more trailing blocks only cost more memory
+    for (size_t recompute = 0; recompute + resident <= n; ++recompute) {
+      for (size_t g = 0; g < n; ++g)
+        dec[g] = g >= n - resident ? FLAME_POLICY_RESIDENT : (g < recompute ? FLAME_POLICY_RECOMPUTE : offload_decision);
+      const SimResult r = simulate(*in, blocks, n, dec, ratio);
+      const double cost = r.stall_ms + r.recompute_ms;
+      // strictly better time wins; within 0.01 ms prefer fewer resident bytes (earlier in the search)
+      if (best.empty() || cost < best_cost - 0.01) { best = dec; best_r = r; best_cost = cost; }
+    }
+  }
+  for (size_t g = 0; g < n; ++g) decisions[g] = best.empty() ? offload_decision : best[g];
+  if (out) { out->est_stall_ms = best_r.stall_ms; out->est_recompute_ms = best_r.recompute_ms; out->resident_bytes = best_r.resident; out->link_bytes = best_r.link; }
+  return FLAME_OFFLOAD_OK;
+}
+
+}  // extern "C"

@@ -60,3 +60,34 @@ def plan(tensors: list[SavedTensor], *, d2h_gbs: float, h2d_gbs: float, fwd_ms: 
     st = _lib.lib().flame_offload_policy_plan(C.byref(inp), arr, n, dec, C.byref(est))
     raise_for_status(st, _lib.last_error())
     return [Decision(dec[i]) for i in range(n)], est.value
+
+
+@dataclass
+class Block:
+    saved_bytes: int
+    fwd_ms: float
+    bwd_ms: float
+
+
+@dataclass
+class BlockPlan:
+    decisions: list
+    est_stall_ms: float
+    est_recompute_ms: float
+    resident_bytes: int
+    link_bytes: int
+
+
+def plan_blocks(blocks: list[Block], *, d2h_gbs: float, h2d_gbs: float, device_budget_bytes: int,
+                offload: Decision = Decision.OFFLOAD_INT8) -> BlockPlan:
+    """Per-block decision for a stack of checkpointed blocks (flame_offload_policy_plan_blocks)."""
+    n = len(blocks)
+    arr = (_lib.PolicyBlock * max(n, 1))()
+    for i, b in enumerate(blocks):
+        arr[i] = _lib.PolicyBlock(b.saved_bytes, b.fwd_ms, b.bwd_ms)
+    inp = _lib.PolicyInput(d2h_gbs, h2d_gbs, 0.0, 0.0, device_budget_bytes, int(offload), 0.0)
+    dec = (C.c_int32 * max(n, 1))()
+    out = _lib.PolicyBlockPlan()
+    st = _lib.lib().flame_offload_policy_plan_blocks(C.byref(inp), arr, n, int(offload), dec, C.byref(out))
+    raise_for_status(st, _lib.last_error())
+    return BlockPlan([Decision(dec[i]) for i in range(n)], out.est_stall_ms, out.est_recompute_ms, out.resident_bytes, out.link_bytes)

@@ -172,6 +172,11 @@ typedef struct {
   int32_t codec_max_ctas;     /* thread blocks per codec launch; 0 = default */
   int32_t numa_node;          /* bind the slab to this NUMA node with mbind(); -1 = leave to first touch */
   uint32_t tile_chunks;       /* chunks per staging tile = per codec kernel launch; default 8 */
+  uint64_t d2h_piece_bytes;   /* a chunk's device-to-host copy is issued in pieces of this size; 0 = whole chunk.
+                                 A copy engine that saturates the link slows concurrent HBM-bound kernels by
+                                 50 % and more; 1-2 MiB pieces leave gaps that cut this to ~10-20 % at ~85 %
+                                 of the copy rate.  Use small pieces when offload overlaps training compute. */
+  uint64_t h2d_piece_bytes;   /* the same for host-to-device copies; 0 = whole chunk */
 } FlameOffloadPoolConfig;
 
 typedef struct {
@@ -215,6 +220,11 @@ FlameOffloadStatus flame_offload_pool_push(FlameOffloadPool* pool, const void* s
 FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* pool, FlameOffloadHandle handle, void* dst_device, size_t dst_bytes, void* compute_stream, unsigned int flags);
 /* Makes `stream` wait for the most recent restore issued from `slot`. */
 FlameOffloadStatus flame_offload_pool_wait_ready(FlameOffloadPool* pool, size_t slot, void* stream);
+
+/* Gives the slot of `handle` back without restoring it (the reference releases
+ * the slots of an abandoned block by pulling every handle,
+ * src/autograd.rs:1742-1769; this does the same bookkeeping without the copy). */
+FlameOffloadStatus flame_offload_pool_discard(FlameOffloadPool* pool, FlameOffloadHandle handle);
 
 /* clear(): src/activation_offload.rs:742-760.  Does not synchronise. */
 FlameOffloadStatus flame_offload_pool_clear(FlameOffloadPool* pool);
@@ -299,6 +309,29 @@ typedef struct {
 
 /* Deterministic for given inputs.  decisions[i] receives a FLAME_POLICY_* value. */
 FlameOffloadStatus flame_offload_policy_plan(const FlamePolicyInput* in, const FlamePolicyTensor* tensors, size_t n, int32_t* decisions, double* est_overhead_ms);
+
+/* Block-level plan for a stack of G checkpointed blocks run in order and
+ * back-propagated in reverse.  Simulates the two FIFO copy queues against the
+ * compute timeline: block g's saved bytes can start D2H when its forward ends,
+ * must be back on the device when its backward starts, and a restore cannot
+ * start before its own offload has finished.  Searches over how many trailing
+ * blocks stay resident (within device_budget_bytes) and how many leading
+ * blocks are recomputed instead, and returns the plan with the least estimated
+ * step time (ties: fewest resident bytes).  Deterministic. */
+typedef struct {
+  uint64_t saved_bytes; /* BF16 bytes the block saves for backward */
+  double fwd_ms;        /* forward time of the block (= its recompute cost) */
+  double bwd_ms;        /* backward time of the block */
+} FlamePolicyBlock;
+
+typedef struct {
+  double est_stall_ms;     /* backward waiting for restores, summed */
+  double est_recompute_ms; /* forward re-runs inside backward */
+  uint64_t resident_bytes; /* activation bytes kept on the device */
+  uint64_t link_bytes;     /* payload per direction per step */
+} FlamePolicyBlockPlan;
+
+FlameOffloadStatus flame_offload_policy_plan_blocks(const FlamePolicyInput* in, const FlamePolicyBlock* blocks, size_t n, int offload_decision, int32_t* decisions, FlamePolicyBlockPlan* out);
 
 #ifdef __cplusplus
 }
