@@ -59,24 +59,55 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs (read-only NVML, else nvidia-smi)."""
 
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index: int):
-        self.index, self.rows, self._stop, self._t = index, [], threading.Event(), None
+        self.index, self.sm, self.sm_max, self.reasons, self._stop, self._t = index, [], None, set(), threading.Event(), None
+        self._nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[index]) if visible and all(v.strip().isdigit() for v in visible.split(",")) else index
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+            self._nvml = pynvml
+        except Exception:
+            self._nvml = None
+
+    def _sample_nvml(self):
+        n = self._nvml
+        self.sm.append(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM))
+        r = n.nvmlDeviceGetCurrentClocksEventReasons(self._h) if hasattr(n, "nvmlDeviceGetCurrentClocksEventReasons") \
+            else n.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+        for name, bit in (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4)):
+            if r & bit:
+                self.reasons.add(name)
+
+    def _sample_smi(self):
+        out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
+                             capture_output=True, text=True, timeout=5).stdout.strip()
+        if out:
+            c = [x.strip() for x in out.split(",")]
+            if c[0].isdigit():
+                self.sm.append(int(c[0]))
+            if c[1].isdigit():
+                self.sm_max = int(c[1])
+            for i, name in enumerate(self.NAMES):
+                if len(c) > 2 + i and c[2 + i] == "Active":
+                    self.reasons.add(name)
 
     def _run(self):
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
-                                     capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.rows.append([c.strip() for c in out.split(",")])
+                self._sample_nvml() if self._nvml else self._sample_smi()
             except Exception:
                 pass
-            self._stop.wait(0.2)
+            self._stop.wait(0.002 if self._nvml else 0.2)
 
     def __enter__(self):
         self._t = threading.Thread(target=self._run, daemon=True)
@@ -88,13 +119,10 @@ class ClockSampler:
         self._t.join(timeout=6)
 
     def summary(self):
-        if not self.rows:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        sm = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": int(self.rows[0][1]) if self.rows[0][1].isdigit() else None,
-                "reasons": reasons, "samples": len(self.rows)}
+        if not self.sm:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": ["no clock samples"]}
+        sm = sorted(self.sm)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons), "samples": len(sm)}
 
 
 def make_workload(torch, dev, seed: int, blocks: int = BLOCKS):
@@ -260,21 +288,29 @@ def main():
             packed = [torch.empty(t.numel() * 2, dtype=torch.uint8, device=dev) for t in tensors]
             per_step_launches = 0
         else:
-            q, dq = (lib.flame_act_quant_int8_b128, lib.flame_act_dequant_int8_b128) if args.codec == "int8" else \
-                    (lib.flame_act_quant_fp8_b128, lib.flame_act_dequant_fp8_b128)
+            # one launch per checkpointed block: its five saved tensors are pushed together
+            # (flame_act_quant_b128_multi), as checkpoint_offload pushes a block's sub-tape in one loop
+            codec_id = 2 if args.codec == "int8" else 3
             packed = [torch.empty(lib.flame_act_packed_bytes(t.numel()), dtype=torch.uint8, device=dev) for t in tensors]
             so = [lib.flame_act_packed_scales_offset(t.numel()) for t in tensors]
+            per_block = len(BLOCK_SAVED)
+            groups = [list(range(b, min(b + per_block, len(tensors)))) for b in range(0, len(tensors), per_block)]
+
+            def table(bf16):
+                return [((_lib.ActTensor * len(g))(*[_lib.ActTensor(bf16[i].data_ptr(), packed[i].data_ptr(), packed[i].data_ptr() + so[i],
+                                                                      bf16[i].numel()) for i in g]), len(g)) for g in groups]
+            q_tables, d_tables = table(tensors), table(dst)
 
             def offload_all():
-                for t, p, o in zip(tensors, packed, so):
-                    rc = q(t.data_ptr(), p.data_ptr(), p.data_ptr() + o, t.numel(), 0, sp)
+                for arr, n in q_tables:
+                    rc = lib.flame_act_quant_b128_multi(codec_id, arr, n, 0, sp)
                     assert rc == 0, rc
 
             def restore_all():
-                for d, p, o in zip(reversed(dst), reversed(packed), reversed(so)):
-                    rc = dq(p.data_ptr(), p.data_ptr() + o, d.data_ptr(), d.numel(), sp)
+                for arr, n in reversed(d_tables):
+                    rc = lib.flame_act_dequant_b128_multi(codec_id, arr, n, sp)
                     assert rc == 0, rc
-            per_step_launches = 2 * len(tensors)
+            per_step_launches = 2 * len(groups)
 
         for _ in range(max(args.warmup, 1)):
             offload_all(); restore_all()
@@ -366,7 +402,7 @@ def main():
         if args.codec != "none":
             alg = ALG_BYTES_PER_ELEM * step_elems
             qa, da = alg / (quant_ms * 1e-3) * 1e-9, alg / (dequant_ms * 1e-3) * 1e-9
-            n_l = len(tensors)
+            n_l = per_step_launches // 2
             line["roofline"] = {"bound": "hbm", "kernel": "compress_b128_kernel", "achieved": round(qa, 1), "peak": hbm_peak, "unit": "GB/s",
                                 "frac": round(qa / hbm_peak, 4), "peak_kind": f"of {peak_kind}", "traffic": None,
                                 "alg_bytes_per_launch": int(alg / n_l), "avg_launch_us": round(quant_ms * 1e3 / n_l, 2), "launches_per_step": n_l}

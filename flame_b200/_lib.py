@@ -41,6 +41,10 @@ class SlotInfo(C.Structure):
                 ("bytes", C.c_uint64), ("stored_bytes", C.c_uint64), ("chunks", C.c_uint64)]
 
 
+class ActTensor(C.Structure):
+    _fields_ = [("bf16", C.c_void_p), ("codes", C.c_void_p), ("scales", C.c_void_p), ("n", C.c_size_t)]
+
+
 class LinkProbe(C.Structure):
     _fields_ = [(n, C.c_double) for n in ("d2h_gbs", "h2d_gbs", "hbm_copy_gbs", "quant_gbs", "dequant_gbs")]
 
@@ -81,6 +85,8 @@ SIGNATURES = {
     "flame_act_dequant_int8_b128": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "flame_act_quant_fp8_b128": (_i, [_vp, _vp, _vp, _sz, _u, _vp]),
     "flame_act_dequant_fp8_b128": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "flame_act_quant_b128_multi": (_i, [_i, C.POINTER(ActTensor), _sz, _u, _vp]),
+    "flame_act_dequant_b128_multi": (_i, [_i, C.POINTER(ActTensor), _sz, _vp]),
     "flame_act_packed_scales_offset": (_sz, [_sz]),
     "flame_act_packed_bytes": (_sz, [_sz]),
     "flame_act_set_max_ctas": (_i, [_i]),

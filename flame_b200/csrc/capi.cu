@@ -2,6 +2,7 @@
 // points.  The pool, the pinned cache and the policy live in their own files.
 #include <atomic>
 #include <cstring>
+#include <vector>
 
 #include "codec_kernels.cuh"
 #include "common.h"
@@ -134,6 +135,27 @@ int flame_act_quant_fp8_b128(const void* in, void* codes, void* scales, size_t n
 }
 int flame_act_dequant_fp8_b128(const void* codes, const void* scales, void* out, size_t n, void* stream) {
   return dequant_entry(kCodecFp8, codes, scales, out, n, stream);
+}
+
+static int multi_entry(bool quant, int codec, const FlameActTensor* t, size_t count, unsigned flags, void* stream) {
+  if (count == 0) return 0;
+  if (!t || (codec != kCodecInt8 && codec != kCodecFp8)) return (int)cudaErrorInvalidValue;
+  std::vector<TensorJob> jobs;
+  jobs.reserve(count);
+  for (size_t k = 0; k < count; ++k) {
+    if (t[k].n == 0) continue;
+    if (!t[k].bf16 || !t[k].codes || !t[k].scales) return (int)cudaErrorInvalidValue;
+    jobs.push_back(TensorJob{t[k].bf16, t[k].codes, t[k].n, single_chunk_layout(t[k].codes, t[k].scales, t[k].n)});
+  }
+  return quant ? (int)launch_compress_multi(codec, jobs.data(), jobs.size(), flags, (cudaStream_t)stream, 0)
+               : (int)launch_dequant_multi(codec, jobs.data(), jobs.size(), (cudaStream_t)stream, 0);
+}
+
+int flame_act_quant_b128_multi(int codec, const FlameActTensor* tensors, size_t count, unsigned int flags, void* stream) {
+  return multi_entry(true, codec, tensors, count, flags, stream);
+}
+int flame_act_dequant_b128_multi(int codec, const FlameActTensor* tensors, size_t count, void* stream) {
+  return multi_entry(false, codec, tensors, count, 0, stream);
 }
 
 size_t flame_act_packed_scales_offset(size_t n) { return (n + 255u) & ~(size_t)255u; }

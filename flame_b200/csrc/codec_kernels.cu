@@ -33,6 +33,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "codec_kernels.cuh"
 
@@ -45,6 +46,7 @@ constexpr int kUnroll = 2;                                   // loads in flight 
 constexpr int kTileElems = kThreads * kLaneElems * kUnroll;  // 8192
 constexpr int kTileBlocks = kTileElems / 128;                // 64 scales per tile
 constexpr int kLanesPerBlock = 128 / kLaneElems;             // 8
+constexpr int kStagedBufBytes = kTileElems + kTileBlocks * 4;  // one staged tile: codes then scales
 constexpr int kDequantUnroll = 4;                            // 16-byte code loads in flight per thread
 constexpr int kDequantTileElems = kThreads * kLaneElems * kDequantUnroll;  // 16384
 
@@ -309,141 +311,141 @@ __device__ __forceinline__ OutAddr locate(const uint8_t* base, const PackedLayou
   return locate(const_cast<uint8_t*>(base), L, elem0);
 }
 
+// ---- job table ----------------------------------------------------------------
+// One launch can serve several tensors (the saved activations of one checkpointed
+// block are pushed together): the table lists them with the index of each one's
+// first tile, and thread blocks walk the concatenated tile space.
+struct CodecJob {
+  const void* in;   // compress: BF16 source; dequantise: packed base
+  void* out;        // compress: packed base; dequantise: BF16 destination
+  size_t n;
+  PackedLayout L;
+  uint32_t tile0;   // first tile of this job in the launch's tile space
+  uint32_t pad;
+};
+constexpr int kMaxJobs = 48;
+struct JobTable {
+  uint32_t count;
+  uint32_t total_tiles;
+  CodecJob jobs[kMaxJobs];
+};
+static_assert(sizeof(JobTable) <= 4000, "kernel parameters must stay under 4 KB");
+
 // ---- compress kernel --------------------------------------------------------
-// Requires: in 32-byte aligned; every chunk's codes and scales 16-byte aligned;
-// chunk_elems a multiple of 8192 (or >= n).  Full tiles go through the shared
-// memory tiles and bulk stores; the last, partial tile uses predicated loads and
-// direct stores.
+// Requires per job: in 32-byte aligned; every chunk's codes and scales 16-byte
+// aligned; chunk_elems a multiple of 16384 (or >= n).  A job's last tile may be
+// ragged: it uses predicated loads and direct stores.
+
+// One tile's worth of work for one lane-vector: 16 elements in, 16 codes out.
 template <int kCodec, bool kFlag>
-__device__ __forceinline__ void compress_tail(const uint16_t* __restrict__ in, uint8_t* __restrict__ out, size_t n,
-                                              const PackedLayout& L, size_t full_tiles, int tid);
+__device__ __forceinline__ uint4 compress_lane(const U32x8& raw, float& scale) {
+  float x[kLaneElems];
+  unpack16(raw, x);
+  const float amax = absmax_8lanes(absmax_n<kLaneElems>(x));
+  uint32_t c[kLaneElems / 4];
+  encode_block_part<kCodec, kFlag, kLaneElems>(x, raw.v, amax, scale, c);
+  return make_uint4(c[0], c[1], c[2], c[3]);
+}
+
+// Ragged last tile of a job: `rem` (< 8192) elements starting at tin / o.
+template <int kCodec, bool kFlag>
+__device__ __forceinline__ void compress_ragged_tile(const uint16_t* __restrict__ tin, const OutAddr o, size_t rem, int tid) {
+#pragma unroll 1
+  for (int u = 0; u < kUnroll; ++u) {
+    const size_t e0 = (size_t)(u * kThreads + tid) * kLaneElems;
+    // whole warps enter together so the shuffles stay converged
+    if (((size_t)(u * kThreads + (tid & ~31)) * kLaneElems) >= rem) break;
+    U32x8 r;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r.v[i] = 0u;
+    if (e0 + kLaneElems <= rem) {
+      r = ld_stream32(tin + e0);
+    } else if (e0 < rem) {
+      for (size_t i = 0; e0 + i < rem; ++i) {
+        const uint32_t h = tin[e0 + i];
+        r.v[i >> 1] |= (i & 1) ? (h << 16) : h;
+      }
+    }
+    float scale;
+    const uint4 c4 = compress_lane<kCodec, kFlag>(r, scale);
+    if (e0 + kLaneElems <= rem) {
+      *reinterpret_cast<uint4*>(o.codes + e0) = c4;
+    } else if (e0 < rem) {
+      const uint32_t c[4] = {c4.x, c4.y, c4.z, c4.w};
+      for (size_t i = 0; e0 + i < rem; ++i) o.codes[e0 + i] = (uint8_t)(c[i >> 2] >> (8 * (i & 3)));
+    }
+    if ((tid & (kLanesPerBlock - 1)) == 0 && e0 < rem) o.scales[e0 / 128] = scale;
+  }
+}
 
 // kStaged = true : codes and scales of a tile are collected in shared memory and
 //                  leave as two bulk asynchronous copies issued by one thread.
 // kStaged = false: every lane stores its 16 codes with one 16-byte store and one
 //                  lane in eight stores the scale; no shared memory, no barrier.
+// Round k of every thread block works on tile k*grid + block of the launch's
+// tile space; the host sizes the grid so that all blocks run the same number of
+// rounds (see grid_balanced).
 template <int kCodec, bool kFlag, bool kStaged>
-__global__ void __launch_bounds__(kThreads)
-compress_b128_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ out, size_t n, PackedLayout L,
-                     unsigned tiles_per_cta) {
+__global__ void __launch_bounds__(kThreads, 5)
+compress_b128_kernel(const __grid_constant__ JobTable T, unsigned rounds) {
+  // staged variant only: two buffers of (codes tile | scales tile) in dynamic shared memory
+  extern __shared__ __align__(128) uint8_t smem_tiles[];
   const int tid = threadIdx.x;
-  const size_t full_tiles = n / kTileElems;
-  // Round k of every thread block works on the window [k*grid, (k+1)*grid) of tiles;
-  // the host sizes the grid so that all blocks run the same number of rounds
-  // (see grid_balanced) and all are resident at once.
-
-  if (!kStaged) {
-    for (unsigned k = 0; k < tiles_per_cta; ++k) {
-      const size_t tile = (size_t)k * gridDim.x + blockIdx.x;
-      if (tile >= full_tiles) break;
-      const uint16_t* tin = in + tile * kTileElems;
-      U32x8 raw[kUnroll];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) raw[u] = ld_stream32(tin + (size_t)(u * kThreads + tid) * kLaneElems);
-      const OutAddr o = locate(out, L, tile * kTileElems);
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        float x[kLaneElems];
-        unpack16(raw[u], x);
-        const float amax = absmax_8lanes(absmax_n<kLaneElems>(x));
-        float scale;
-        uint32_t c[kLaneElems / 4];
-        encode_block_part<kCodec, kFlag, kLaneElems>(x, raw[u].v, amax, scale, c);
-        const int v = u * kThreads + tid;
-        __stcs(reinterpret_cast<uint4*>(o.codes + v * kLaneElems), make_uint4(c[0], c[1], c[2], c[3]));
-        if ((tid & (kLanesPerBlock - 1)) == 0) o.scales[v / kLanesPerBlock] = scale;
-      }
-    }
-    compress_tail<kCodec, kFlag>(in, out, n, L, full_tiles, tid);
-    return;
-  }
-
-  __shared__ __align__(128) uint8_t s_codes[2][kTileElems];
-  __shared__ __align__(128) float s_scales[2][kTileBlocks];
   int buf = 0;
+  uint32_t j = 0;
 
-  for (unsigned k = 0; k < tiles_per_cta; ++k) {
-    const size_t tile = (size_t)k * gridDim.x + blockIdx.x;
-    if (tile >= full_tiles) break;
-    const uint16_t* tin = in + tile * kTileElems;
+  for (unsigned k = 0; k < rounds; ++k) {
+    const uint32_t g = k * gridDim.x + blockIdx.x;
+    if (g >= T.total_tiles) break;
+    while (j + 1 < T.count && g >= T.jobs[j + 1].tile0) ++j;
+    const CodecJob& J = T.jobs[j];
+    const size_t e_tile = (size_t)(g - J.tile0) * kTileElems;
+    const uint16_t* tin = static_cast<const uint16_t*>(J.in) + e_tile;
+    if (e_tile + kTileElems > J.n) {  // the job's ragged last tile
+      compress_ragged_tile<kCodec, kFlag>(tin, locate(static_cast<uint8_t*>(J.out), J.L, e_tile), J.n - e_tile, tid);
+      continue;
+    }
     U32x8 raw[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) raw[u] = ld_stream32(tin + (size_t)(u * kThreads + tid) * kLaneElems);
 
-    // The bulk store issued two tiles ago read this buffer; it must be done.
-    if (tid == 0) bulk_wait_read<1>();
-    __syncthreads();
-
+    if (!kStaged) {
+      const OutAddr o = locate(static_cast<uint8_t*>(J.out), J.L, e_tile);
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      float x[kLaneElems];
-      unpack16(raw[u], x);
-      const float amax = absmax_8lanes(absmax_n<kLaneElems>(x));
-      float scale;
-      uint32_t c[kLaneElems / 4];
-      encode_block_part<kCodec, kFlag, kLaneElems>(x, raw[u].v, amax, scale, c);
-      const int v = u * kThreads + tid;
-      *reinterpret_cast<uint4*>(&s_codes[buf][v * kLaneElems]) = make_uint4(c[0], c[1], c[2], c[3]);
-      if ((tid & (kLanesPerBlock - 1)) == 0) s_scales[buf][v / kLanesPerBlock] = scale;
-    }
-    fence_async_smem();
-    __syncthreads();
-    if (tid == 0) {
-      const OutAddr o = locate(out, L, tile * kTileElems);
-      bulk_store(o.codes, s_codes[buf], kTileElems);
-      bulk_store(o.scales, s_scales[buf], kTileBlocks * sizeof(float));
-      bulk_commit();
-    }
-    buf ^= 1;
-  }
-
-  compress_tail<kCodec, kFlag>(in, out, n, L, full_tiles, tid);
-  if (tid == 0) bulk_wait_all<0>();
-}
-
-// Ragged tail (n not a multiple of 8192): handled by the last thread block with
-// predicated loads and direct stores.
-template <int kCodec, bool kFlag>
-__device__ __forceinline__ void compress_tail(const uint16_t* __restrict__ in, uint8_t* __restrict__ out, size_t n,
-                                              const PackedLayout& L, size_t full_tiles, int tid) {
-  const size_t tail0 = full_tiles * kTileElems;
-  if (tail0 < n && blockIdx.x == gridDim.x - 1) {
-    const uint16_t* tin = in + tail0;
-    const size_t rem = n - tail0;
-    const OutAddr o = locate(out, L, tail0);
-#pragma unroll 1
-    for (int u = 0; u < kUnroll; ++u) {
-      const size_t e0 = (size_t)(u * kThreads + tid) * kLaneElems;
-      // whole warps enter together so the shuffles stay converged
-      if (((size_t)(u * kThreads + (tid & ~31)) * kLaneElems) >= rem) break;
-      U32x8 r;
+      for (int u = 0; u < kUnroll; ++u) {
+        float scale;
+        const uint4 c = compress_lane<kCodec, kFlag>(raw[u], scale);
+        const int v = u * kThreads + tid;
+        __stcs(reinterpret_cast<uint4*>(o.codes + v * kLaneElems), c);
+        if ((tid & (kLanesPerBlock - 1)) == 0) o.scales[v / kLanesPerBlock] = scale;
+      }
+    } else {
+      // The bulk store issued two tiles ago read this buffer; it must be done.
+      if (tid == 0) bulk_wait_read<1>();
+      __syncthreads();
 #pragma unroll
-      for (int i = 0; i < 8; ++i) r.v[i] = 0u;
-      if (e0 + kLaneElems <= rem) {
-        r = ld_stream32(tin + e0);
-      } else if (e0 < rem) {
-        for (size_t i = 0; e0 + i < rem; ++i) {
-          const uint32_t h = tin[e0 + i];
-          r.v[i >> 1] |= (i & 1) ? (h << 16) : h;
-        }
+      for (int u = 0; u < kUnroll; ++u) {
+        float scale;
+        const uint4 c = compress_lane<kCodec, kFlag>(raw[u], scale);
+        const int v = u * kThreads + tid;
+        uint8_t* s_codes = smem_tiles + buf * kStagedBufBytes;
+        *reinterpret_cast<uint4*>(s_codes + v * kLaneElems) = c;
+        if ((tid & (kLanesPerBlock - 1)) == 0) reinterpret_cast<float*>(s_codes + kTileElems)[v / kLanesPerBlock] = scale;
       }
-      float x[kLaneElems];
-      unpack16(r, x);
-      const float amax = absmax_8lanes(absmax_n<kLaneElems>(x));
-      float scale;
-      uint32_t c[kLaneElems / 4];
-      encode_block_part<kCodec, kFlag, kLaneElems>(x, r.v, amax, scale, c);
-      if (e0 + kLaneElems <= rem) {
-        *reinterpret_cast<uint4*>(o.codes + e0) = make_uint4(c[0], c[1], c[2], c[3]);
-      } else if (e0 < rem) {
-        for (size_t i = 0; e0 + i < rem; ++i) o.codes[e0 + i] = (uint8_t)(c[i >> 2] >> (8 * (i & 3)));
+      fence_async_smem();
+      __syncthreads();
+      if (tid == 0) {
+        const OutAddr o = locate(static_cast<uint8_t*>(J.out), J.L, e_tile);
+        const uint8_t* s_codes = smem_tiles + buf * kStagedBufBytes;
+        bulk_store(o.codes, s_codes, kTileElems);
+        bulk_store(o.scales, s_codes + kTileElems, kTileBlocks * sizeof(float));
+        bulk_commit();
       }
-      if ((tid & (kLanesPerBlock - 1)) == 0 && e0 < rem) o.scales[e0 / 128] = scale;
+      buf ^= 1;
     }
   }
-
+  if (kStaged && tid == 0) bulk_wait_all<0>();
 }
-
 
 // Any alignment, any n: one warp per 128-element block, scalar accesses.
 template <int kCodec, bool kFlag>
@@ -519,52 +521,56 @@ __device__ __forceinline__ uint16_t decode1(uint8_t c, float scale) {
   return (uint16_t)(o0 & 0xFFFFu);
 }
 
-// Requires: every chunk's codes 16-byte aligned, out 32-byte aligned.  Each
-// thread turns 16 codes (one 16-byte load) into 16 BF16 (one 32-byte store);
-// the 8 lanes of a block read the same scale, which the L1 serves.
+// Requires per job: every chunk's codes 16-byte aligned, out 32-byte aligned.
+// Each thread turns 16 codes (one 16-byte load) into 16 BF16 (one 32-byte
+// store); the 8 lanes of a block read the same scale, which the L1 serves.
+// Tiles are 16384 elements; a job's last tile is predicated per 16-element
+// vector and its last (up to 15) elements are handled one per thread.
 template <int kCodec>
-__global__ void __launch_bounds__(kThreads)
-dequant_b128_kernel(const uint8_t* __restrict__ in, uint16_t* __restrict__ out, size_t n, PackedLayout L,
-                    unsigned tiles_per_cta) {
-  constexpr int kDU = kDequantUnroll;  // 16-byte loads in flight per thread
+__global__ void __launch_bounds__(kThreads, 5)
+dequant_b128_kernel(const __grid_constant__ JobTable T, unsigned rounds) {
+  constexpr int kDU = kDequantUnroll;
   const int tid = threadIdx.x;
-  const size_t nvec = n / kLaneElems;  // whole 16-element vectors
-  const size_t tiles = (nvec + kThreads * kDU - 1) / (kThreads * kDU);
-  for (unsigned k = 0; k < tiles_per_cta; ++k) {
-    const size_t tile = (size_t)k * gridDim.x + blockIdx.x;
-    if (tile >= tiles) break;
-    const size_t v0 = tile * (kThreads * kDU);
-    const OutAddr A = locate(in, L, v0 * kLaneElems);  // a tile never straddles chunks
+  uint32_t j = 0;
+  for (unsigned k = 0; k < rounds; ++k) {
+    const uint32_t g = k * gridDim.x + blockIdx.x;
+    if (g >= T.total_tiles) break;
+    while (j + 1 < T.count && g >= T.jobs[j + 1].tile0) ++j;
+    const CodecJob& J = T.jobs[j];
+    const size_t e_tile = (size_t)(g - J.tile0) * kDequantTileElems;
+    const size_t nvec = (J.n - e_tile) / kLaneElems;  // whole vectors from here to the end of the job
+    const OutAddr A = locate(static_cast<const uint8_t*>(J.in), J.L, e_tile);  // a tile never straddles chunks
+    uint16_t* out = static_cast<uint16_t*>(J.out) + e_tile;
     uint4 c[kDU];
     float s[kDU];
 #pragma unroll
     for (int u = 0; u < kDU; ++u) {
-      const size_t v = v0 + (size_t)(u * kThreads + tid);
-      if (v < nvec) {
-        const int lv = u * kThreads + tid;
+      const int lv = u * kThreads + tid;
+      if ((size_t)lv < nvec) {
         c[u] = __ldcs(reinterpret_cast<const uint4*>(A.codes + (size_t)lv * kLaneElems));
         s[u] = __ldg(A.scales + lv / kLanesPerBlock);
       }
     }
 #pragma unroll
     for (int u = 0; u < kDU; ++u) {
-      const size_t v = v0 + (size_t)(u * kThreads + tid);
-      if (v < nvec) {
+      const int lv = u * kThreads + tid;
+      if ((size_t)lv < nvec) {
         U32x8 o;
         decode4<kCodec>(c[u].x, s[u], o.v[0], o.v[1]);
         decode4<kCodec>(c[u].y, s[u], o.v[2], o.v[3]);
         decode4<kCodec>(c[u].z, s[u], o.v[4], o.v[5]);
         decode4<kCodec>(c[u].w, s[u], o.v[6], o.v[7]);
-        st_stream32(out + v * kLaneElems, o);
+        st_stream32(out + (size_t)lv * kLaneElems, o);
       }
     }
-  }
-  // up to 15 trailing elements
-  const size_t t0 = nvec * kLaneElems;
-  if (blockIdx.x == gridDim.x - 1 && tid < (int)(n - t0)) {
-    const size_t e = t0 + tid;
-    const OutAddr a = locate(in, L, e & ~(size_t)127);
-    out[e] = decode1<kCodec>(a.codes[e & 127], a.scales[0]);
+    // up to 15 trailing elements of the job, in its last tile
+    if (nvec < (size_t)kThreads * kDU) {
+      const size_t t0 = nvec * kLaneElems, left = J.n - e_tile - t0;
+      if ((size_t)tid < left) {
+        const size_t e = t0 + tid;
+        out[e] = decode1<kCodec>(A.codes[e], A.scales[e / 128]);
+      }
+    }
   }
 }
 
@@ -680,11 +686,11 @@ int grid_for(size_t work_items, int ctas_per_sm, int max_ctas) {
 
 // Resident thread blocks per SM of a kernel (queried once per kernel).
 template <typename K>
-int resident_ctas_per_sm(K kernel) {
+int resident_ctas_per_sm(K kernel, size_t dyn_smem = 0) {
   static int cached = 0;
   if (cached == 0) {
     int v = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, kernel, kThreads, 0) != cudaSuccess || v <= 0) v = 4;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, kernel, kThreads, dyn_smem) != cudaSuccess || v <= 0) v = 4;
     cached = v;
   }
   return cached;
@@ -693,12 +699,28 @@ int resident_ctas_per_sm(K kernel) {
 // A grid in which every thread block takes the same number of consecutive tiles
 // and all blocks are resident at once: no second wave, no ragged last round.
 struct Grid { int ctas; unsigned tiles_per_cta; };
-Grid grid_balanced(size_t tiles, int ctas_per_sm, int max_ctas) {
+int env_int(const char* name) {
+  const char* e = getenv(name);
+  return e ? (atoi(e) < 1 ? 1 : atoi(e)) : 0;
+}
+// Small launches (at most `balance_limit` rounds per block): every block resident, the same number
+// of rounds for all, no second wave and no ragged last round.  Large launches: `max_rounds` rounds
+// per block and many more blocks than fit at once, so that the hardware block scheduler evens out
+// SM speed differences, which add up over hundreds of rounds of a static assignment.  The two
+// thresholds were swept on a B200 per kernel kind (compress 16 / 4, dequantise 2 / 2);
+// FLAME_ACT_BALANCE_LIMIT and FLAME_ACT_MAX_ROUNDS override them for tuning.
+Grid grid_balanced(size_t tiles, int ctas_per_sm, int max_ctas, int balance_limit, int max_rounds) {
+  static int env_limit = -1, env_rounds = -1;
+  if (env_limit < 0) { env_limit = env_int("FLAME_ACT_BALANCE_LIMIT"); env_rounds = env_int("FLAME_ACT_MAX_ROUNDS"); }
+  if (env_limit > 0) balance_limit = env_limit;
+  if (env_rounds > 0) max_rounds = env_rounds;
   if (tiles == 0) tiles = 1;
   size_t cap = (size_t)sm_count() * (size_t)ctas_per_sm;
   const int lim = max_ctas > 0 ? max_ctas : g_max_ctas;
-  if (lim > 0 && cap > (size_t)lim) cap = (size_t)lim;
-  const size_t per = (tiles + cap - 1) / cap;
+  const bool capped = lim > 0 && cap > (size_t)lim;
+  if (capped) cap = (size_t)lim;
+  size_t per = (tiles + cap - 1) / cap;
+  if (!capped && per > (size_t)balance_limit) per = (size_t)max_rounds;
   return {(int)((tiles + per - 1) / per), (unsigned)per};
 }
 
@@ -735,67 +757,130 @@ PackedLayout packed_chunks_layout(size_t n, size_t chunk_elems, size_t chunk_str
   return L;
 }
 
+namespace {
+
+bool compress_job_fast(const TensorJob& j) { return aligned(j.bf16, 32) && layout_fast(j.packed, j.layout, j.n); }
+
+template <int kTile>
+void add_job(JobTable& T, const void* in, void* out, const TensorJob& j) {
+  CodecJob& c = T.jobs[T.count++];
+  c.in = in; c.out = out; c.n = j.n; c.L = j.layout; c.tile0 = T.total_tiles; c.pad = 0;
+  T.total_tiles += (uint32_t)((j.n + kTile - 1) / kTile);
+}
+
+template <int kCodec, bool kFlag, bool kStaged>
+cudaError_t launch_compress_table(const JobTable& T, cudaStream_t stream, int max_ctas) {
+  auto kern = compress_b128_kernel<kCodec, kFlag, kStaged>;
+  const size_t smem = kStaged ? 2 * kStagedBufBytes : 0;
+  const Grid g = grid_balanced(T.total_tiles, resident_ctas_per_sm(kern, smem), max_ctas, 16, 4);
+  kern<<<g.ctas, kThreads, smem, stream>>>(T, g.tiles_per_cta);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_compress_table(int codec, unsigned flags, const JobTable& T, cudaStream_t stream, int max_ctas) {
+  const bool f = (flags & 1u) != 0, st = (flags & kFlagStagedStores) != 0;
+  if (codec == kCodecInt8) {
+    if (f) return st ? launch_compress_table<kCodecInt8, true, true>(T, stream, max_ctas) : launch_compress_table<kCodecInt8, true, false>(T, stream, max_ctas);
+    return st ? launch_compress_table<kCodecInt8, false, true>(T, stream, max_ctas) : launch_compress_table<kCodecInt8, false, false>(T, stream, max_ctas);
+  }
+  if (f) return st ? launch_compress_table<kCodecFp8, true, true>(T, stream, max_ctas) : launch_compress_table<kCodecFp8, true, false>(T, stream, max_ctas);
+  return st ? launch_compress_table<kCodecFp8, false, true>(T, stream, max_ctas) : launch_compress_table<kCodecFp8, false, false>(T, stream, max_ctas);
+}
+
+cudaError_t launch_compress_generic(int codec, unsigned flags, const TensorJob& j, cudaStream_t stream, int max_ctas) {
+  const bool flag = (flags & 1u) != 0;
+  auto* i = static_cast<const uint16_t*>(j.bf16);
+  auto* o = static_cast<uint8_t*>(j.packed);
+  const size_t warps = (j.n + 127) / 128;
+  const int grid = grid_for((warps + 7) / 8, 8, max_ctas);
+  if (codec == kCodecInt8) {
+    if (flag) compress_b128_generic_kernel<kCodecInt8, true><<<grid, kThreads, 0, stream>>>(i, o, j.n, j.layout);
+    else compress_b128_generic_kernel<kCodecInt8, false><<<grid, kThreads, 0, stream>>>(i, o, j.n, j.layout);
+  } else {
+    if (flag) compress_b128_generic_kernel<kCodecFp8, true><<<grid, kThreads, 0, stream>>>(i, o, j.n, j.layout);
+    else compress_b128_generic_kernel<kCodecFp8, false><<<grid, kThreads, 0, stream>>>(i, o, j.n, j.layout);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_compress_multi(int codec, const TensorJob* jobs, size_t count, unsigned flags, cudaStream_t stream, int max_ctas) {
+  JobTable T;
+  T.count = 0; T.total_tiles = 0;
+  for (size_t k = 0; k < count; ++k) {
+    const TensorJob& j = jobs[k];
+    if (j.n == 0) continue;
+    if (!j.bf16 || !j.packed) return cudaErrorInvalidValue;
+    if (!compress_job_fast(j)) {
+      cudaError_t e = launch_compress_generic(codec, flags, j, stream, max_ctas);
+      if (e != cudaSuccess) return e;
+      continue;
+    }
+    add_job<kTileElems>(T, j.bf16, j.packed, j);
+    if (T.count == kMaxJobs) {
+      cudaError_t e = launch_compress_table(codec, flags, T, stream, max_ctas);
+      if (e != cudaSuccess) return e;
+      T.count = 0; T.total_tiles = 0;
+    }
+  }
+  return T.count ? launch_compress_table(codec, flags, T, stream, max_ctas) : cudaSuccess;
+}
+
+cudaError_t launch_dequant_multi(int codec, const TensorJob* jobs, size_t count, cudaStream_t stream, int max_ctas) {
+  JobTable T;
+  T.count = 0; T.total_tiles = 0;
+  auto flush = [&]() -> cudaError_t {
+    if (T.count == 0) return cudaSuccess;
+    if (codec == kCodecInt8) {
+      auto kern = dequant_b128_kernel<kCodecInt8>;
+      const Grid g = grid_balanced(T.total_tiles, resident_ctas_per_sm(kern), max_ctas, 2, 2);
+      kern<<<g.ctas, kThreads, 0, stream>>>(T, g.tiles_per_cta);
+    } else {
+      auto kern = dequant_b128_kernel<kCodecFp8>;
+      const Grid g = grid_balanced(T.total_tiles, resident_ctas_per_sm(kern), max_ctas, 2, 2);
+      kern<<<g.ctas, kThreads, 0, stream>>>(T, g.tiles_per_cta);
+    }
+    T.count = 0; T.total_tiles = 0;
+    return cudaGetLastError();
+  };
+  for (size_t k = 0; k < count; ++k) {
+    const TensorJob& j = jobs[k];
+    if (j.n == 0) continue;
+    if (!j.bf16 || !j.packed) return cudaErrorInvalidValue;
+    if (!(aligned(j.bf16, 32) && layout_fast(j.packed, j.layout, j.n))) {
+      auto* c = static_cast<const uint8_t*>(j.packed);
+      auto* o = static_cast<uint16_t*>(j.bf16);
+      const int grid = grid_for((j.n + kThreads - 1) / kThreads, 8, max_ctas);
+      if (codec == kCodecInt8) dequant_b128_generic_kernel<kCodecInt8><<<grid, kThreads, 0, stream>>>(c, o, j.n, j.layout);
+      else dequant_b128_generic_kernel<kCodecFp8><<<grid, kThreads, 0, stream>>>(c, o, j.n, j.layout);
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+      continue;
+    }
+    add_job<kDequantTileElems>(T, j.packed, j.bf16, j);
+    if (T.count == kMaxJobs) {
+      cudaError_t e = flush();
+      if (e != cudaSuccess) return e;
+    }
+  }
+  return flush();
+}
+
 cudaError_t launch_compress(int codec, const void* in, void* out, size_t n, const PackedLayout& L,
                             unsigned flags, cudaStream_t stream, int max_ctas) {
   if (n == 0) return cudaSuccess;
   if (!in || !out) return cudaErrorInvalidValue;
-  const bool flag = (flags & 1u) != 0;
-  auto* i = static_cast<const uint16_t*>(in);
-  auto* o = static_cast<uint8_t*>(out);
-  if (aligned(in, 32) && layout_fast(out, L, n)) {
-    const size_t tiles = (n + kTileElems - 1) / kTileElems;  // the ragged tail rides with the last block
-    const bool staged = (flags & kFlagStagedStores) != 0;
-#define FLAME_LAUNCH_COMPRESS(C, F, S)                                                          \
-    do {                                                                                          \
-      auto kern = compress_b128_kernel<C, F, S>;                                                  \
-      const Grid g = grid_balanced(tiles, resident_ctas_per_sm(kern), max_ctas);                  \
-      kern<<<g.ctas, kThreads, 0, stream>>>(i, o, n, L, g.tiles_per_cta);                         \
-    } while (0)
-    if (codec == kCodecInt8) {
-      if (flag) { if (staged) FLAME_LAUNCH_COMPRESS(kCodecInt8, true, true); else FLAME_LAUNCH_COMPRESS(kCodecInt8, true, false); }
-      else { if (staged) FLAME_LAUNCH_COMPRESS(kCodecInt8, false, true); else FLAME_LAUNCH_COMPRESS(kCodecInt8, false, false); }
-    } else {
-      if (flag) { if (staged) FLAME_LAUNCH_COMPRESS(kCodecFp8, true, true); else FLAME_LAUNCH_COMPRESS(kCodecFp8, true, false); }
-      else { if (staged) FLAME_LAUNCH_COMPRESS(kCodecFp8, false, true); else FLAME_LAUNCH_COMPRESS(kCodecFp8, false, false); }
-    }
-#undef FLAME_LAUNCH_COMPRESS
-  } else {
-    const size_t warps = (n + 127) / 128;
-    const int grid = grid_for((warps + 7) / 8, 8, max_ctas);
-    if (codec == kCodecInt8) {
-      if (flag) compress_b128_generic_kernel<kCodecInt8, true><<<grid, kThreads, 0, stream>>>(i, o, n, L);
-      else compress_b128_generic_kernel<kCodecInt8, false><<<grid, kThreads, 0, stream>>>(i, o, n, L);
-    } else {
-      if (flag) compress_b128_generic_kernel<kCodecFp8, true><<<grid, kThreads, 0, stream>>>(i, o, n, L);
-      else compress_b128_generic_kernel<kCodecFp8, false><<<grid, kThreads, 0, stream>>>(i, o, n, L);
-    }
-  }
-  return cudaGetLastError();
+  const TensorJob j{const_cast<void*>(in), out, n, L};
+  return launch_compress_multi(codec, &j, 1, flags, stream, max_ctas);
 }
 
 cudaError_t launch_dequant(int codec, const void* in, void* out, size_t n, const PackedLayout& L,
                            cudaStream_t stream, int max_ctas) {
   if (n == 0) return cudaSuccess;
   if (!in || !out) return cudaErrorInvalidValue;
-  auto* c = static_cast<const uint8_t*>(in);
-  auto* o = static_cast<uint16_t*>(out);
-  if (aligned(out, 32) && layout_fast(in, L, n)) {
-    const size_t tiles = (n + kDequantTileElems - 1) / kDequantTileElems;
-    if (codec == kCodecInt8) {
-      auto kern = dequant_b128_kernel<kCodecInt8>;
-      const Grid g = grid_balanced(tiles, resident_ctas_per_sm(kern), max_ctas);
-      kern<<<g.ctas, kThreads, 0, stream>>>(c, o, n, L, g.tiles_per_cta);
-    } else {
-      auto kern = dequant_b128_kernel<kCodecFp8>;
-      const Grid g = grid_balanced(tiles, resident_ctas_per_sm(kern), max_ctas);
-      kern<<<g.ctas, kThreads, 0, stream>>>(c, o, n, L, g.tiles_per_cta);
-    }
-  } else {
-    const int grid = grid_for((n + kThreads - 1) / kThreads, 8, max_ctas);
-    if (codec == kCodecInt8) dequant_b128_generic_kernel<kCodecInt8><<<grid, kThreads, 0, stream>>>(c, o, n, L);
-    else dequant_b128_generic_kernel<kCodecFp8><<<grid, kThreads, 0, stream>>>(c, o, n, L);
-  }
-  return cudaGetLastError();
+  const TensorJob j{out, const_cast<void*>(in), n, L};
+  return launch_dequant_multi(codec, &j, 1, stream, max_ctas);
 }
 
 cudaError_t launch_bf16_to_fp8(const void* in, void* out, float inv_scale, size_t n, cudaStream_t stream, int max_ctas) {

@@ -32,6 +32,20 @@ PackedLayout single_chunk_layout(const void* codes, const void* scales, size_t n
 // in the packed layout codes | pad to 256 B | scales.
 PackedLayout packed_chunks_layout(size_t n, size_t chunk_elems, size_t chunk_stride);
 
+// One tensor of a multi-tensor launch: its BF16 memory (source of compress,
+// destination of dequantise) and its compressed memory.
+struct TensorJob {
+  void* bf16;
+  void* packed;
+  size_t n;
+  PackedLayout layout;
+};
+
+// Up to any number of tensors; tensors that qualify for the fast kernels are
+// batched 48 to a launch, the others go one by one through the generic kernels.
+cudaError_t launch_compress_multi(int codec, const TensorJob* jobs, size_t count, unsigned flags, cudaStream_t stream, int max_ctas);
+cudaError_t launch_dequant_multi(int codec, const TensorJob* jobs, size_t count, cudaStream_t stream, int max_ctas);
+
 // max_ctas: 0 = process default (see set_max_ctas), otherwise a cap on the grid.
 cudaError_t launch_compress(int codec, const void* in_bf16, void* out_base, size_t n, const PackedLayout& layout,
                             unsigned flags, cudaStream_t stream, int max_ctas);

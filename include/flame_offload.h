@@ -97,6 +97,20 @@ int flame_act_dequant_int8_b128(const void* codes_i8, const void* scales_f32, vo
 int flame_act_quant_fp8_b128(const void* in_bf16, void* codes_u8, void* scales_f32, size_t n, unsigned int flags, void* stream);
 int flame_act_dequant_fp8_b128(const void* codes_u8, const void* scales_f32, void* out_bf16, size_t n, void* stream);
 
+/* Several tensors in one launch: the saved activations of a checkpointed block
+ * are pushed together (the loop at src/autograd.rs:1714-1741), and one launch over
+ * all of them avoids a launch gap and a ragged last wave per tensor.  Results are
+ * identical to calling the single-tensor entry points one by one. */
+typedef struct {
+  void* bf16;   /* BF16 tensor: source of quantise, destination of dequantise */
+  void* codes;  /* n bytes */
+  void* scales; /* ceil(n/128) floats */
+  size_t n;
+} FlameActTensor;
+/* codec: FLAME_OFFLOAD_COMPRESSION_INT8_B128 or _FP8_B128 */
+int flame_act_quant_b128_multi(int codec, const FlameActTensor* tensors, size_t count, unsigned int flags, void* stream);
+int flame_act_dequant_b128_multi(int codec, const FlameActTensor* tensors, size_t count, void* stream);
+
 /* Packed layout of one compressed tensor or chunk in one buffer:
  * codes[n] | zero padding up to a 256-byte boundary | scales[ceil(n/128)]. */
 size_t flame_act_packed_scales_offset(size_t n);

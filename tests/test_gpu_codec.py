@@ -118,6 +118,34 @@ def test_ocp_encoder_flag(cuda_device):
     _check_fp8(synthetic.edge_values(), cuda_device, flags=1)
 
 
+@pytest.mark.parametrize("codec,name", [(2, "int8"), (3, "fp8")])
+def test_multi_tensor_launch_equals_single_launches(cuda_device, codec, name):
+    """One launch over many tensors of ragged sizes (more than one table's worth) gives the same bytes."""
+    import ctypes as C
+
+    lib = _lib.lib()
+    sizes = [8192 * 3, 1, 129, 8192 * 2 + 77, 16384 * 5, 16384 * 2 + 15, 100000, 8191] * 7  # 56 tensors
+    xs, codes, scales, outs = [], [], [], []
+    for i, n in enumerate(sizes):
+        xs.append(G.to_dev(synthetic.normal_with_outliers(n, seed=1000 + i), cuda_device))
+        codes.append(torch.full((n,), 0xAB, dtype=torch.uint8, device=cuda_device))
+        scales.append(torch.full(((n + 127) // 128,), -7.0, dtype=torch.float32, device=cuda_device))
+        outs.append(torch.zeros(n, dtype=torch.bfloat16, device=cuda_device))
+    arr = (_lib.ActTensor * len(sizes))(*[_lib.ActTensor(x.data_ptr(), c.data_ptr(), s.data_ptr(), n)
+                                           for x, c, s, n in zip(xs, codes, scales, sizes)])
+    assert lib.flame_act_quant_b128_multi(codec, arr, len(sizes), 0, G.stream_ptr(cuda_device)) == 0
+    arr2 = (_lib.ActTensor * len(sizes))(*[_lib.ActTensor(o.data_ptr(), c.data_ptr(), s.data_ptr(), n)
+                                            for o, c, s, n in zip(outs, codes, scales, sizes)])
+    assert lib.flame_act_dequant_b128_multi(codec, arr2, len(sizes), G.stream_ptr(cuda_device)) == 0
+    torch.cuda.synchronize()
+    for x, c, s, o, n in zip(xs, codes, scales, outs, sizes):
+        c1, s1 = G.quant(name, x)
+        assert torch.equal(c, c1) and torch.equal(s, s1)
+        assert torch.equal(o.view(torch.int16), G.dequant(name, c1, s1, n).view(torch.int16))
+    assert lib.flame_act_quant_b128_multi(codec, None, 0, 0, None) == 0
+    assert lib.flame_act_quant_b128_multi(9, arr, 1, 0, None) == 1
+
+
 def test_block_codec_goldens(cuda_device, golden_dir):
     from tests.golden.make_golden import BLOCK_CASES
 
