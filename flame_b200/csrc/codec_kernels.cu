@@ -209,22 +209,56 @@ __device__ __forceinline__ uint32_t fp8_encode_ref_scaled(float x, float inv) { 
 // the rounding boundaries (they are FP16 numbers with a zero low bit) without
 // crossing one, and puts exact ties just above: round-to-nearest-even of that
 // equals round-half-up of |y|.  |y| >= 248 must give 0x7F: those lanes are made
-// NaN, which the converter encodes as 0x7F.  Zero gives 0.  Magnitudes in
-// (0, 2^-6) need the reference's float formula: the caller detects them from
-// `min_nz` (the smallest magnitude among elements whose source is not +-0) and
-// re-encodes the lane with fp8_encode_ref.  `xpair` is the two source BF16.
-__device__ __forceinline__ uint32_t fp8_encode_pair_fast(float ylo_abs, float yhi_abs, uint32_t xpair, __half2& min_nz) {
+// NaN, which the converter encodes as 0x7F.  Zero gives 0.  `min_all` collects the
+// smallest magnitude seen, so that the caller can tell whether any lane needs
+// more care (see fp8_encode_lane_ref).
+__device__ __forceinline__ uint32_t fp8_encode_pair_fast(float ylo_abs, float yhi_abs, __half2& min_all) {
   uint32_t h;
   asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(yhi_abs), "f"(ylo_abs));
   const __half2 hh = *reinterpret_cast<const __half2*>(&h);
   const uint32_t sat = __hge2_mask(hh, __half2half2(__ushort_as_half((unsigned short)0x5BC0)));  // 248.0
-  const uint32_t zero = __heq2_mask(*reinterpret_cast<const __nv_bfloat162*>(&xpair), __float2bfloat162_rn(0.0f));
-  const uint32_t hz = h | zero;  // lanes whose source is zero become NaN, which __hmin2 ignores
-  min_nz = __hmin2(min_nz, *reinterpret_cast<const __half2*>(&hz));
+  min_all = __hmin2(min_all, hh);  // a NaN lane is ignored
   const uint32_t h2 = h | 0x00010001u | sat;
   uint16_t c;
   asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(c) : "r"(h2));
   return c;  // low byte = code(ylo), high byte = code(yhi); bit 7 may be set on saturated lanes
+}
+
+// N elements of one lane with the reference encoder: codes of x[i] * inv, inv finite and positive.
+// raw: the N/2 input words (two BF16 each), which carry the sign bits.
+//   common case  : every magnitude is 0 or >= 2^-6 and no source element is zero: hardware path,
+//                  sign = sign bit of x.
+//   zeros present: same codes, but a zero magnitude keeps sign 0 (`val < 0` is false for -0.0).
+//   a magnitude in (0, 2^-6): the reference's float formula decides; the lane is re-encoded exactly.
+template <int N>
+__device__ __forceinline__ void fp8_encode_lane_ref(const float (&x)[N], const uint32_t* raw, float inv, uint32_t (&out)[N / 4]) {
+  __half2 min_all = __half2half2(__ushort_as_half((unsigned short)0x7BFF));  // 65504
+#pragma unroll
+  for (int i = 0; i < N / 4; ++i) {
+    const uint32_t c01 = fp8_encode_pair_fast(__fmul_rn(fabsf(x[4 * i]), inv), __fmul_rn(fabsf(x[4 * i + 1]), inv), min_all);
+    const uint32_t c23 = fp8_encode_pair_fast(__fmul_rn(fabsf(x[4 * i + 2]), inv), __fmul_rn(fabsf(x[4 * i + 3]), inv), min_all);
+    const uint32_t mag = __byte_perm(c01, c23, 0x5410);
+    const uint32_t sgn = __byte_perm(raw[2 * i], raw[2 * i + 1], 0x7531);  // high bytes of the four BF16
+    out[i] = (mag & 0x7F7F7F7Fu) | (sgn & 0x80808080u);
+  }
+  // anything below 2^-6 (0x2400 in FP16)?  Zero counts: rare enough to be handled off the fast path.
+  if (__hlt(__hmin(__low2half(min_all), __high2half(min_all)), __ushort_as_half((unsigned short)0x2400))) {
+    bool tiny = false;
+#pragma unroll
+    for (int i = 0; i < N; ++i) tiny |= (x[i] != 0.0f) && (__fmul_rn(fabsf(x[i]), inv) < 0.015625f);
+    if (!tiny) {
+#pragma unroll
+      for (int i = 0; i < N / 4; ++i) {
+        const uint32_t mag = out[i] & 0x7F7F7F7Fu;
+        out[i] = mag | (out[i] & ((mag + 0x7F7F7F7Fu) & 0x80808080u));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < N / 4; ++i)
+        out[i] = fp8_encode_ref_scaled(x[4 * i], inv) | (fp8_encode_ref_scaled(x[4 * i + 1], inv) << 8) |
+                 (fp8_encode_ref_scaled(x[4 * i + 2], inv) << 16) | (fp8_encode_ref_scaled(x[4 * i + 3], inv) << 24);
+    }
+  }
 }
 
 // OCP E4M3: round-to-nearest-even, saturate to +-448.  The hardware converter
@@ -266,26 +300,7 @@ __device__ __forceinline__ void encode_fp8(const float (&x)[N], const uint32_t* 
                (fp8_encode_ocp_pair(__fmul_rn(x[4 * i + 2], inv), __fmul_rn(x[4 * i + 3], inv)) << 16);
     return;
   }
-  __half2 min_nz = __half2half2(__ushort_as_half((unsigned short)0x7BFF));  // 65504
-#pragma unroll
-  for (int i = 0; i < N / 4; ++i) {
-    const uint32_t c01 = fp8_encode_pair_fast(__fmul_rn(fabsf(x[4 * i]), inv), __fmul_rn(fabsf(x[4 * i + 1]), inv), raw[2 * i], min_nz);
-    const uint32_t c23 = fp8_encode_pair_fast(__fmul_rn(fabsf(x[4 * i + 2]), inv), __fmul_rn(fabsf(x[4 * i + 3]), inv), raw[2 * i + 1], min_nz);
-    const uint32_t mag = (c01 | (c23 << 16)) & 0x7F7F7F7Fu;
-    // sign bytes of the four BF16 (their high bytes); a zero magnitude keeps sign 0,
-    // which is what `val < 0` gives for +-0.0
-    const uint32_t sgn = __byte_perm(raw[2 * i], raw[2 * i + 1], 0x7531);
-    const uint32_t nz = (mag + 0x7F7F7F7Fu) & 0x80808080u;
-    out[i] = mag | (sgn & nz);
-  }
-  // any magnitude in (0, 2^-6)?  (0x2400 = 2^-6 in FP16)
-  const __half lo = __low2half(min_nz), hi = __high2half(min_nz);
-  if (__hlt(__hmin(lo, hi), __ushort_as_half((unsigned short)0x2400))) {
-#pragma unroll
-    for (int i = 0; i < N / 4; ++i)
-      out[i] = fp8_encode_ref_scaled(x[4 * i], inv) | (fp8_encode_ref_scaled(x[4 * i + 1], inv) << 8) |
-               (fp8_encode_ref_scaled(x[4 * i + 2], inv) << 16) | (fp8_encode_ref_scaled(x[4 * i + 3], inv) << 24);
-  }
+  fp8_encode_lane_ref<N>(x, raw, inv, out);
 }
 
 template <int kCodec, bool kFlag, int N>
@@ -385,8 +400,13 @@ __device__ __forceinline__ void compress_ragged_tile(const uint16_t* __restrict_
 // Round k of every thread block works on tile k*grid + block of the launch's
 // tile space; the host sizes the grid so that all blocks run the same number of
 // rounds (see grid_balanced).
+// Resident blocks per SM the compiler must allow: the int8 body fits 5 in 48 registers; the FP8 body
+// (two encoders: conversion hardware plus the exact sub-normal arm) needs 64 and runs 4.
+template <int kCodec>
+struct CompressOccupancy { static constexpr int kMinBlocks = kCodec == kCodecFp8 ? 4 : 5; };
+
 template <int kCodec, bool kFlag, bool kStaged>
-__global__ void __launch_bounds__(kThreads, 5)
+__global__ void __launch_bounds__(kThreads, CompressOccupancy<kCodec>::kMinBlocks)
 compress_b128_kernel(const __grid_constant__ JobTable T, unsigned rounds) {
   // staged variant only: two buffers of (codes tile | scales tile) in dynamic shared memory
   extern __shared__ __align__(128) uint8_t smem_tiles[];
@@ -597,20 +617,9 @@ bf16_to_fp8_vec_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ ou
     float x[kLaneElems];
     unpack16(r, x);
     uint32_t c[4];
-    bool slow = !(inv_scale > 0.0f) || !(inv_scale < 3.0e38f);  // sign of y must equal sign of x
-    if (!slow) {
-      __half2 min_nz = __half2half2(__ushort_as_half((unsigned short)0x7BFF));
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t c01 = fp8_encode_pair_fast(__fmul_rn(fabsf(x[4 * i]), inv_scale), __fmul_rn(fabsf(x[4 * i + 1]), inv_scale), r.v[2 * i], min_nz);
-        const uint32_t c23 = fp8_encode_pair_fast(__fmul_rn(fabsf(x[4 * i + 2]), inv_scale), __fmul_rn(fabsf(x[4 * i + 3]), inv_scale), r.v[2 * i + 1], min_nz);
-        const uint32_t mag = (c01 | (c23 << 16)) & 0x7F7F7F7Fu;
-        const uint32_t sgn = __byte_perm(r.v[2 * i], r.v[2 * i + 1], 0x7531);
-        c[i] = mag | (sgn & ((mag + 0x7F7F7F7Fu) & 0x80808080u));
-      }
-      slow = __hlt(__hmin(__low2half(min_nz), __high2half(min_nz)), __ushort_as_half((unsigned short)0x2400));
-    }
-    if (slow) {
+    if ((inv_scale > 0.0f) && (inv_scale < 3.0e38f)) {  // the sign of x*inv_scale is the sign of x
+      fp8_encode_lane_ref<kLaneElems>(x, r.v, inv_scale, c);
+    } else {
 #pragma unroll
       for (int i = 0; i < 4; ++i)
         c[i] = fp8_encode_ref_scaled(x[4 * i], inv_scale) | (fp8_encode_ref_scaled(x[4 * i + 1], inv_scale) << 8) |

@@ -104,6 +104,24 @@ def test_scale_edge_blocks(cuda_device):
     _check_fp8(x, cuda_device)
 
 
+def test_sparse_activations_with_signed_zeros(cuda_device):
+    """ReLU-like data: half the elements are exact zeros, some of them -0.0, a few tiny values among them."""
+    rng = np.random.default_rng(3)
+    bits = synthetic.normal(200000 + 5, seed=8)
+    zero = rng.random(bits.size) < 0.5
+    bits[zero] = np.where(rng.random(int(zero.sum())) < 0.3, 0x8000, 0x0000).astype(np.uint16)
+    tiny = rng.choice(bits.size, 300, replace=False)
+    bits[tiny] = (0x2000 | (rng.integers(0, 2, 300) << 15) | rng.integers(0, 128, 300)).astype(np.uint16)  # ~1e-19
+    _check_fp8(bits, cuda_device)
+    _check_int8(bits, cuda_device)
+    lib = _lib.lib()
+    x = G.to_dev(bits, cuda_device)
+    codes = torch.empty(bits.size, dtype=torch.uint8, device=cuda_device)
+    assert lib.flame_bf16_to_fp8(x.data_ptr(), codes.data_ptr(), 56.0, bits.size, None) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(codes.cpu().numpy(), capi.bf16_to_fp8(bits, 56.0))
+
+
 def test_nan_elements_do_not_poison_a_block(cuda_device):
     x = synthetic.normal(512, 4)
     x[3] = 0x7FC0
