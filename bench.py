@@ -44,6 +44,11 @@ if ROOT not in sys.path:
 METRIC = "activation offload+restore GB/s per GPU (BF16-equiv), whole job"
 UNIT = "GB/s"
 ALG_BYTES_PER_ELEM = 3.03125  # 2 B read + 1 B code + 4/128 B scale (and the mirror image for dequantise)
+# dram__bytes_read.sum + dram__bytes_write.sum per element from the ncu captures summarised under profiles/
+# (one launch = one DiT block, 169,869,312 elements: 486.1 MB compress, 458.1 MB dequantise); traffic grows in
+# proportion to the elements of a launch.  Below the algorithmic figure because the L2 still holds part of the
+# output when the kernel ends.
+NCU_TRAFFIC_PER_ELEM = {"compress": 486.1e6 / 169869312, "dequant": 458.1e6 / 169869312}
 PCIE_GEN5_X16_GBS = 63.0      # 32 GT/s x 16 lanes x 128/130 / 8
 TOKENS, HIDDEN, BLOCKS = 4608, 3072, 20
 # saved set of one block, as last dims: norm1 out, QKV, attention out, norm2 out, SwiGLU gate+up
@@ -217,6 +222,139 @@ def workload_config(args, world):
             "l2": "inputs larger than L2 (6.79 GB of distinct tensors per step)", "replicas": world, "parallelism": f"dp{world} independent replicas, no collective"}
 
 
+def _event_ms(torch, stream, fn, reps: int):
+    """Median CUDA-event milliseconds of fn() on `stream` after one warm-up call."""
+    fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def run_sweep(args, torch, lib, dev, rank):
+    """Config 5: one contiguous BF16 N(0,1) tensor of 1 MB .. 4 GB, offload + restore through the pool with no
+    compression, int8 and fp8, chunk sizes 2 / 8 / 32 MB.  One JSON line per point: BF16-equivalent GB/s of the
+    round trip, link GB/s against the PCIe Gen5 x16 bound, and the codec kernels' share against the HBM peak."""
+    from flame_b200 import ActivationOffloadPool, OffloadCompression
+
+    hbm_peak, peak_kind = measured_peaks()
+    stream = torch.cuda.current_stream()
+    modes = {"none": OffloadCompression.NONE, "int8": OffloadCompression.INT8_B128, "fp8": OffloadCompression.FP8_B128}
+    g = torch.Generator(device=dev).manual_seed(0)
+    mb = 1
+    while mb <= args.sweep_max_mb:
+        nbytes = mb << 20
+        n = nbytes // 2
+        x = torch.randn(n, device=dev, dtype=torch.float32, generator=g).to(torch.bfloat16) if n <= (1 << 28) else \
+            torch.randn(n // 8, device=dev, dtype=torch.float32, generator=g).to(torch.bfloat16).repeat(8)
+        dst = torch.empty_like(x)
+        for codec, mode in modes.items():
+            for chunk_mb in (2, 8, 32):
+                pool = ActivationOffloadPool(dev, 1, nbytes, mode, chunk_bytes=chunk_mb << 20)
+
+                def round_trip():
+                    pool.pull_into(pool.push(x), dst)
+
+                reps = 7 if mb <= 256 else 3
+                ms = _event_ms(torch, stream, round_trip, reps)
+                st = pool.stats()
+                link_bytes = st["bytes_link_out"] // st["pushes"]
+                point = {"mode": "sweep", "tensor_mb": mb, "codec": codec, "chunk_mb": chunk_mb, "round_trip_ms": round(ms, 4),
+                         "gbs_bf16_equiv": round(2 * nbytes / (ms * 1e-3) * 1e-9, 2),
+                         # the round trip is one offload followed by one restore: each direction gets about half the time
+                         "link_gbs_per_direction": round(link_bytes / (ms * 1e-3 / 2) * 1e-9, 2),
+                         "link_frac_of_pcie_gen5_x16": round(link_bytes / (ms * 1e-3 / 2) * 1e-9 / PCIE_GEN5_X16_GBS, 3)}
+                if codec != "none":
+                    q = lib.flame_act_quant_int8_b128 if codec == "int8" else lib.flame_act_quant_fp8_b128
+                    d = lib.flame_act_dequant_int8_b128 if codec == "int8" else lib.flame_act_dequant_fp8_b128
+                    codes = torch.empty(n, dtype=torch.uint8, device=dev)
+                    scales = torch.empty((n + 127) // 128, dtype=torch.float32, device=dev)
+                    sp = stream.cuda_stream
+                    qms = _event_ms(torch, stream, lambda: q(x.data_ptr(), codes.data_ptr(), scales.data_ptr(), n, 0, sp), reps)
+                    dms = _event_ms(torch, stream, lambda: d(codes.data_ptr(), scales.data_ptr(), dst.data_ptr(), n, sp), reps)
+                    alg = ALG_BYTES_PER_ELEM * n
+                    point["compress_gbs"] = round(alg / (qms * 1e-3) * 1e-9, 1)
+                    point["dequant_gbs"] = round(alg / (dms * 1e-3) * 1e-9, 1)
+                    point["compress_frac_of_hbm"] = round(point["compress_gbs"] / hbm_peak, 3)
+                    point["dequant_frac_of_hbm"] = round(point["dequant_gbs"] / hbm_peak, 3)
+                    point["hbm_peak_kind"] = peak_kind
+                    del codes, scales
+                if rank == 0:
+                    print(json.dumps(point), flush=True)
+                pool.close()
+        del x, dst
+        torch.cuda.empty_cache()
+        mb *= 2
+
+
+def run_interference(args, torch, lib, dev):
+    """How much a host-link copy slows kernels that run beside it.  An HBM-bound loop (SiLU over 28 MB tensors)
+    and a compute-bound loop (BF16 GEMM) are timed alone and while 1 GiB crosses the link on another stream,
+    device-to-host and host-to-device, issued as one copy or in pieces."""
+    import torch.nn.functional as F
+
+    xs = [torch.randn(1, TOKENS, HIDDEN, device=dev, dtype=torch.bfloat16) for _ in range(8)]
+    a = torch.randn(TOKENS, HIDDEN, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(HIDDEN, 3 * HIDDEN, device=dev, dtype=torch.bfloat16)
+    nb = 256 << 20
+    src = torch.randn(nb // 2, device=dev).to(torch.bfloat16)
+    back = torch.empty_like(src)
+    host = torch.empty(nb, dtype=torch.uint8).pin_memory()
+    side = torch.cuda.Stream(dev)
+
+    def elementwise():
+        for i in range(300):
+            F.silu(xs[i % 8])
+
+    def gemm():
+        for _ in range(60):
+            torch.matmul(a, w)
+
+    def copies(kind, piece):
+        def issue():
+            for _ in range(4):
+                for off in range(0, nb, piece):
+                    if kind == 2:
+                        lib.flame_cuda_memcpy_async(host.data_ptr() + off, src.data_ptr() + off, piece, 2, side.cuda_stream)
+                    else:
+                        lib.flame_cuda_memcpy_async(back.data_ptr() + off, host.data_ptr() + off, piece, 1, side.cuda_stream)
+        return issue
+
+    def run(fg, bg):
+        torch.cuda.synchronize()
+        e0, e1, s0, s1 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+        s0.record(side)
+        if bg is not None:
+            bg()
+        s1.record(side)
+        e0.record()
+        fg()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1), (4 * nb / (s0.elapsed_time(s1) * 1e-3) * 1e-9 if bg is not None else None)
+
+    for fg in (elementwise, gemm):
+        run(fg, None)
+    base = {"elementwise": min(run(elementwise, None)[0] for _ in range(3)), "gemm": min(run(gemm, None)[0] for _ in range(3))}
+    print(json.dumps({"mode": "interference", "alone_ms": {k: round(v, 3) for k, v in base.items()}}), flush=True)
+    for direction, kind in (("d2h", 2), ("h2d", 1)):
+        for piece_mb in (1, 2, 4, 16, 256):
+            row = {"mode": "interference", "copy": direction, "piece_mb": piece_mb}
+            for name, fg in (("elementwise", elementwise), ("gemm", gemm)):
+                ms, gbs = run(fg, copies(kind, piece_mb << 20))
+                row[name + "_ms"] = round(ms, 3)
+                row[name + "_slowdown_pct"] = round(100.0 * (ms - base[name]) / base[name], 1)
+                row[name + "_copy_gbs"] = round(gbs, 1)
+            print(json.dumps(row), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -230,6 +368,9 @@ def main():
     ap.add_argument("--no-dit", action="store_true", help="skip the DiT training-step overhead measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--only", choices=["all", "value", "e2e"], default="all", help="profiling: run only one timed region")
+    ap.add_argument("--mode", choices=["bench", "sweep", "interference"], default="bench",
+                    help="sweep: 1 MB..4 GB single tensor x codec x chunk size; interference: copies against HBM-bound kernels")
+    ap.add_argument("--sweep-max-mb", type=int, default=4096)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
 
@@ -251,19 +392,28 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.lib()  # raises if the CUDA library is missing: there is no fallback
 
+    from flame_b200 import replicas
+
     def barrier():
-        if world > 1:
-            dist.barrier()
+        replicas.barrier(world)
         torch.cuda.synchronize()
 
     def max_over_ranks(ms: float) -> float:
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return replicas.max_over_ranks(ms, world, dev)
 
-    tensors = make_workload(torch, dev, seed=rank, blocks=args.blocks)
+    if args.mode == "sweep":
+        run_sweep(args, torch, lib, dev, rank)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.mode == "interference":
+        if rank == 0:
+            run_interference(args, torch, lib, dev)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    tensors = make_workload(torch, dev, seed=replicas.workload_seed(rank), blocks=args.blocks)
     step_bytes = sum(t.numel() * 2 for t in tensors)
     step_elems = sum(t.numel() for t in tensors)
     max_bytes = max(t.numel() * 2 for t in tensors)
@@ -404,10 +554,12 @@ def main():
             qa, da = alg / (quant_ms * 1e-3) * 1e-9, alg / (dequant_ms * 1e-3) * 1e-9
             n_l = per_step_launches // 2
             line["roofline"] = {"bound": "hbm", "kernel": "compress_b128_kernel", "achieved": round(qa, 1), "peak": hbm_peak, "unit": "GB/s",
-                                "frac": round(qa / hbm_peak, 4), "peak_kind": f"of {peak_kind}", "traffic": None,
+                                "frac": round(qa / hbm_peak, 4), "peak_kind": f"of {peak_kind}",
+                                "traffic": int(NCU_TRAFFIC_PER_ELEM["compress"] * step_elems / (per_step_launches // 2)) if args.codec == "int8" else None,
                                 "alg_bytes_per_launch": int(alg / n_l), "avg_launch_us": round(quant_ms * 1e3 / n_l, 2), "launches_per_step": n_l}
             line["roofline_dequant"] = {"bound": "hbm", "kernel": "dequant_b128_kernel", "achieved": round(da, 1), "peak": hbm_peak, "unit": "GB/s",
-                                        "frac": round(da / hbm_peak, 4), "peak_kind": f"of {peak_kind}", "traffic": None,
+                                        "frac": round(da / hbm_peak, 4), "peak_kind": f"of {peak_kind}",
+                                        "traffic": int(NCU_TRAFFIC_PER_ELEM["dequant"] * step_elems / (per_step_launches // 2)) if args.codec == "int8" else None,
                                         "alg_bytes_per_launch": int(alg / n_l), "avg_launch_us": round(dequant_ms * 1e3 / n_l, 2)}
         line["clocks"] = clk_value.summary()
     else:

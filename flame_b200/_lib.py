@@ -55,7 +55,8 @@ class PolicyTensor(C.Structure):
 
 class PolicyInput(C.Structure):
     _fields_ = [("d2h_gbs", C.c_double), ("h2d_gbs", C.c_double), ("fwd_ms", C.c_double), ("bwd_ms", C.c_double),
-                ("device_budget_bytes", C.c_uint64), ("lossy_codec", C.c_int32), ("link_utilisation", C.c_double)]
+                ("device_budget_bytes", C.c_uint64), ("lossy_codec", C.c_int32), ("link_utilisation", C.c_double),
+                ("interference", C.c_double)]
 
 
 class PolicyBlock(C.Structure):
@@ -63,7 +64,8 @@ class PolicyBlock(C.Structure):
 
 
 class PolicyBlockPlan(C.Structure):
-    _fields_ = [("est_stall_ms", C.c_double), ("est_recompute_ms", C.c_double), ("resident_bytes", C.c_uint64), ("link_bytes", C.c_uint64)]
+    _fields_ = [("est_stall_ms", C.c_double), ("est_recompute_ms", C.c_double), ("resident_bytes", C.c_uint64), ("link_bytes", C.c_uint64),
+                ("est_interference_ms", C.c_double)]
 
 
 _vp, _sz, _i, _u, _f, _d = C.c_void_p, C.c_size_t, C.c_int, C.c_uint, C.c_float, C.c_double

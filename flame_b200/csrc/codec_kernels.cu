@@ -17,7 +17,7 @@
 // per 16 elements of a lane.  Codes and scales are written into a shared-memory
 // tile (double buffered) and leave the SM as two bulk asynchronous copies
 // (cp.async.bulk.global.shared::cta), so the store path costs one instruction
-// per tile instead of one per thread.  Cluster size is 1; no multicast.
+// per tile instead of one per thread.  Cluster size is 1; every copy is CTA-local.
 //
 // Output addressing is "packed chunks": chunk c of `chunk_elems` elements lives
 // at out + c*chunk_stride, codes first, its scales at a byte offset inside the

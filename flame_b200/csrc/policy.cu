@@ -156,12 +156,12 @@ FlameOffloadStatus flame_offload_policy_plan(const FlamePolicyInput* in, const F
 
 namespace {
 
-struct SimResult { double stall_ms, recompute_ms; uint64_t resident, link; };
+struct SimResult { double stall_ms, recompute_ms; uint64_t resident, link; double busy_ms; };
 
 // Timeline of one step under a given plan (see the header comment).
 SimResult simulate(const FlamePolicyInput& in, const FlamePolicyBlock* b, size_t n, const std::vector<int32_t>& dec, double payload_ratio) {
   const double out_rate = in.d2h_gbs * 1e6, in_rate = in.h2d_gbs * 1e6;  // bytes per ms
-  SimResult r{0.0, 0.0, 0, 0};
+  SimResult r{0.0, 0.0, 0, 0, 0.0};
   std::vector<double> d2h_done(n, 0.0);
   double t = 0.0, q_out = 0.0;
   for (size_t g = 0; g < n; ++g) {  // forward
@@ -172,6 +172,7 @@ SimResult simulate(const FlamePolicyInput& in, const FlamePolicyBlock* b, size_t
     r.link += (uint64_t)payload;
     q_out = std::max(q_out, t) + payload / out_rate;
     d2h_done[g] = q_out;
+    r.busy_ms += payload / out_rate;
   }
   // backward: restores are issued one block ahead of their consumer, in reverse order
   double q_in = t;
@@ -181,6 +182,7 @@ SimResult simulate(const FlamePolicyInput& in, const FlamePolicyBlock* b, size_t
     const double payload = (double)b[g].saved_bytes * (dec[g] == FLAME_POLICY_OFFLOAD_BF16 ? 1.0 : payload_ratio);
     q_in = std::max(std::max(q_in, now), d2h_done[g]) + payload / in_rate;
     ready[g] = q_in;
+    r.busy_ms += payload / in_rate;
   };
   if (n) issue(n - 1, t);
   for (size_t k = 0; k < n; ++k) {
@@ -216,13 +218,14 @@ FlameOffloadStatus flame_offload_policy_plan_blocks(const FlamePolicyInput* in, 
       for (size_t g = 0; g < n; ++g)
         dec[g] = g >= n - resident ? FLAME_POLICY_RESIDENT : (g < recompute ? FLAME_POLICY_RECOMPUTE : offload_decision);
       const SimResult r = simulate(*in, blocks, n, dec, ratio);
-      const double cost = r.stall_ms + r.recompute_ms;
+      const double cost = r.stall_ms + r.recompute_ms + std::max(0.0, in->interference) * r.busy_ms;
       // strictly better time wins; within 0.01 ms prefer fewer resident bytes (earlier in the search)
       if (best.empty() || cost < best_cost - 0.01) { best = dec; best_r = r; best_cost = cost; }
     }
   }
   for (size_t g = 0; g < n; ++g) decisions[g] = best.empty() ? offload_decision : best[g];
-  if (out) { out->est_stall_ms = best_r.stall_ms; out->est_recompute_ms = best_r.recompute_ms; out->resident_bytes = best_r.resident; out->link_bytes = best_r.link; }
+  if (out) { out->est_stall_ms = best_r.stall_ms; out->est_recompute_ms = best_r.recompute_ms; out->resident_bytes = best_r.resident; out->link_bytes = best_r.link;
+             out->est_interference_ms = std::max(0.0, in->interference) * best_r.busy_ms; }
   return FLAME_OFFLOAD_OK;
 }
 

@@ -258,7 +258,15 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20, 
         p = plan_blocks(blk, d2h_gbs=link.d2h_gbs, h2d_gbs=link.h2d_gbs, device_budget_bytes=budget, offload=Decision.OFFLOAD_INT8)
         out["offload_int8_planned"] = run_arm("offload_int8_planned", p.decisions, OffloadCompression.INT8_B128)
         out["offload_int8_planned"]["plan_est_stall_ms"] = round(p.est_stall_ms, 2)
+        out["offload_int8_planned"]["plan_est_interference_ms"] = round(p.est_interference_ms, 2)
         out["offload_int8_all"] = run_arm("offload_int8_all", [Decision.OFFLOAD_INT8] * blocks, OffloadCompression.INT8_B128)
+        # overhead against how much is offloaded: the first k blocks go out, the rest stay resident
+        curve = []
+        for k in sorted({blocks * 2 // 5, blocks * 3 // 5, blocks * 3 // 4}):
+            r = run_arm(f"int8_{k}", [Decision.OFFLOAD_INT8] * k + [Decision.RESIDENT] * (blocks - k), OffloadCompression.INT8_B128)
+            curve.append({"offloaded_blocks": k, "overhead_pct": r["overhead_pct"], "ms_per_step": r["ms_per_step"],
+                          "held_after_forward_gb": r["held_after_forward_gb"], "offloaded_gb_per_step": r.get("offloaded_gb_per_step")})
+        out["offload_int8_curve"] = curve
     if "offload_bf16" in arms:
         p = plan_blocks(blk, d2h_gbs=link.d2h_gbs, h2d_gbs=link.h2d_gbs, device_budget_bytes=budget, offload=Decision.OFFLOAD_BF16)
         out["offload_bf16_planned"] = run_arm("offload_bf16_planned", p.decisions, OffloadCompression.NONE)

@@ -319,6 +319,9 @@ typedef struct {
   uint64_t device_budget_bytes; /* activation bytes that may stay resident */
   int32_t lossy_codec;          /* FLAME_POLICY_OFFLOAD_INT8 or _FP8 */
   double link_utilisation;      /* fraction of fwd/bwd time the link may be busy; default 0.9 */
+  double interference;          /* plan_blocks: extra compute time per unit of time a copy engine is busy beside it
+                                   (copies slow HBM-bound kernels, see FlameOffloadPoolConfig.d2h_piece_bytes);
+                                   ~0.1 measured on a B200 DiT step with 2 MiB pieces; 0 = ignore */
 } FlamePolicyInput;
 
 /* Deterministic for given inputs.  decisions[i] receives a FLAME_POLICY_* value. */
@@ -343,6 +346,7 @@ typedef struct {
   double est_recompute_ms; /* forward re-runs inside backward */
   uint64_t resident_bytes; /* activation bytes kept on the device */
   uint64_t link_bytes;     /* payload per direction per step */
+  double est_interference_ms; /* compute slowed by concurrent copies */
 } FlamePolicyBlockPlan;
 
 FlameOffloadStatus flame_offload_policy_plan_blocks(const FlamePolicyInput* in, const FlamePolicyBlock* blocks, size_t n, int offload_decision, int32_t* decisions, FlamePolicyBlockPlan* out);

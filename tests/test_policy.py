@@ -42,3 +42,20 @@ def test_lossless_tensors_stay_bf16_and_plan_is_deterministic():
 def test_bad_rates_are_rejected():
     with pytest.raises(InvalidInput):
         plan(dit_tensors(1), d2h_gbs=0, h2d_gbs=10, fwd_ms=1, bwd_ms=1)
+
+
+def test_block_plan_keeps_trailing_blocks_resident_and_counts_interference():
+    from flame_b200.policy import Block, plan_blocks
+
+    blocks = [Block(340 * MB, 1.64, 3.74) for _ in range(20)]
+    free = plan_blocks(blocks, d2h_gbs=57, h2d_gbs=55.5, device_budget_bytes=8 * 340 * MB, interference=0.0)
+    # without an interference term the cheapest plan in memory wins among the stall-free ones
+    assert free.est_stall_ms < 0.5 and "".join("R" if d == Decision.RESIDENT else "O" for d in free.decisions).endswith("RRRR")
+    assert free.decisions.count(Decision.RESIDENT) < 8
+    costed = plan_blocks(blocks, d2h_gbs=57, h2d_gbs=55.5, device_budget_bytes=8 * 340 * MB, interference=0.1)
+    assert costed.decisions.count(Decision.RESIDENT) == 8 and costed.decisions[:12] == [Decision.OFFLOAD_INT8] * 12
+    assert 0 < costed.est_interference_ms < 10
+    all_res = plan_blocks(blocks, d2h_gbs=57, h2d_gbs=55.5, device_budget_bytes=10 ** 12)
+    assert set(all_res.decisions) == {Decision.RESIDENT} and all_res.link_bytes == 0
+    none = plan_blocks(blocks, d2h_gbs=57, h2d_gbs=55.5, device_budget_bytes=0, offload=Decision.OFFLOAD_BF16)
+    assert Decision.RESIDENT not in none.decisions and (Decision.RECOMPUTE in none.decisions)
