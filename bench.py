@@ -167,6 +167,26 @@ def verify_against_oracle(torch, lib, x, codec: str) -> bool:
             and np.array_equal(out.view(torch.int16).cpu().numpy().view(np.uint16), wo))
 
 
+def plain_copy_rates(torch, lib, dev, barrier):
+    """(D2H GB/s, H2D GB/s) of a plain 1 GiB pinned cudaMemcpyAsync on this replica, started together with the others."""
+    nb = 1 << 30
+    d = torch.empty(nb, dtype=torch.uint8, device=dev)
+    h = torch.empty(nb, dtype=torch.uint8).pin_memory()
+    st = torch.cuda.current_stream()
+    rates = []
+    for kind, dst, src in ((2, h, d), (1, d, h)):
+        lib.flame_cuda_memcpy_async(dst.data_ptr(), src.data_ptr(), nb, kind, st.cuda_stream)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(2):
+            lib.flame_cuda_memcpy_async(dst.data_ptr(), src.data_ptr(), nb, kind, st.cuda_stream)
+        e1.record(st)
+        torch.cuda.synchronize()
+        rates.append(2 * nb / (e0.elapsed_time(e1) * 1e-3) * 1e-9)
+    return rates
+
+
 def cpu_leg(seconds_target: float = 12.0, codec_name: str = "int8"):
     """CPU oracle pack+unpack on all host threads over a bounded sample of the workload. Returns (GB/s bf16-equiv, cores, sample)."""
     import numpy as np
@@ -527,10 +547,21 @@ def main():
             pool.pull_into(h, d)          # the compute stream waits for each restore
         a2.record(stream)
         torch.cuda.synchronize()
-        link = {"bound_gbs": PCIE_GEN5_X16_GBS, "d2h_gbs": round(d2h_b / d2h_s * 1e-9, 2),
-                "h2d_gbs": round(h2d_b / (a1.elapsed_time(a2) * 1e-3) * 1e-9, 2)}
+        d2h_all = replicas.gather_over_ranks(d2h_b / d2h_s * 1e-9, world, dev)
+        h2d_all = replicas.gather_over_ranks(h2d_b / (a1.elapsed_time(a2) * 1e-3) * 1e-9, world, dev)
+        # the practical ceiling at this replica count: plain 1 GiB pinned copies, all replicas at the same moment
+        plain = plain_copy_rates(torch, lib, dev, barrier)
+        plain_d2h = replicas.gather_over_ranks(plain[0], world, dev)
+        plain_h2d = replicas.gather_over_ranks(plain[1], world, dev)
+        link = {"bound_gbs": PCIE_GEN5_X16_GBS, "d2h_gbs": round(min(d2h_all), 2), "h2d_gbs": round(min(h2d_all), 2),
+                "d2h_gbs_per_replica": [round(v, 1) for v in d2h_all], "h2d_gbs_per_replica": [round(v, 1) for v in h2d_all],
+                "plain_copy_d2h_gbs_per_replica": [round(v, 1) for v in plain_d2h],
+                "plain_copy_h2d_gbs_per_replica": [round(v, 1) for v in plain_h2d],
+                "note": "d2h_gbs / h2d_gbs are the slowest replica's; plain_copy_* is cudaMemcpyAsync of 1 GiB from all replicas at once"}
         link["d2h_frac_of_bound"] = round(link["d2h_gbs"] / PCIE_GEN5_X16_GBS, 3)
         link["h2d_frac_of_bound"] = round(link["h2d_gbs"] / PCIE_GEN5_X16_GBS, 3)
+        link["d2h_frac_of_plain_copy"] = round(min(a / b for a, b in zip(d2h_all, plain_d2h)), 3)
+        link["h2d_frac_of_plain_copy"] = round(min(a / b for a, b in zip(h2d_all, plain_h2d)), 3)
         pool.clear()
         e2e_value = world * 2 * step_bytes / (e2e_ms * 1e-3) * 1e-9
         e2e = {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": int(h2d_b), "d2h_bytes_per_step": int(d2h_b),

@@ -64,3 +64,16 @@ def aggregate_gbs(bytes_per_rank: float, world: int, slowest_ms: float, device=N
     """Whole-job GB/s: bytes all replicas moved divided by the slowest replica's time."""
     total = sum_over_ranks(bytes_per_rank, world, device)
     return total / (slowest_ms * 1e-3) * 1e-9
+
+
+def gather_over_ranks(value: float, world: int, device=None) -> list:
+    """The same scalar from every rank, in rank order (for per-replica link rates)."""
+    if world == 1:
+        return [value]
+    import torch
+    import torch.distributed as dist
+
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    out = [torch.zeros_like(t) for _ in range(world)]
+    dist.all_gather(out, t)
+    return [float(o.item()) for o in out]
