@@ -130,10 +130,25 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons), "samples": len(sm)}
 
 
-def make_workload(torch, dev, seed: int, blocks: int = BLOCKS):
-    """The saved activations of one step: N(0,1) with 0.1 % of entries replaced by +-U(20,60), BF16."""
+C4_TENSORS, C4_SHAPE = 200, (8, 4096, 3072)  # 200 x 201.3 MB = 40.27 GB of BF16 per GPU per step
+
+
+def make_workload(torch, dev, seed: int, blocks: int = BLOCKS, kind: str = "dit"):
+    """The saved activations of one step: N(0,1) with 0.1 % of entries replaced by +-U(20,60), BF16.
+
+    kind "dit": 20 blocks x the five saved tensors of a DiT block.  kind "c4": the 40 GB-per-GPU case, 200 tensors
+    of [8,4096,3072] (25 distinct ones, each used 8 times: the bytes moved are what matters here)."""
     g = torch.Generator(device=dev).manual_seed(seed)
     tensors = []
+    if kind == "c4":
+        distinct = []
+        for _ in range(25):
+            x = torch.randn(C4_SHAPE, device=dev, dtype=torch.float32, generator=g)
+            mask = torch.rand(C4_SHAPE, device=dev, generator=g) < 1e-3
+            x = torch.where(mask, x.sign() * (20.0 + 40.0 * torch.rand(C4_SHAPE, device=dev, generator=g)), x)
+            distinct.append(x.to(torch.bfloat16).contiguous())
+            del x, mask
+        return [distinct[i % 25] for i in range(C4_TENSORS)]
     for _ in range(blocks):
         for last in BLOCK_SAVED:
             x = torch.randn(1, TOKENS, last, device=dev, dtype=torch.float32, generator=g)
@@ -236,6 +251,10 @@ def run_reference_arm(args):
 
 
 def workload_config(args, world):
+    if getattr(args, "workload", "dit") == "c4":
+        return {"workload": f"{C4_TENSORS} x {list(C4_SHAPE)} BF16 per GPU per step = {C4_TENSORS * 8 * 4096 * 3072 * 2 / 1e9:.2f} GB; offload all, restore all in reverse",
+                "codec": args.codec + ("-b128" if args.codec != "none" else ""), "chunk_bytes": args.chunk_mb << 20, "tile_chunks": args.tile_chunks,
+                "l2": "inputs larger than L2", "replicas": world, "parallelism": f"dp{world} independent replicas, no collective"}
     return {"workload": f"DiT saved activations: {BLOCKS} blocks x [norm1 3072, QKV 9216, attn 3072, norm2 3072, gate+up 18432] x {TOKENS} tokens, BF16, "
                         f"{BLOCKS * sum(BLOCK_SAVED) * TOKENS * 2 / 1e9:.2f} GB per step per GPU; offload all in forward order, restore all in reverse",
             "codec": args.codec + ("-b128" if args.codec != "none" else ""), "chunk_bytes": args.chunk_mb << 20, "tile_chunks": args.tile_chunks,
@@ -391,6 +410,8 @@ def main():
     ap.add_argument("--mode", choices=["bench", "sweep", "interference"], default="bench",
                     help="sweep: 1 MB..4 GB single tensor x codec x chunk size; interference: copies against HBM-bound kernels")
     ap.add_argument("--sweep-max-mb", type=int, default=4096)
+    ap.add_argument("--workload", choices=["dit", "c4"], default="dit",
+                    help="c4: 200 x [8,4096,3072] BF16 = 40 GB per GPU per step (the replica-contention case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
 
@@ -433,7 +454,7 @@ def main():
             dist.destroy_process_group()
         return
 
-    tensors = make_workload(torch, dev, seed=replicas.workload_seed(rank), blocks=args.blocks)
+    tensors = make_workload(torch, dev, seed=replicas.workload_seed(rank), blocks=args.blocks, kind=args.workload)
     step_bytes = sum(t.numel() * 2 for t in tensors)
     step_elems = sum(t.numel() for t in tensors)
     max_bytes = max(t.numel() * 2 for t in tensors)

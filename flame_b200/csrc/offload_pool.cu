@@ -27,6 +27,7 @@
 #include <cctype>
 #include <chrono>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <thread>
@@ -92,6 +93,13 @@ void set_preferred_node(int node) {
 #else
   (void)node;
 #endif
+}
+
+// FLAME_OFFLOAD_TRACE=1: one line per push / pull on stderr (the reference traces with env-gated
+// eprintln!, e.g. FLAME_PROFILE and FLAME_COPY_TRACE, src/autograd.rs:1086-1089, src/staging.rs:382-415).
+bool trace_on() {
+  static const bool on = [] { const char* e = getenv("FLAME_OFFLOAD_TRACE"); return e && *e && *e != '0'; }();
+  return on;
 }
 
 int gpu_numa_node(int device) {
@@ -533,6 +541,9 @@ FlameOffloadStatus flame_offload_pool_push(FlameOffloadPool* p, const void* src,
     return FLAME_OFFLOAD_ERR_CUDA;
   }
   s.state = SlotState::Pushed;
+  if (trace_on())
+    fprintf(stderr, "[flame_offload] push slot=%zu epoch=%llu numel=%zu dtype=%d bytes=%zu stored=%llu chunks=%zu free_chunks=%zu\n", slot,
+            (unsigned long long)p->epoch, numel, dtype, bytes, (unsigned long long)s.stored_bytes, nchunks, p->free_chunks.size());
   p->stats.pushes++;
   p->stats.bytes_logical_out += bytes;
   p->stats.host_chunks_free = p->free_chunks.size();
@@ -554,6 +565,9 @@ FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* p, FlameOffloa
   cudaError_t e = enqueue_pull(*p, s, static_cast<uint8_t*>(dst), (cudaStream_t)compute_stream, flags);
   if (e != cudaSuccess) return FLAME_OFFLOAD_ERR_CUDA;  // slot stays Pushed (src/activation_offload.rs:704-711)
   s.state = SlotState::Idle;
+  if (trace_on())
+    fprintf(stderr, "[flame_offload] pull slot=%llu bytes=%llu chunks=%zu deferred_wait=%u\n", (unsigned long long)h.slot,
+            (unsigned long long)s.bytes, s.chunks.size(), flags & FLAME_OFFLOAD_PULL_DEFER_WAIT);
   p->release_chunks(s, (int32_t)h.slot);
   p->free_stack.push_back(h.slot);
   p->stats.pulls++;

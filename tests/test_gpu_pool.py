@@ -142,6 +142,30 @@ def test_stored_bytes_and_round_trip(cuda_device, mode, n, chunk):
     pool.close()
 
 
+@pytest.mark.parametrize("mode", [INT8B, NONE])
+def test_config1_tensor_one_round_trip_through_the_pool(cuda_device, mode):
+    """[1,4096,3072] BF16, N(0,1) with 0.1 % +-U(20,60) outliers, seed 0: what lands in pinned memory is the oracle's
+    packing, what comes back is the oracle's dequantisation (int8) or the source bit for bit (uncompressed)."""
+    bits = synthetic.normal_with_outliers(4096 * 3072, 0)
+    x = G.to_dev(bits, cuda_device).view(1, 4096, 3072)
+    pool = ActivationOffloadPool(cuda_device, 1, bits.size * 2, mode, chunk_bytes=8 << 20)
+    h = pool.push(x)
+    codes, scales = pool.read_slot(h)
+    y = pool.pull(h)
+    torch.cuda.synchronize()
+    assert tuple(y.shape) == (1, 4096, 3072)
+    if mode == INT8B:
+        wc, ws = capi.quant_int8_b128(bits)
+        assert np.array_equal(codes, wc.view(np.uint8)) and np.array_equal(scales.view(np.uint32), ws.view(np.uint32))
+        assert np.array_equal(G.bits_of(y).reshape(-1), capi.dequant_int8_b128(wc, ws))
+        err = (y.float() - x.float()).abs().view(-1, 128).amax(dim=1)
+        assert bool((err <= torch.from_numpy(ws).to(cuda_device)).all())   # |err| <= absmax/127 per block
+        assert pool.slot_bytes() == 25165824 and pool.stats()["bytes_link_out"] == 12976128
+    else:
+        assert np.array_equal(codes.view(np.uint16), bits) and np.array_equal(G.bits_of(y).reshape(-1), bits)
+    pool.close()
+
+
 def test_pull_into_deferred_wait_and_source_release(cuda_device):
     n = 1 << 20
     bits = synthetic.normal(n, 1)
