@@ -118,6 +118,15 @@ class _Entry:
         self.restored = None
         self.waited = False
 
+    def __del__(self):
+        # The graph was dropped without a backward pass (an evaluation step, an exception): the
+        # slot must not stay Pushed for ever.
+        if self.restored is None:
+            try:
+                self.block.pool.discard(self.handle)
+            except Exception:
+                pass
+
 
 class _View:
     """A saved tensor that is a reshaped and/or permuted view of an offloaded entry's flat memory."""

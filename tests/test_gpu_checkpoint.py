@@ -93,6 +93,25 @@ def test_pool_exhaustion_falls_back_to_recompute(cuda_device, model_and_input, c
     assert pool.in_flight() == 0
 
 
+def test_a_graph_dropped_without_backward_gives_its_slots_back(cuda_device, model_and_input):
+    model, x = model_and_input
+    pool = ActivationOffloadPool(cuda_device, 64, 2 * 1024 * 2048 * 2 * 2, OffloadCompression.INT8_B128, chunk_bytes=1 << 20)
+    ckpt.set_activation_offload_pool(pool)
+    y = x.clone().requires_grad_(True)
+    for blk in model:
+        y = ckpt.checkpoint_offload([y], blk, min_bytes=1 << 12)
+    assert pool.in_flight() > 0
+    del y                      # no backward: the autograd graph and its packed entries die here
+    import gc
+    gc.collect()
+    assert pool.in_flight() == 0
+    st = pool.stats()
+    assert st["host_chunks_free"] == st["host_chunks_total"]
+    want = _grads(model, x, ["resident"] * 4)       # and the pool still works
+    got = _grads(model, x, ["offload"] * 4)
+    assert all((a.float() - b.float()).norm() / a.float().norm().clamp_min(1e-12) < 0.05 for a, b in zip(want, got))
+
+
 def test_without_a_pool_checkpoint_offload_is_checkpoint(cuda_device, model_and_input):
     model, x = model_and_input
     ckpt.clear_activation_offload_pool()

@@ -76,6 +76,23 @@ def test_unaligned_pointers_take_the_generic_kernels(cuda_device, n):
     assert np.array_equal(G.bits_of(out), capi.dequant_int8_b128(wc, ws))
 
 
+def test_random_sizes_alignments_and_magnitudes(cuda_device):
+    """Seeded fuzz: ragged sizes, odd pointer offsets, block magnitudes spread over the whole BF16 range."""
+    rng = np.random.default_rng(12345)
+    for trial in range(40):
+        n = int(rng.choice([rng.integers(1, 300), rng.integers(300, 20000), rng.integers(20000, 400000)]))
+        bits = synthetic.normal_with_outliers(n, seed=500 + trial)
+        # scale every 128-block by a random power of two between 2^-60 and 2^60, flip some blocks to zero
+        expo = rng.integers(-60, 61, size=(n + 127) // 128)
+        f = synthetic.bf16_bits_to_f32(bits) * np.repeat(np.exp2(expo.astype(np.float64)), 128)[:n].astype(np.float32)
+        f[np.repeat(rng.random((n + 127) // 128) < 0.05, 128)[:n]] = 0.0
+        bits = synthetic.f32_to_bf16_bits(f.astype(np.float32))
+        offs = dict(in_offset=int(rng.integers(0, 3)) * int(rng.integers(0, 2)), code_offset=int(rng.integers(0, 4)) * int(rng.integers(0, 2)),
+                    scale_offset=int(rng.integers(0, 2)))
+        _check_int8(bits, cuda_device, **dict(offs))
+        _check_fp8(bits, cuda_device, **dict(offs))
+
+
 def test_every_finite_bf16_value(cuda_device):
     """All 65,280 finite BF16 patterns, in blocks that mix magnitudes and in blocks of similar magnitude."""
     vals = synthetic.edge_values()

@@ -178,3 +178,23 @@ def test_int8_kernel_quotient_shortcut_is_exact(tmp_path):
     assert r.returncode == 0, r.stdout + r.stderr
     checked, bad = map(int, r.stdout.split())
     assert checked > 10_000_000 and bad == 0
+
+
+def test_restatements_agree_on_random_magnitude_spread():
+    """C and numpy restatements on blocks whose magnitudes span the BF16 range (seeded)."""
+    rng = np.random.default_rng(7)
+    for trial in range(10):
+        n = int(rng.integers(1, 50000))
+        bits = synthetic.normal_with_outliers(n, seed=900 + trial)
+        expo = rng.integers(-100, 101, size=(n + 127) // 128)
+        with np.errstate(all="ignore"):
+            f = synthetic.bf16_bits_to_f32(bits).astype(np.float64) * np.repeat(np.exp2(expo.astype(np.float64)), 128)[:n]
+        bits = synthetic.f32_to_bf16_bits(np.clip(f, -3e38, 3e38).astype(np.float32))
+        c8, s8 = capi.quant_int8_b128(bits)
+        n8, ns8 = codec_np.quant_int8_b128(bits)
+        assert np.array_equal(c8, n8) and np.array_equal(s8.view(np.uint32), ns8.view(np.uint32))
+        cf, sf = capi.quant_fp8_b128(bits)
+        nf, nsf = codec_np.quant_fp8_b128(bits)
+        assert np.array_equal(cf, nf) and np.array_equal(sf.view(np.uint32), nsf.view(np.uint32))
+        assert np.array_equal(capi.dequant_fp8_b128(cf, sf), codec_np.dequant_fp8_b128(cf, sf))
+        assert np.array_equal(capi.dequant_int8_b128(c8, s8), codec_np.dequant_int8_b128(c8, s8))
