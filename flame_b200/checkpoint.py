@@ -156,7 +156,10 @@ class _Block:
         # Only BF16 activations that take part in the gradient are offloaded; weights, non-BF16
         # tensors and small tensors stay resident (autograd.rs:1721-1739).
         if self.failed or not offloadable(t, self.min_bytes):
-            return t
+            # A tensor that stays resident is kept detached: autograd hands the hook tensors with their
+            # grad_fn, and a saved OUTPUT held that way (attention's log-sum-exp, a norm's 1/rms) would keep
+            # its own node alive for ever if the graph is dropped without a backward pass.
+            return t.detach() if t.grad_fn is not None else t
         perm = dense_permutation(t)
         inverse = tuple(perm.index(d) for d in range(t.dim()))
         base = t.permute(perm)  # contiguous view of the same memory
@@ -172,7 +175,7 @@ class _Block:
             log.warning("checkpoint_offload: pool push failed (%s), falling back to recompute; %d handles already pushed",
                         exc, len(self.entries))
             self.failed = True
-            return t
+            return t.detach() if t.grad_fn is not None else t
         e = _Entry(h, (t.numel(),), t.dtype, self)
         self.entries.append(weakref.ref(e))
         self._by_key[key] = e
