@@ -211,6 +211,60 @@ def test_many_tensors_reverse_order_with_slot_and_chunk_reuse(cuda_device):
     assert st["host_chunks_free"] == st["host_chunks_total"]
 
 
+@pytest.mark.parametrize("mode", [INT8B, FP8B, NONE])
+def test_random_interleaving_of_pushes_and_pulls(cuda_device, mode):
+    """Seeded random schedule: pushes and pulls in any order (not only LIFO), deferred waits, a two-tile staging
+    ring, chunks far smaller than the tensors, a pinned slab that is nearly full, while the compute stream is kept
+    busy overwriting freed sources.  Every restore must equal the oracle's result for its own tensor."""
+    rng = np.random.default_rng(2024)
+    sizes = [int(v) for v in rng.integers(1000, 600000, size=24)]
+    pool = ActivationOffloadPool(cuda_device, 8, 2 * max(sizes), mode, chunk_bytes=64 << 10, staging_tiles=2, tile_chunks=3,
+                                 host_budget_bytes=ActivationOffloadPool.host_bytes_needed([2 * s for s in sorted(sizes)[-6:]], mode, 64 << 10))
+    want = {}
+    live = {}      # handle -> index
+    pending = []   # (dst, index, slot, deferred)
+    scratch = torch.empty(1 << 22, dtype=torch.bfloat16, device=cuda_device)
+    next_i = 0
+    for step in range(200):
+        do_push = next_i < len(sizes) and (not live or rng.random() < 0.55)
+        if do_push:
+            n = sizes[next_i]
+            bits = synthetic.normal_with_outliers(n, seed=3000 + next_i)
+            x = G.to_dev(bits, cuda_device)
+            try:
+                h = pool.push(x)
+            except InvalidOperation:
+                do_push = False        # slab or slots full: pull something instead
+            else:
+                if mode == INT8B:
+                    want[next_i] = capi.dequant_int8_b128(*capi.quant_int8_b128(bits))
+                elif mode == FP8B:
+                    want[next_i] = capi.dequant_fp8_b128(*capi.quant_fp8_b128(bits))
+                else:
+                    want[next_i] = bits
+                live[h] = next_i
+                next_i += 1
+                del x
+                scratch.normal_()      # the allocator may hand the freed source to this kernel
+        if not do_push and live:
+            h = list(live)[int(rng.integers(0, len(live)))]
+            i = live.pop(h)
+            dst = torch.full((sizes[i],), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+            deferred = bool(rng.random() < 0.5)
+            pool.pull_into(h, dst, defer_wait=deferred)
+            pending.append((dst, i, h.slot, deferred))
+        if not live and next_i >= len(sizes):
+            break
+    for dst, i, slot, deferred in pending:
+        if deferred:
+            pool.wait_ready(slot)
+    torch.cuda.synchronize()
+    assert len(pending) == len(sizes)
+    for dst, i, _, _ in pending:
+        assert np.array_equal(G.bits_of(dst), want[i]), i
+    assert pool.in_flight() == 0
+
+
 def test_host_budget_smaller_than_slots_rejects_then_recovers(cuda_device):
     n = 1 << 18
     x = torch.randn(n, device=cuda_device).to(torch.bfloat16)
