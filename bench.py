@@ -225,6 +225,110 @@ def cpu_leg(seconds_target: float = 12.0, codec_name: str = "int8"):
     return gbs, cores, f"{reps} x one [1,{TOKENS},{HIDDEN}] BF16 tensor ({2 * n / 1e6:.1f} MB), quantise+pack then unpack+dequantise, {cores} threads, {dt:.1f} s", dt / reps
 
 
+def reference_gpu_path(args):
+    """The reference's GPU path for the same workload, as far as it can be run here: its three CUDA files of this
+    path (src/cuda/fp8_quant.cu, fp8_dequant.cu, pinned_host.cu) compiled unmodified into oracle/_ref, driven in the
+    order its pool drives them (src/activation_offload.rs:465-611 push, :619-731 pull): one pinned buffer and one
+    device staging buffer per slot, ONE transfer stream, whole-tensor copies, a fixed FP8 scale of 8/448, a fresh
+    destination per pull, the compute stream waiting on each pull's ready event.  The Rust host code itself cannot
+    be built on this image, so the sequence is issued from this function; none of this library's code is on it.
+    Returns None when the compiled reference or a GPU is absent."""
+    try:
+        import torch
+        from oracle import capi
+        ref = capi.load_ref_cuda()
+        if ref is None or not torch.cuda.is_available():
+            return None
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        tensors = make_workload(torch, dev, seed=0, blocks=args.blocks, kind="dit")
+        step_bytes = sum(t.numel() * 2 for t in tensors)
+        step_elems = sum(t.numel() for t in tensors)
+        max_bytes = max(t.numel() * 2 for t in tensors)
+        compute = torch.cuda.current_stream()
+        transfer = torch.cuda.Stream(dev)
+        tp = transfer.cuda_stream
+        out = {"sources": "src/cuda/fp8_quant.cu, fp8_dequant.cu, pinned_host.cu compiled unmodified (nvcc, sm_100a); push/pull order of "
+                          "src/activation_offload.rs:465-731 issued by bench.py", "unit": UNIT}
+        hbm_peak, _ = measured_peaks()
+        # kernels alone, device-resident, events on the launching stream
+        codes = [torch.empty(t.numel(), dtype=torch.uint8, device=dev) for t in tensors]
+        back = torch.empty(max_bytes // 2, dtype=torch.bfloat16, device=dev)
+        inv, scale = 448.0 / 8.0, 8.0 / 448.0
+        for phase in range(2):
+            e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            e0.record(transfer)
+            for t, c in zip(tensors, codes):
+                assert ref.flame_bf16_to_fp8(t.data_ptr(), c.data_ptr(), inv, t.numel(), tp) == 0
+            e1.record(transfer)
+            for t, c in zip(tensors, codes):
+                assert ref.flame_fp8_to_bf16(c.data_ptr(), back.data_ptr(), scale, t.numel(), tp) == 0
+            e2.record(transfer)
+            torch.cuda.synchronize()
+        alg = 3.0 * step_elems
+        qg, dg = alg / (e0.elapsed_time(e1) * 1e-3) * 1e-9, alg / (e1.elapsed_time(e2) * 1e-3) * 1e-9
+        out["kernels"] = {"bf16_to_fp8_kernel_gbs": round(qg, 1), "fp8_to_bf16_kernel_gbs": round(dg, 1), "alg_bytes_per_elem": 3.0,
+                          "frac_of_hbm": [round(qg / hbm_peak, 3), round(dg / hbm_peak, 3)],
+                          "device_roundtrip_bf16eq_gbs": round(2 * step_bytes / (e0.elapsed_time(e2) * 1e-3) * 1e-9, 1)}
+        del codes, back
+        for mode in ("fp8", "none"):
+            slot_bytes = (max_bytes + 1) // 2 if mode == "fp8" else max_bytes
+            host = [ref.flame_cuda_alloc_pinned_host(slot_bytes, 0) for _ in tensors]       # cudaHostAllocDefault, as the pool does
+            if any(h is None for h in host):
+                for h in host:
+                    if h is not None:
+                        ref.flame_cuda_free_pinned_host(h)
+                out[mode] = {"unavailable": "cudaHostAlloc failed"}
+                continue
+            staging = [torch.empty(slot_bytes, dtype=torch.uint8, device=dev) for _ in tensors] if mode == "fp8" else None
+            done = [torch.cuda.Event() for _ in tensors]
+            ready = [torch.cuda.Event() for _ in tensors]
+
+            def step():
+                for i, t in enumerate(tensors):                      # push
+                    done[i].record(compute)
+                    transfer.wait_event(done[i])
+                    if mode == "fp8":
+                        assert ref.flame_bf16_to_fp8(t.data_ptr(), staging[i].data_ptr(), inv, t.numel(), tp) == 0
+                        assert ref.flame_cuda_memcpy_async(host[i], staging[i].data_ptr(), t.numel(), 2, tp) == 0
+                    else:
+                        assert ref.flame_cuda_memcpy_async(host[i], t.data_ptr(), t.numel() * 2, 2, tp) == 0
+                for i in reversed(range(len(tensors))):             # pull, last pushed first
+                    t = tensors[i]
+                    fresh = torch.empty_like(t)
+                    if mode == "fp8":
+                        assert ref.flame_cuda_memcpy_async(staging[i].data_ptr(), host[i], t.numel(), 1, tp) == 0
+                        assert ref.flame_fp8_to_bf16(staging[i].data_ptr(), fresh.data_ptr(), scale, t.numel(), tp) == 0
+                    else:
+                        assert ref.flame_cuda_memcpy_async(fresh.data_ptr(), host[i], t.numel() * 2, 1, tp) == 0
+                    ready[i].record(transfer)
+                    compute.wait_event(ready[i])
+                    fresh.record_stream(transfer)
+
+            for _ in range(max(1, min(args.warmup, 3))):
+                step()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k = max(1, min(args.steps, 5))
+            a.record(compute)
+            for _ in range(k):
+                step()
+            b.record(compute)
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / k
+            link_bytes = step_elems if mode == "fp8" else step_bytes
+            out[mode] = {"e2e_gbs": round(2 * step_bytes / (ms * 1e-3) * 1e-9, 2), "ms_per_step": round(ms, 3), "steps": k,
+                         "d2h_bytes_per_step": int(link_bytes), "h2d_bytes_per_step": int(link_bytes),
+                         "pinned_bytes": int(slot_bytes * len(tensors)), "device_staging_bytes": int(slot_bytes * len(tensors)) if mode == "fp8" else 0}
+            for h in host:
+                ref.flame_cuda_free_pinned_host(h)
+            del staging
+            torch.cuda.empty_cache()
+        return out
+    except Exception as exc:  # the CPU line below stands on its own
+        return {"error": f"{type(exc).__name__}: {exc}"}
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -247,6 +351,10 @@ def run_reference_arm(args):
         "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference crate is GPU-only Rust with no CPU quantise/pack path; this arm times the C oracle (a port of its formulas) on the host cores",
     }
+    if args.gpus == 1 and not args.no_ref_gpu:
+        gpu = reference_gpu_path(args)
+        if gpu is not None:
+            line["reference_gpu_path"] = gpu
     print(json.dumps(line), flush=True)
 
 
@@ -406,6 +514,7 @@ def main():
     ap.add_argument("--blocks", type=int, default=BLOCKS, help="fewer blocks = smaller case (profiling only)")
     ap.add_argument("--no-dit", action="store_true", help="skip the DiT training-step overhead measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-ref-gpu", action="store_true", help="--impl reference: skip timing the reference's own compiled CUDA files")
     ap.add_argument("--only", choices=["all", "value", "e2e"], default="all", help="profiling: run only one timed region")
     ap.add_argument("--mode", choices=["bench", "sweep", "interference"], default="bench",
                     help="sweep: 1 MB..4 GB single tensor x codec x chunk size; interference: copies against HBM-bound kernels")

@@ -201,6 +201,17 @@ __device__ __forceinline__ uint32_t fp8_encode_ref(float y, float x) {
 // y = x * inv, except that a zero element stays zero even when inv is infinite.
 __device__ __forceinline__ float scaled(float x, float inv) { return x == 0.0f ? x : __fmul_rn(x, inv); }
 __device__ __forceinline__ uint32_t fp8_encode_ref_scaled(float x, float inv) { return fp8_encode_ref(scaled(x, inv), x); }
+// The element-wise entry point keeps the reference's result for the plain product x * inv in every case
+// (src/cuda/fp8_quant.cu:69-70): when the product is NaN (a NaN element, 0 * inf, inf * 0, a NaN inv) none of
+// the reference's comparisons holds, its frexpf leaves the exponent 0 and the mantissa converts to 0: 0x30.
+__device__ __forceinline__ uint32_t fp8_encode_legacy(float x, float inv) {
+  const float y = __fmul_rn(x, inv);
+  return (y != y) ? 0x30u : fp8_encode_ref(y, x);
+}
+template <bool kLegacy>
+__device__ __forceinline__ uint32_t fp8_encode_exact(float x, float inv) {
+  return kLegacy ? fp8_encode_legacy(x, inv) : fp8_encode_ref_scaled(x, inv);
+}
 
 // Fast form of the same encoder for a lane's worth of magnitudes, two at a time,
 // on the conversion hardware.  For 2^-6 <= |y| < 248 the reference rounds the
@@ -212,12 +223,13 @@ __device__ __forceinline__ uint32_t fp8_encode_ref_scaled(float x, float inv) { 
 // NaN, which the converter encodes as 0x7F.  Zero gives 0.  `min_all` collects the
 // smallest magnitude seen, so that the caller can tell whether any lane needs
 // more care (see fp8_encode_lane_ref).
+template <bool kNanPropagates = false>
 __device__ __forceinline__ uint32_t fp8_encode_pair_fast(float ylo_abs, float yhi_abs, __half2& min_all) {
   uint32_t h;
   asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(yhi_abs), "f"(ylo_abs));
   const __half2 hh = *reinterpret_cast<const __half2*>(&h);
   const uint32_t sat = __hge2_mask(hh, __half2half2(__ushort_as_half((unsigned short)0x5BC0)));  // 248.0
-  min_all = __hmin2(min_all, hh);  // a NaN lane is ignored
+  min_all = kNanPropagates ? __hmin2_nan(min_all, hh) : __hmin2(min_all, hh);  // default: a NaN lane is ignored
   const uint32_t h2 = h | 0x00010001u | sat;
   uint16_t c;
   asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(c) : "r"(h2));
@@ -230,13 +242,15 @@ __device__ __forceinline__ uint32_t fp8_encode_pair_fast(float ylo_abs, float yh
 //                  sign = sign bit of x.
 //   zeros present: same codes, but a zero magnitude keeps sign 0 (`val < 0` is false for -0.0).
 //   a magnitude in (0, 2^-6): the reference's float formula decides; the lane is re-encoded exactly.
-template <int N>
+// kLegacy (the element-wise entry point): a NaN element also sends the lane to the exact arm, which
+// gives it the reference's 0x30; the block codecs keep NaN on the fast path (saturation code, sign of x).
+template <int N, bool kLegacy = false>
 __device__ __forceinline__ void fp8_encode_lane_ref(const float (&x)[N], const uint32_t* raw, float inv, uint32_t (&out)[N / 4]) {
   __half2 min_all = __half2half2(__ushort_as_half((unsigned short)0x7BFF));  // 65504
 #pragma unroll
   for (int i = 0; i < N / 4; ++i) {
-    const uint32_t c01 = fp8_encode_pair_fast(__fmul_rn(fabsf(x[4 * i]), inv), __fmul_rn(fabsf(x[4 * i + 1]), inv), min_all);
-    const uint32_t c23 = fp8_encode_pair_fast(__fmul_rn(fabsf(x[4 * i + 2]), inv), __fmul_rn(fabsf(x[4 * i + 3]), inv), min_all);
+    const uint32_t c01 = fp8_encode_pair_fast<kLegacy>(__fmul_rn(fabsf(x[4 * i]), inv), __fmul_rn(fabsf(x[4 * i + 1]), inv), min_all);
+    const uint32_t c23 = fp8_encode_pair_fast<kLegacy>(__fmul_rn(fabsf(x[4 * i + 2]), inv), __fmul_rn(fabsf(x[4 * i + 3]), inv), min_all);
     const uint32_t mag = __byte_perm(c01, c23, 0x5410);
     const uint32_t sgn = __byte_perm(raw[2 * i], raw[2 * i + 1], 0x7531);  // high bytes of the four BF16
     out[i] = (mag & 0x7F7F7F7Fu) | (sgn & 0x80808080u);
@@ -244,13 +258,17 @@ __device__ __forceinline__ void fp8_encode_lane_ref(const float (&x)[N], const u
   // anything below 2^-6 (0x2400 in FP16)?  Zero counts: rare enough to be handled off the fast path.
   // The careful arms unpack the elements again from `raw` so that x[] need not stay in registers
   // across the fast loop.
-  if (__hlt(__hmin(__low2half(min_all), __high2half(min_all)), __ushort_as_half((unsigned short)0x2400))) {
+  const __half thr = __ushort_as_half((unsigned short)0x2400);
+  const bool careful = kLegacy ? !__hge(__hmin_nan(__low2half(min_all), __high2half(min_all)), thr)
+                               : __hlt(__hmin(__low2half(min_all), __high2half(min_all)), thr);
+  if (careful) {
     bool tiny = false;
 #pragma unroll
     for (int i = 0; i < N / 2; ++i) {
       const float lo = bf16lo(raw[i]), hi = bf16hi(raw[i]);
       tiny |= (lo != 0.0f) && (__fmul_rn(fabsf(lo), inv) < 0.015625f);
       tiny |= (hi != 0.0f) && (__fmul_rn(fabsf(hi), inv) < 0.015625f);
+      if (kLegacy) tiny |= (lo != lo) || (hi != hi);
     }
     if (!tiny) {
 #pragma unroll
@@ -261,8 +279,8 @@ __device__ __forceinline__ void fp8_encode_lane_ref(const float (&x)[N], const u
     } else {
 #pragma unroll
       for (int i = 0; i < N / 4; ++i)
-        out[i] = fp8_encode_ref_scaled(bf16lo(raw[2 * i]), inv) | (fp8_encode_ref_scaled(bf16hi(raw[2 * i]), inv) << 8) |
-                 (fp8_encode_ref_scaled(bf16lo(raw[2 * i + 1]), inv) << 16) | (fp8_encode_ref_scaled(bf16hi(raw[2 * i + 1]), inv) << 24);
+        out[i] = fp8_encode_exact<kLegacy>(bf16lo(raw[2 * i]), inv) | (fp8_encode_exact<kLegacy>(bf16hi(raw[2 * i]), inv) << 8) |
+                 (fp8_encode_exact<kLegacy>(bf16lo(raw[2 * i + 1]), inv) << 16) | (fp8_encode_exact<kLegacy>(bf16hi(raw[2 * i + 1]), inv) << 24);
     }
   }
 }
@@ -624,19 +642,19 @@ bf16_to_fp8_vec_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ ou
     unpack16(r, x);
     uint32_t c[4];
     if ((inv_scale > 0.0f) && (inv_scale < 3.0e38f)) {  // the sign of x*inv_scale is the sign of x
-      fp8_encode_lane_ref<kLaneElems>(x, r.v, inv_scale, c);
+      fp8_encode_lane_ref<kLaneElems, true>(x, r.v, inv_scale, c);
     } else {
 #pragma unroll
       for (int i = 0; i < 4; ++i)
-        c[i] = fp8_encode_ref_scaled(x[4 * i], inv_scale) | (fp8_encode_ref_scaled(x[4 * i + 1], inv_scale) << 8) |
-               (fp8_encode_ref_scaled(x[4 * i + 2], inv_scale) << 16) | (fp8_encode_ref_scaled(x[4 * i + 3], inv_scale) << 24);
+        c[i] = fp8_encode_legacy(x[4 * i], inv_scale) | (fp8_encode_legacy(x[4 * i + 1], inv_scale) << 8) |
+               (fp8_encode_legacy(x[4 * i + 2], inv_scale) << 16) | (fp8_encode_legacy(x[4 * i + 3], inv_scale) << 24);
     }
     __stcs(reinterpret_cast<uint4*>(out + v * kLaneElems), make_uint4(c[0], c[1], c[2], c[3]));
   }
   const size_t t0 = nvec * kLaneElems;
   if (blockIdx.x == 0 && threadIdx.x < (unsigned)(n - t0)) {
     const size_t e = t0 + threadIdx.x;
-    out[e] = (uint8_t)fp8_encode_ref_scaled(__uint_as_float((uint32_t)in[e] << 16), inv_scale);
+    out[e] = (uint8_t)fp8_encode_legacy(__uint_as_float((uint32_t)in[e] << 16), inv_scale);
   }
 }
 
@@ -644,7 +662,7 @@ __global__ void __launch_bounds__(kThreads)
 bf16_to_fp8_scalar_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ out, float inv_scale, size_t n) {
   const size_t stride = (size_t)gridDim.x * kThreads;
   for (size_t e = (size_t)blockIdx.x * kThreads + threadIdx.x; e < n; e += stride)
-    out[e] = (uint8_t)fp8_encode_ref_scaled(__uint_as_float((uint32_t)in[e] << 16), inv_scale);
+    out[e] = (uint8_t)fp8_encode_legacy(__uint_as_float((uint32_t)in[e] << 16), inv_scale);
 }
 
 __global__ void __launch_bounds__(kThreads)

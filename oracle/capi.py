@@ -100,6 +100,32 @@ def load_ref_encoder():
     return fn
 
 
+_REF_CUDA = None
+
+
+def load_ref_cuda():
+    """The reference's own CUDA files of this path (src/cuda/fp8_quant.cu, fp8_dequant.cu, pinned_host.cu)
+    compiled unmodified by ``make -C oracle refcuda``, or None when that library was not built.
+
+    Its symbols carry the same names as the shipped library's legacy entry points, so it is opened
+    RTLD_LOCAL and used only through the handle returned here (GPU tests, and the bench's reference-kernel
+    timing)."""
+    global _REF_CUDA
+    so = os.path.join(_HERE, "_ref", "libflame_ref_cuda.so")
+    if not os.path.exists(so):
+        return None
+    if _REF_CUDA is None:
+        lib = C.CDLL(so, mode=os.RTLD_LOCAL | os.RTLD_NOW)
+        vp, sz, u, i, f = C.c_void_p, C.c_size_t, C.c_uint, C.c_int, C.c_float
+        lib.flame_bf16_to_fp8.restype, lib.flame_bf16_to_fp8.argtypes = i, [vp, vp, f, sz, vp]
+        lib.flame_fp8_to_bf16.restype, lib.flame_fp8_to_bf16.argtypes = i, [vp, vp, f, sz, vp]
+        lib.flame_cuda_alloc_pinned_host.restype, lib.flame_cuda_alloc_pinned_host.argtypes = vp, [sz, u]
+        lib.flame_cuda_free_pinned_host.restype, lib.flame_cuda_free_pinned_host.argtypes = i, [vp]
+        lib.flame_cuda_memcpy_async.restype, lib.flame_cuda_memcpy_async.argtypes = i, [vp, vp, sz, i, vp]
+        _REF_CUDA = lib
+    return _REF_CUDA
+
+
 def _p(a: np.ndarray):
     return a.ctypes.data_as(C.c_void_p)
 

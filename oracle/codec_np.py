@@ -41,10 +41,8 @@ def fp8_encode_ref(y) -> np.ndarray:
     sub = np.minimum(np.floor(np.where(small, w, 0)).astype(np.int64), 7)
     c = np.where(small, sub, c)
     s = np.where(y < 0, 0x80, 0)
-    nan = a > 0x7F800000
-    s = np.where(nan, (b >> 24) & 0x80, s)
-    c = np.where(nan, 0x7F, c)
-    return (s | c).astype(np.uint8)
+    nan = a > 0x7F800000   # the reference's arithmetic ends at 0x30 for NaN (see codec_oracle.c, form A)
+    return np.where(nan, 0x30, s | c).astype(np.uint8)
 
 
 def fp8_decode(c) -> np.ndarray:
@@ -55,7 +53,7 @@ def fp8_decode(c) -> np.ndarray:
 
 
 def _fp8_code_of(x, inv) -> np.ndarray:
-    """enc(x*inv); a zero element stays zero when inv is infinite; a NaN result takes x's sign bit."""
+    """Block codecs: enc(x*inv); a zero element stays zero when inv is infinite; a NaN result saturates with x's sign bit."""
     x = np.asarray(x, F32)
     with np.errstate(all="ignore"):
         y = np.where(x == 0, x, (x * inv).astype(F32)).astype(F32)
@@ -118,7 +116,9 @@ def dequant_fp8_b128(codes, scales):
 
 
 def bf16_to_fp8(bits, inv_scale):
-    return _fp8_code_of(bf16_to_f32(bits), F32(inv_scale))
+    """src/cuda/fp8_quant.cu:69-70: the code of the plain product."""
+    with np.errstate(all="ignore"):
+        return fp8_encode_ref((bf16_to_f32(bits) * F32(inv_scale)).astype(F32))
 
 
 def fp8_to_bf16(codes, scale):

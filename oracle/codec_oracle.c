@@ -68,9 +68,13 @@ uint16_t oracle_f32_to_bf16(float f) {
 /* Form A: follows the reference's control flow (frexpf, float mantissa maths). */
 uint8_t oracle_fp8_e4m3_encode_ref(float y) {
     uint8_t s = 0;
-    if (y != y) { /* NaN: undefined in the reference; defined here */
-        return (uint8_t)(((f32_to_bits(y) >> 24) & 0x80u) | 0x7Fu);
-    }
+    /* NaN: every comparison below is false, frexpf leaves the exponent 0 (biased
+     * 6) and the integer conversion of a NaN mantissa yields zero bits, so the
+     * reference's arithmetic ends at 0x30 with no sign.  Stated outright here
+     * because (int)NaN is undefined in C; 0x30 is what the reference's kernel
+     * compiled for sm_100a returns on a B200 and what its encoder compiled for
+     * x86-64 returns. */
+    if (y != y) return 0x30;
     if (y < 0.0f) { s = 0x80; y = -y; }
     if (y > 448.0f) y = 448.0f;
     if (y == 0.0f) return s;
@@ -100,7 +104,7 @@ uint8_t oracle_fp8_e4m3_encode_ref(float y) {
 uint8_t oracle_fp8_e4m3_encode_bits(float y) {
     uint32_t b = f32_to_bits(y);
     uint32_t a = b & 0x7FFFFFFFu;
-    if (a > 0x7F800000u) return (uint8_t)(((b >> 24) & 0x80u) | 0x7Fu);
+    if (a > 0x7F800000u) return 0x30; /* NaN, as form A */
     uint8_t s = (y < 0.0f) ? 0x80 : 0x00; /* -0.0 keeps sign 0, as `val < 0` does */
     if (a == 0) return 0;
     if (a < 0x3C800000u) { /* |y| < 2^-6 */
@@ -147,15 +151,14 @@ uint8_t oracle_fp8_e4m3_encode_ocp(float y) {
 
 /* Sweeps binary32 patterns lo, lo+stride, ... < hi through form B and through
  * `other` (form A, or the reference's own compiled encoder) and counts the
- * patterns on which they disagree; NaN patterns are skipped (undefined in the
- * reference).  first_bad receives the first disagreeing pattern. */
+ * patterns on which they disagree, NaN patterns included.  first_bad receives
+ * the first disagreeing pattern. */
 typedef unsigned char (*oracle_enc_fn)(float);
 uint64_t oracle_fp8_encode_sweep(oracle_enc_fn other, uint64_t lo, uint64_t hi, uint64_t stride, uint32_t* first_bad) {
     uint64_t bad = 0;
     if (stride == 0) stride = 1;
     for (uint64_t b = lo; b < hi; b += stride) {
         uint32_t bits = (uint32_t)b;
-        if ((bits & 0x7FFFFFFFu) > 0x7F800000u) continue;
         float y = bits_to_f32(bits);
         if (oracle_fp8_e4m3_encode_bits(y) != other(y)) {
             if (!bad && first_bad) *first_bad = bits;
@@ -172,10 +175,10 @@ void oracle_fp8_encode_many(const float* y, uint8_t* out, size_t n, int form) {
 
 /* ---- element-wise fixed-scale entry points (legacy mode) ---------------- */
 
-/* code of x scaled by inv.  Two cases the reference leaves undefined are pinned
- * here so that every platform gives the same byte: a zero element stays zero
- * even when inv is infinite (0*inf would be NaN), and a NaN result takes the
- * sign bit of the source element x. */
+/* Block codecs only: code of x scaled by the block's inv.  Two cases are this
+ * library's own definition (the reference has no block codec): a zero element
+ * stays zero even when inv is infinite (0*inf would be NaN), and a NaN result
+ * saturates with the sign bit of the source element x. */
 static inline uint8_t fp8_code_of(float x, float inv, int ocp) {
     float y = (x == 0.0f) ? x : x * inv;
     if (y != y) return (uint8_t)(((f32_to_bits(x) >> 24) & 0x80u) | 0x7Fu);
@@ -183,7 +186,8 @@ static inline uint8_t fp8_code_of(float x, float inv, int ocp) {
 }
 
 void oracle_bf16_to_fp8(const uint16_t* in, uint8_t* out, float inv_scale, size_t n) {
-    for (size_t i = 0; i < n; ++i) out[i] = fp8_code_of(oracle_bf16_to_f32(in[i]), inv_scale, 0);
+    /* src/cuda/fp8_quant.cu:69-70: the plain product, whatever it is (0*inf and NaN included) */
+    for (size_t i = 0; i < n; ++i) out[i] = oracle_fp8_e4m3_encode_bits(oracle_bf16_to_f32(in[i]) * inv_scale);
 }
 
 void oracle_fp8_to_bf16(const uint8_t* in, uint16_t* out, float scale, size_t n) {

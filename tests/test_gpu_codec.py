@@ -245,12 +245,71 @@ def test_elementwise_encoder_against_reference_golden(cuda_device, golden_dir):
         assert lib.flame_bf16_to_fp8(x.data_ptr(), codes.data_ptr(), float(inv), bits.size, None) == 0
         torch.cuda.synchronize()
         assert np.array_equal(codes.cpu().numpy(), g[f"codes_{k}"])
+    # bytes the reference's own kernels wrote on a B200, every BF16 pattern x eleven inverse scales
+    k100 = np.load(os.path.join(golden_dir, "fp8_reference_kernel_sm100.npz"))
+    every = G.to_dev(np.arange(1 << 16, dtype=np.uint16), cuda_device)
+    for k, inv in enumerate(k100["inv_scales"]):
+        codes = torch.empty(1 << 16, dtype=torch.uint8, device=cuda_device)
+        assert lib.flame_bf16_to_fp8(every.data_ptr(), codes.data_ptr(), float(inv), 1 << 16, None) == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(codes.cpu().numpy(), k100["codes"][k]), float(inv)
     dec = np.load(os.path.join(golden_dir, "fp8_reference_decoder.npy"))
     all_codes = torch.arange(256, dtype=torch.int16, device=cuda_device).to(torch.uint8)
     out = torch.empty(256, dtype=torch.bfloat16, device=cuda_device)
     assert lib.flame_fp8_to_bf16(all_codes.data_ptr(), out.data_ptr(), 1.0, 256, None) == 0
     torch.cuda.synchronize()
     assert np.array_equal(out.float().cpu().numpy().view(np.uint32), dec.view(np.uint32))  # every decoded value is a BF16
+
+
+def test_legacy_entry_points_equal_the_reference_kernels_on_this_gpu(cuda_device):
+    """flame_bf16_to_fp8 / flame_fp8_to_bf16 against the reference's own src/cuda/fp8_quant.cu and
+    fp8_dequant.cu, compiled unmodified and run on the same device buffers: every BF16 bit pattern
+    (NaN and infinity included) at several scales, and every code at several scales."""
+    ref = capi.load_ref_cuda()
+    if ref is None:
+        pytest.skip("oracle/_ref/libflame_ref_cuda.so was not built (reference checkout absent at build time)")
+    lib = _lib.lib()
+    bits = np.arange(1 << 16, dtype=np.uint16)
+    x = G.to_dev(bits, cuda_device)
+    sp = G.stream_ptr(cuda_device)
+    scales = [np.float32(8.0) / np.float32(448.0), np.float32(1.0), np.float32(0.37) / np.float32(448.0),
+              np.float32(3.0e-5), np.float32(1.0e30), np.float32(1.0e-30)]
+    invs = [np.float32(1.0) / sc for sc in scales] + [np.float32(v) for v in (0.0, np.inf, np.nan, -2.0, -np.inf)]
+    for inv in invs:
+        mine = torch.empty(bits.size, dtype=torch.uint8, device=cuda_device)
+        theirs = torch.empty_like(mine)
+        assert lib.flame_bf16_to_fp8(x.data_ptr(), mine.data_ptr(), float(inv), bits.size, sp) == 0
+        assert ref.flame_bf16_to_fp8(x.data_ptr(), theirs.data_ptr(), float(inv), bits.size, sp) == 0
+        torch.cuda.synchronize()
+        a, b = mine.cpu().numpy(), theirs.cpu().numpy()
+        assert np.array_equal(a, b), (float(inv), bits[a != b][:8], a[a != b][:8], b[a != b][:8])
+        assert np.array_equal(a, capi.bf16_to_fp8(bits, inv)), float(inv)       # and the CPU oracle says the same
+        # an unaligned copy of the same values takes this library's scalar kernel
+        xu = G.to_dev(bits, cuda_device, 1)
+        mu = torch.empty(bits.size + 1, dtype=torch.uint8, device=cuda_device)[1:]
+        assert lib.flame_bf16_to_fp8(xu.data_ptr(), mu.data_ptr(), float(inv), bits.size, sp) == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(mu.cpu().numpy(), b), float(inv)
+    all_codes = torch.arange(256, dtype=torch.int16, device=cuda_device).to(torch.uint8)
+    for scale in scales + [np.float32(0.0)]:
+        mine = torch.empty(256, dtype=torch.bfloat16, device=cuda_device)
+        theirs = torch.empty_like(mine)
+        assert lib.flame_fp8_to_bf16(all_codes.data_ptr(), mine.data_ptr(), float(scale), 256, sp) == 0
+        assert ref.flame_fp8_to_bf16(all_codes.data_ptr(), theirs.data_ptr(), float(scale), 256, sp) == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(G.bits_of(mine), G.bits_of(theirs)), float(scale)
+    # a tensor of the pool's size class, through both libraries: same bytes out, same BF16 back
+    vals = synthetic.normal_with_outliers(1 << 22, seed=3)
+    xv = G.to_dev(vals, cuda_device)
+    inv = np.float32(448.0) / np.float32(8.0)
+    c1 = torch.empty(vals.size, dtype=torch.uint8, device=cuda_device); c2 = torch.empty_like(c1)
+    assert lib.flame_bf16_to_fp8(xv.data_ptr(), c1.data_ptr(), float(inv), vals.size, sp) == 0
+    assert ref.flame_bf16_to_fp8(xv.data_ptr(), c2.data_ptr(), float(inv), vals.size, sp) == 0
+    o1 = torch.empty(vals.size, dtype=torch.bfloat16, device=cuda_device); o2 = torch.empty_like(o1)
+    assert lib.flame_fp8_to_bf16(c1.data_ptr(), o1.data_ptr(), float(1 / inv), vals.size, sp) == 0
+    assert ref.flame_fp8_to_bf16(c2.data_ptr(), o2.data_ptr(), float(1 / inv), vals.size, sp) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(c1, c2) and torch.equal(o1.view(torch.int16), o2.view(torch.int16))
 
 
 # ---- size-independent properties at benchmark sizes -------------------------------------------

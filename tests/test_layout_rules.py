@@ -26,7 +26,10 @@ def test_the_package_never_touches_the_oracle():
 def test_bench_uses_the_oracle_only_as_checker_and_cpu_baseline():
     text = open(os.path.join(ROOT, "bench.py")).read()
     users = {m.group(1) for m in re.finditer(r"def (\w+)\([^)]*\):(?:(?!\ndef ).)*?from oracle import", text, re.S)}
-    assert users <= {"verify_against_oracle", "cpu_leg"}, users
+    assert users <= {"verify_against_oracle", "cpu_leg", "reference_gpu_path"}, users
+    # the compiled reference files are timed by the --impl reference arm only, never by this library's arm
+    callers = {m.group(1) for m in re.finditer(r"def (\w+)\([^)]*\):(?:(?!\ndef ).)*?reference_gpu_path\(", text, re.S)}
+    assert callers == {"run_reference_arm"}, callers
 
 
 def test_nothing_committed_reads_the_working_folder_or_the_reference_checkout():

@@ -30,6 +30,26 @@ def test_encoder_matches_reference_golden(golden_dir):
         assert np.array_equal(capi.bf16_to_fp8(synthetic.edge_values(), inv), want)
 
 
+def test_oracle_equals_the_reference_kernels_run_on_a_b200(golden_dir):
+    """fp8_reference_kernel_sm100.npz: bytes written by the reference's own flame_bf16_to_fp8 / flame_fp8_to_bf16,
+    compiled unmodified and run on a B200, for every BF16 pattern (NaN, infinity) and every code, at ordinary,
+    extreme, zero, infinite, NaN and negative scales."""
+    g = _golden(golden_dir, "fp8_reference_kernel_sm100.npz")
+    bits = np.arange(1 << 16, dtype=np.uint16)
+    for k, inv in enumerate(g["inv_scales"]):
+        want = g["codes"][k]
+        assert np.array_equal(capi.bf16_to_fp8(bits, inv), want), float(inv)
+        assert np.array_equal(codec_np.bf16_to_fp8(bits, inv), want), float(inv)
+    codes = np.arange(256, dtype=np.uint8)
+    for k, sc in enumerate(g["dec_scales"]):
+        want = g["decoded_bf16_bits"][k]
+        nan = (want & 0x7FFF) > 0x7F80                       # 0 * inf: a NaN, whose payload bits are not compared
+        got = capi.fp8_to_bf16(codes, sc)
+        assert np.array_equal(got[~nan], want[~nan]) and np.all((got[nan] & 0x7FFF) > 0x7F80), float(sc)
+        got = codec_np.fp8_to_bf16(codes, sc)
+        assert np.array_equal(got[~nan], want[~nan]) and np.all((got[nan] & 0x7FFF) > 0x7F80), float(sc)
+
+
 def test_decoder_matches_reference_golden(golden_dir):
     want = _golden(golden_dir, "fp8_reference_decoder.npy")
     lib = capi.load()
