@@ -502,6 +502,56 @@ def run_interference(args, torch, lib, dev):
             print(json.dumps(row), flush=True)
 
 
+def run_weights(args, torch, dev):
+    """Block weights streamed host -> device through the pool (BlockOffloader): every block once forward, once backward."""
+    from flame_b200 import BlockOffloader, OffloadCompression
+
+    mode = {"int8": OffloadCompression.INT8_B128, "fp8": OffloadCompression.FP8_B128, "none": OffloadCompression.NONE}[args.codec]
+    g = torch.Generator(device=dev).manual_seed(0)
+    shapes = {"attn.qkv.weight": (3 * HIDDEN, HIDDEN), "attn.out.weight": (HIDDEN, HIDDEN),
+              "mlp.up.weight": (6 * HIDDEN, HIDDEN), "mlp.down.weight": (HIDDEN, 3 * HIDDEN),
+              "norm1.weight": (HIDDEN,), "norm2.weight": (HIDDEN,)}
+    blocks = [{k: (torch.randn(v, device=dev, generator=g) * 0.02).to(torch.bfloat16) for k, v in shapes.items()} for _ in range(args.blocks)]
+    block_bytes = sum(t.numel() * 2 for t in blocks[0].values())
+    off = BlockOffloader(dev, blocks, mode, chunk_bytes=args.chunk_mb << 20)
+    del blocks
+    torch.cuda.empty_cache()
+    order = list(range(args.blocks)) + list(reversed(range(args.blocks)))
+    stream = torch.cuda.current_stream()
+
+    def step():
+        off.prefetch_block(order[0])
+        for i, idx in enumerate(order):
+            w = off.await_block(idx)
+            if i + 1 < len(order):
+                off.prefetch_block(order[i + 1])
+            w["norm1.weight"].add_(0)      # a consumer on the compute stream, so each block is really waited for
+    for _ in range(max(1, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    st0 = off.stats()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(dev.index or 0) as clk:
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    st1 = off.stats()
+    link = (st1["bytes_link_in"] - st0["bytes_link_in"]) / args.steps
+    # consecutive equal indices (the turn-around block) are served from the slot that already holds them
+    loaded = sum(1 for i, idx in enumerate(order) if i == 0 or order[i - 1] != idx)
+    print(json.dumps({
+        "mode": "weights", "metric": "block weights streamed host->device, BF16-equivalent GB/s", "unit": "GB/s",
+        "value": round(loaded * block_bytes / (ms * 1e-3) * 1e-9, 2), "ms_per_step": round(ms, 3), "steps": args.steps, "warmup": args.warmup,
+        "codec": args.codec, "blocks": args.blocks, "block_bytes": block_bytes, "blocks_loaded_per_step": loaded,
+        "h2d_link_gbs": round(link / (ms * 1e-3) * 1e-9, 2), "h2d_frac_of_bound": round(link / (ms * 1e-3) * 1e-9 / PCIE_GEN5_X16_GBS, 3),
+        "pinned_bytes": off.pinned_bytes(), "device_slot_bytes": off.device_bytes(), "codec_launches": st1["codec_launches"] - st0["codec_launches"],
+        "clocks": clk.summary()}), flush=True)
+    off.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -516,8 +566,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-ref-gpu", action="store_true", help="--impl reference: skip timing the reference's own compiled CUDA files")
     ap.add_argument("--only", choices=["all", "value", "e2e"], default="all", help="profiling: run only one timed region")
-    ap.add_argument("--mode", choices=["bench", "sweep", "interference"], default="bench",
-                    help="sweep: 1 MB..4 GB single tensor x codec x chunk size; interference: copies against HBM-bound kernels")
+    ap.add_argument("--mode", choices=["bench", "sweep", "interference", "weights"], default="bench",
+                    help="sweep: 1 MB..4 GB single tensor x codec x chunk size; interference: copies against HBM-bound kernels; "
+                         "weights: block weights streamed host->device through the same pool")
     ap.add_argument("--sweep-max-mb", type=int, default=4096)
     ap.add_argument("--workload", choices=["dit", "c4"], default="dit",
                     help="c4: 200 x [8,4096,3072] BF16 = 40 GB per GPU per step (the replica-contention case)")
@@ -553,6 +604,12 @@ def main():
 
     if args.mode == "sweep":
         run_sweep(args, torch, lib, dev, rank)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.mode == "weights":
+        if rank == 0:
+            run_weights(args, torch, dev)
         if world > 1:
             dist.destroy_process_group()
         return

@@ -3,7 +3,8 @@
 Only what the hot path needs: the CUDA kernels and C ABI (``csrc/``,
 ``libflame_offload.so``), and Python mirrors of the reference interface
 (``ActivationOffloadPool``, ``PinnedHostBuffer``, ``PinnedPool``,
-``CheckpointPolicy`` / ``CheckpointManager``, ``checkpoint_offload``).
+``CheckpointPolicy`` / ``CheckpointManager``, ``checkpoint_offload``, and
+``BlockOffloader`` for block weights streamed through the same pool).
 
 Importing the package does not load CUDA.  Every operation goes through the
 shared library; there is no CPU or eager fallback, and a missing library is an
@@ -22,7 +23,10 @@ from .activation_offload import (  # noqa: F401
     CudaError,
 )
 
+from .block_offload import BlockOffloader  # noqa: F401,E402
+
 __all__ = [
+    "BlockOffloader",
     "PinnedAllocFlags", "PinnedHostBuffer", "StagingDeviceBuf", "PinnedPool",
     "ActivationOffloadPool", "OffloadCompression", "OffloadHandle",
     "OffloadError", "InvalidInput", "InvalidOperation", "Unsupported", "CudaError",

@@ -154,14 +154,19 @@ class ActivationOffloadPool:
         self._keep_alive[h.slot] = (h, tensor.detach())
         return handle
 
-    def pull_into(self, handle: OffloadHandle, dst, defer_wait: bool = False) -> None:
-        """Restore into `dst` (contiguous, same dtype, at least as many bytes)."""
+    def pull_into(self, handle: OffloadHandle, dst, defer_wait: bool = False, keep: bool = False) -> None:
+        """Restore into `dst` (contiguous, same dtype, at least as many bytes).
+
+        keep=True leaves the slot Pushed with its pinned copy intact, so the same handle can be
+        restored again (weights streamed in every step)."""
         if not dst.is_contiguous() or dst.device != self.device:
             raise InvalidInput("ActivationOffloadPool::pull_into: destination must be a contiguous tensor on the pool's device")
         st = self._lib.flame_offload_pool_pull_into(self._h, handle._c(), dst.data_ptr(), dst.numel() * dst.element_size(),
-                                                   self._stream(), 1 if defer_wait else 0)
+                                                   self._stream(), (1 if defer_wait else 0) | (2 if keep else 0))
         if st != 0:
             raise_for_status(st, _lib.last_error())
+        if keep:
+            return
         if not defer_wait:
             self._keep_alive.pop(handle.slot, None)
         self._meta.pop(handle.slot, None)

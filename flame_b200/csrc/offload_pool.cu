@@ -564,12 +564,14 @@ FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* p, FlameOffloa
   DeviceGuard guard(p->device);
   cudaError_t e = enqueue_pull(*p, s, static_cast<uint8_t*>(dst), (cudaStream_t)compute_stream, flags);
   if (e != cudaSuccess) return FLAME_OFFLOAD_ERR_CUDA;  // slot stays Pushed (src/activation_offload.rs:704-711)
-  s.state = SlotState::Idle;
   if (trace_on())
-    fprintf(stderr, "[flame_offload] pull slot=%llu bytes=%llu chunks=%zu deferred_wait=%u\n", (unsigned long long)h.slot,
-            (unsigned long long)s.bytes, s.chunks.size(), flags & FLAME_OFFLOAD_PULL_DEFER_WAIT);
-  p->release_chunks(s, (int32_t)h.slot);
-  p->free_stack.push_back(h.slot);
+    fprintf(stderr, "[flame_offload] pull slot=%llu bytes=%llu chunks=%zu deferred_wait=%u keep=%u\n", (unsigned long long)h.slot,
+            (unsigned long long)s.bytes, s.chunks.size(), flags & FLAME_OFFLOAD_PULL_DEFER_WAIT, (flags & FLAME_OFFLOAD_PULL_KEEP) >> 1);
+  if (!(flags & FLAME_OFFLOAD_PULL_KEEP)) {
+    s.state = SlotState::Idle;
+    p->release_chunks(s, (int32_t)h.slot);
+    p->free_stack.push_back(h.slot);
+  }
   p->stats.pulls++;
   p->stats.bytes_logical_in += s.bytes;
   p->stats.host_chunks_free = p->free_chunks.size();
@@ -585,7 +587,9 @@ FlameOffloadStatus flame_offload_pool_discard(FlameOffloadPool* p, FlameOffloadH
   s.state = SlotState::Idle;
   // An offload that is still writing these chunks runs on the D2H stream, the
   // stream every later offload into them is queued on, so reuse stays ordered.
-  p->release_chunks(s, -1);
+  // A restore that kept the slot (FLAME_OFFLOAD_PULL_KEEP) may still be reading
+  // them: the next writer waits for this slot's last host-to-device copy.
+  p->release_chunks(s, s.h2d_done.recorded ? (int32_t)h.slot : -1);
   p->free_stack.push_back(h.slot);
   p->stats.host_chunks_free = p->free_chunks.size();
   return FLAME_OFFLOAD_OK;
@@ -606,7 +610,7 @@ FlameOffloadStatus flame_offload_pool_clear(FlameOffloadPool* p) {
   for (size_t i = 0; i < p->slots.size(); ++i) {
     Slot& s = p->slots[i];
     s.state = SlotState::Idle;
-    p->release_chunks(s, -1);
+    p->release_chunks(s, s.h2d_done.recorded ? (int32_t)i : -1);
   }
   p->free_stack.clear();
   for (size_t i = p->num_slots; i-- > 0;) p->free_stack.push_back(i);

@@ -229,8 +229,13 @@ FlameOffloadStatus flame_offload_pool_push(FlameOffloadPool* pool, const void* s
  * `compute_stream` is ordered before the first write into dst.  Unless
  * FLAME_OFFLOAD_PULL_DEFER_WAIT is set, `compute_stream` is made to wait for
  * the restore before returning (src/activation_offload.rs:714-715).  The slot
- * returns to Idle and to the top of the free stack. */
+ * returns to Idle and to the top of the free stack, unless FLAME_OFFLOAD_PULL_KEEP
+ * is set: then the slot stays Pushed with its pinned copy intact and the same
+ * handle can be restored again (block weights streamed in every step, the
+ * pattern of the pinned staging helpers in src/pinned.rs:320-401; the reference's
+ * pool itself has no non-consuming pull). */
 #define FLAME_OFFLOAD_PULL_DEFER_WAIT 1u
+#define FLAME_OFFLOAD_PULL_KEEP 2u
 FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* pool, FlameOffloadHandle handle, void* dst_device, size_t dst_bytes, void* compute_stream, unsigned int flags);
 /* Makes `stream` wait for the most recent restore issued from `slot`. */
 FlameOffloadStatus flame_offload_pool_wait_ready(FlameOffloadPool* pool, size_t slot, void* stream);
