@@ -71,6 +71,11 @@ class PolicyBlockPlan(C.Structure):
 _vp, _sz, _i, _u, _f, _d = C.c_void_p, C.c_size_t, C.c_int, C.c_uint, C.c_float, C.c_double
 
 # name -> (restype, argtypes); one entry per declaration in include/flame_offload.h
+class ArenaStats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("capacity_bytes", "in_use_bytes", "peak_in_use_bytes", "allocs", "releases",
+                                          "rejected", "resets", "live_regions")]
+
+
 SIGNATURES = {
     "flame_offload_last_error": (C.c_char_p, []),
     "flame_cuda_alloc_pinned_host": (_vp, [_sz, _u]),
@@ -111,6 +116,12 @@ SIGNATURES = {
     "flame_offload_pool_read_slot": (_i, [_vp, Handle, _vp, _vp, _d]),
     "flame_offload_pool_stats": (_i, [_vp, C.POINTER(Stats)]),
     "flame_offload_inject_fault": (None, [_i, _i]),
+    "flame_restore_arena_create": (_vp, [_vp, _sz, _sz]),
+    "flame_restore_arena_destroy": (None, [_vp]),
+    "flame_restore_arena_alloc": (_i, [_vp, _sz, C.POINTER(_vp), C.POINTER(C.c_uint64)]),
+    "flame_restore_arena_release": (_i, [_vp, C.c_uint64]),
+    "flame_restore_arena_reset": (_i, [_vp]),
+    "flame_restore_arena_stats": (_i, [_vp, C.POINTER(ArenaStats)]),
     "flame_pinned_pool_create": (_vp, [_u, _sz]),
     "flame_pinned_pool_destroy": (None, [_vp]),
     "flame_pinned_pool_checkout": (_i, [_vp, _sz, C.POINTER(_vp), C.POINTER(_sz)]),

@@ -59,6 +59,25 @@ def activation_offload_pool() -> Optional[ActivationOffloadPool]:
     return _ACTIVATION_POOL
 
 
+_RESTORE_ARENA = None
+
+
+def set_restore_arena(arena) -> None:
+    """Restored activations are written into `arena` (a RestoreArena made on the stream backward runs on) instead
+    of freshly allocated tensors (src/activation_offload.rs:655); None switches back.  When the arena has no
+    released space next in its ring, the restore falls back to a fresh tensor."""
+    global _RESTORE_ARENA
+    _RESTORE_ARENA = arena
+
+
+def _destination(shape, dtype, device) -> torch.Tensor:
+    if _RESTORE_ARENA is not None:
+        t = _RESTORE_ARENA.empty(shape, dtype)
+        if t is not None:
+            return t
+    return torch.empty(shape, dtype=dtype, device=device)
+
+
 def checkpoint(inputs: Sequence[torch.Tensor], f: Callable[..., torch.Tensor]) -> torch.Tensor:
     """Recompute arm: run ``f(*inputs)`` without saving activations, re-run it in backward."""
     if not inputs:
@@ -202,7 +221,7 @@ class _Block:
         for ref in reversed(self.entries):
             e = ref()
             if e is not None and e.restored is None:
-                dst = torch.empty(e.shape, dtype=e.dtype, device=self.pool.device)
+                dst = _destination(e.shape, e.dtype, self.pool.device)
                 self.pool.pull_into(e.handle, dst, defer_wait=True)
                 e.restored = dst
 
@@ -216,7 +235,7 @@ class _Block:
             if not self.restores_issued:
                 self.issue_restores()
         if obj.restored is None:  # pushed after the block's restores were issued: cannot happen, but stay correct
-            dst = torch.empty(obj.shape, dtype=obj.dtype, device=self.pool.device)
+            dst = _destination(obj.shape, obj.dtype, self.pool.device)
             self.pool.pull_into(obj.handle, dst, defer_wait=True)
             obj.restored = dst
         if not obj.waited:

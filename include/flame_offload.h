@@ -356,6 +356,37 @@ typedef struct {
 
 FlameOffloadStatus flame_offload_policy_plan_blocks(const FlamePolicyInput* in, const FlamePolicyBlock* blocks, size_t n, int offload_decision, int32_t* decisions, FlamePolicyBlockPlan* out);
 
+/* ------------------------------------------------------------------------
+ * 7. Restore arena: destinations for pull_into() out of one range reserved at
+ *    set-up.  Replaces the fresh tensor of every pull
+ *    (src/activation_offload.rs:655); the model is the reference's stream-keyed
+ *    arena (src/staging.rs:219-297: arena_alloc, arena_record_and_release,
+ *    arena_reset, arena_stats).
+ *
+ *    The arena is host bookkeeping over [base, base+bytes), memory the caller
+ *    allocated once and keeps alive.  It belongs to ONE stream: every use of a
+ *    region is queued on that stream (or ordered with it, as pull_into orders
+ *    the pool's copies when it is given that stream), and release() is called
+ *    after the last use has been queued.  Space is handed out in ring order;
+ *    releases may arrive in any order and space returns when the oldest (or
+ *    newest) regions have been released.  No call here touches CUDA.
+ * ---------------------------------------------------------------------- */
+typedef struct FlameRestoreArena FlameRestoreArena;
+typedef struct {
+  uint64_t capacity_bytes, in_use_bytes, peak_in_use_bytes;
+  uint64_t allocs, releases, rejected, resets, live_regions;
+} FlameRestoreArenaStats;
+/* alignment: power of two, 0 = 256.  NULL on bad arguments. */
+FlameRestoreArena* flame_restore_arena_create(void* base_device, size_t bytes, size_t alignment);
+void flame_restore_arena_destroy(FlameRestoreArena* arena);
+/* FLAME_OFFLOAD_ERR_STATE when no released space of that size is next in the ring (the caller falls back to its
+ * own allocator); FLAME_OFFLOAD_ERR_INVALID when `bytes` is 0 or larger than the arena. */
+FlameOffloadStatus flame_restore_arena_alloc(FlameRestoreArena* arena, size_t bytes, void** out_ptr, uint64_t* out_ticket);
+FlameOffloadStatus flame_restore_arena_release(FlameRestoreArena* arena, uint64_t ticket);
+/* Forgets every region (arena_reset, src/staging.rs:270): tickets handed out before are no longer valid. */
+FlameOffloadStatus flame_restore_arena_reset(FlameRestoreArena* arena);
+FlameOffloadStatus flame_restore_arena_stats(const FlameRestoreArena* arena, FlameRestoreArenaStats* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -112,6 +112,47 @@ def test_a_graph_dropped_without_backward_gives_its_slots_back(cuda_device, mode
     assert all((a.float() - b.float()).norm() / a.float().norm().clamp_min(1e-12) < 0.05 for a, b in zip(want, got))
 
 
+def test_restore_arena_serves_destinations_and_gets_them_back(cuda_device, model_and_input):
+    import gc
+
+    from flame_b200.restore_arena import RestoreArena
+    model, x = model_and_input
+    arena = RestoreArena(cuda_device, 96 << 20)
+    t = arena.empty((1000, 3), torch.bfloat16)
+    assert t.shape == (1000, 3) and t.dtype == torch.bfloat16 and t.device == x.device and t.data_ptr() % 256 == 0
+    t.fill_(1.5)
+    v = t.view(-1)[10:20]
+    del t
+    gc.collect()
+    assert arena.stats()["live_regions"] == 1          # a view keeps the storage, hence the region
+    assert bool((v == 1.5).all())
+    del v
+    gc.collect()
+    assert arena.stats()["live_regions"] == 0 and arena.stats()["releases"] == 1
+
+    want = _grads(model, x, ["resident"] * 4)
+    pool = ActivationOffloadPool(cuda_device, 64, 2 * 1024 * 2048 * 2 * 2, OffloadCompression.NONE, chunk_bytes=1 << 20)
+    ckpt.set_activation_offload_pool(pool)
+    ckpt.set_restore_arena(arena)
+    try:
+        for _ in range(3):
+            got = _grads(model, x, ["offload"] * 4)
+            assert all(torch.equal(a, b) for a, b in zip(want, got))
+        del got
+        gc.collect()
+        st = arena.stats()
+        assert st["allocs"] > 10 and st["rejected"] == 0 and st["live_regions"] == 0 and st["in_use_bytes"] == 0
+        assert st["peak_in_use_bytes"] <= st["capacity_bytes"]
+        # an arena that is too small: restores fall back to fresh tensors, gradients unchanged
+        small = RestoreArena(cuda_device, 1 << 20)
+        ckpt.set_restore_arena(small)
+        got = _grads(model, x, ["offload"] * 4)
+        assert all(torch.equal(a, b) for a, b in zip(want, got))
+        assert small.stats()["rejected"] > 0
+    finally:
+        ckpt.set_restore_arena(None)
+
+
 def test_without_a_pool_checkpoint_offload_is_checkpoint(cuda_device, model_and_input):
     model, x = model_and_input
     ckpt.clear_activation_offload_pool()
