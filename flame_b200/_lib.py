@@ -27,13 +27,15 @@ class PoolConfig(C.Structure):
         ("staging_tiles", C.c_uint32), ("codec_flags", C.c_uint32), ("host_budget_bytes", C.c_uint64),
         ("host_alloc_flags", C.c_uint32), ("codec_max_ctas", C.c_int32), ("numa_node", C.c_int32),
         ("tile_chunks", C.c_uint32), ("d2h_piece_bytes", C.c_uint64), ("h2d_piece_bytes", C.c_uint64),
+        ("deferred_inflight_bytes", C.c_uint64),
     ]
 
 
 class Stats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in (
         "pushes", "pulls", "bytes_logical_out", "bytes_logical_in", "bytes_link_out", "bytes_link_in",
-        "chunks_out", "chunks_in", "codec_launches", "host_chunks_total", "host_chunks_free", "push_rejected_full")]
+        "chunks_out", "chunks_in", "codec_launches", "host_chunks_total", "host_chunks_free", "push_rejected_full",
+        "pushes_cancelled", "pushes_queued")]
 
 
 class SlotInfo(C.Structure):
@@ -116,6 +118,8 @@ SIGNATURES = {
     "flame_offload_pool_read_slot": (_i, [_vp, Handle, _vp, _vp, _d]),
     "flame_offload_pool_stats": (_i, [_vp, C.POINTER(Stats)]),
     "flame_offload_inject_fault": (None, [_i, _i]),
+    "flame_offload_pool_cancel": (_i, [_vp, Handle]),
+    "flame_offload_pool_hold": (_i, [_vp, _i]),
     "flame_restore_arena_create": (_vp, [_vp, _sz, _sz]),
     "flame_restore_arena_destroy": (None, [_vp]),
     "flame_restore_arena_alloc": (_i, [_vp, _sz, C.POINTER(_vp), C.POINTER(C.c_uint64)]),

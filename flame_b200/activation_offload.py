@@ -66,7 +66,8 @@ class ActivationOffloadPool:
                  compression: OffloadCompression = OffloadCompression.NONE, *,
                  chunk_bytes: int = 0, staging_tiles: int = 0, codec_flags: int = 0,
                  host_budget_bytes: int = 0, host_alloc_flags: int = 0, codec_max_ctas: int = 0,
-                 numa_node: int = -2, tile_chunks: int = 0, d2h_piece_bytes: int = 0, h2d_piece_bytes: int = 0):
+                 numa_node: int = -2, tile_chunks: int = 0, d2h_piece_bytes: int = 0, h2d_piece_bytes: int = 0,
+                 deferred_inflight_bytes: int = 0):
         import torch
 
         self._torch = torch
@@ -77,7 +78,8 @@ class ActivationOffloadPool:
         self.device = torch.device("cuda", index)
         cfg = _lib.PoolConfig(C.sizeof(_lib.PoolConfig), index, chunk_bytes, staging_tiles, codec_flags,
                               host_budget_bytes, host_alloc_flags, codec_max_ctas, numa_node, tile_chunks,
-                              d2h_piece_bytes, h2d_piece_bytes)
+                              d2h_piece_bytes, h2d_piece_bytes, deferred_inflight_bytes)
+        self.deferred = deferred_inflight_bytes > 0
         self._lib = _lib.lib()
         with torch.cuda.device(index):
             self._h = self._lib.flame_offload_pool_create(num_slots, max_bytes, int(compression), C.byref(cfg))
@@ -179,6 +181,25 @@ class ActivationOffloadPool:
         out = self._torch.empty(shape, dtype=dtype, device=self.device)
         self.pull_into(handle, out)
         return out
+
+    def cancel(self, handle: OffloadHandle):
+        """Deferred pools: if the offload of `handle` has not been enqueued yet, takes it out of the queue and returns
+        the source tensor, which never left the device (its slot is free again).  Otherwise None: restore it with
+        pull / pull_into."""
+        if not self.deferred:
+            return None
+        r = self._lib.flame_offload_pool_cancel(self._h, handle._c())
+        if r < 0:
+            raise_for_status(-r, _lib.last_error())
+        if r == 0:
+            return None
+        self._meta.pop(handle.slot, None)
+        return self._keep_alive.pop(handle.slot)[1]
+
+    def hold_offloads(self, on: bool) -> None:
+        """Deferred pools: while on, queued offloads are not enqueued (backward has begun; they are about to be
+        cancelled or pulled)."""
+        raise_for_status(self._lib.flame_offload_pool_hold(self._h, 1 if on else 0), _lib.last_error())
 
     def discard(self, handle: OffloadHandle) -> None:
         """Frees the slot of `handle` without restoring it (an abandoned block, src/autograd.rs:1742-1769)."""

@@ -51,8 +51,8 @@ def set_activation_offload_pool(pool: ActivationOffloadPool) -> None:
 def clear_activation_offload_pool() -> None:
     """Uninstall the pool (the reference's OnceLock cannot be reset; tests and benchmarks need to)."""
     global _ACTIVATION_POOL
+    _SCHEDULER.reset()       # while the pool is still installed: a deferred pool is released from its hold
     _ACTIVATION_POOL = None
-    _SCHEDULER.reset()
 
 
 def activation_offload_pool() -> Optional[ActivationOffloadPool]:
@@ -221,9 +221,19 @@ class _Block:
         for ref in reversed(self.entries):
             e = ref()
             if e is not None and e.restored is None:
-                dst = _destination(e.shape, e.dtype, self.pool.device)
-                self.pool.pull_into(e.handle, dst, defer_wait=True)
-                e.restored = dst
+                self._restore(e)
+
+    def _restore(self, e: "_Entry") -> None:
+        # A deferred pool may not have started this tensor's offload yet: then it never left the device and is
+        # used where it is, instead of being sent out and fetched back while backward waits.
+        src = self.pool.cancel(e.handle)
+        if src is not None:
+            e.restored = src.reshape(e.shape)
+            e.waited = True
+            return
+        dst = _destination(e.shape, e.dtype, self.pool.device)
+        self.pool.pull_into(e.handle, dst, defer_wait=True)
+        e.restored = dst
 
     def unpack(self, obj):
         if isinstance(obj, _View):
@@ -235,9 +245,7 @@ class _Block:
             if not self.restores_issued:
                 self.issue_restores()
         if obj.restored is None:  # pushed after the block's restores were issued: cannot happen, but stay correct
-            dst = _destination(obj.shape, obj.dtype, self.pool.device)
-            self.pool.pull_into(obj.handle, dst, defer_wait=True)
-            obj.restored = dst
+            self._restore(obj)
         if not obj.waited:
             self.pool.wait_ready(obj.handle.slot)
             obj.waited = True
@@ -255,7 +263,19 @@ class _Scheduler:
 
     def reset(self):
         self.blocks.clear()
+        if self._backward_seen:
+            self._hold(False)
         self._backward_seen = False
+
+    @staticmethod
+    def _hold(on: bool) -> None:
+        # deferred pools: nothing new goes out once backward has begun; what is still queued is used in place
+        pool = _ACTIVATION_POOL
+        if pool is not None and getattr(pool, "deferred", False):
+            try:
+                pool.hold_offloads(on)
+            except OffloadError:
+                pass
 
     def register(self, block: Optional[_Block]) -> int:
         if self._backward_seen:     # first forward call after a backward: a new step begins
@@ -265,6 +285,8 @@ class _Scheduler:
 
     def on_backward_reach(self, position: int) -> None:
         """Backward is about to run the block registered at `position`."""
+        if not self._backward_seen:
+            self._hold(True)
         self._backward_seen = True
         for j in range(min(position, len(self.blocks) - 1), max(-1, position - 1 - self.prefetch_blocks), -1):
             ref = self.blocks[j]

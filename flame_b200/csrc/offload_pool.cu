@@ -19,6 +19,16 @@
 //
 // There is no device-side waiting anywhere in this design (no flags, no spin
 // loops): ordering is CUDA events only, and every host wait is a bounded poll.
+//
+// Deferred offload (FlameOffloadPoolConfig.deferred_inflight_bytes > 0): push()
+// records where the source becomes valid and queues the tensor; a thread owned by
+// the pool enqueues the compress + D2H work of queued tensors in push order while
+// the pinned bytes in flight stay under the budget.  A tensor still queued when
+// backward reaches it has not left the device, so cancel() hands it back for use
+// in place: the link then carries only what it can carry beside compute, instead
+// of delaying backward with round trips that free nothing.  In that mode the
+// offload side (compress stream, D2H stream, outgoing tile ring) is driven by the
+// pool's thread only, the restore side by the caller's thread only.
 
 #include <sys/syscall.h>
 #include <unistd.h>
@@ -26,9 +36,12 @@
 #include <algorithm>
 #include <cctype>
 #include <chrono>
+#include <condition_variable>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <deque>
+#include <memory>
 #include <mutex>
 #include <thread>
 #include <vector>
@@ -62,9 +75,26 @@ struct Event {
 };
 
 enum class SlotState { Idle, Pushed };
+enum class Issue { Done, Queued, Issuing };  // Done: the offload's work is enqueued (always so in the immediate mode)
+
+// Everything the offload of one tensor needs, captured when push() is called.
+struct PushPlan {
+  std::vector<uint32_t> chunks;
+  std::vector<cudaEvent_t> readers;  // restores that may still be reading these chunks
+  const uint8_t* src = nullptr;
+  uint64_t numel = 0, bytes = 0;
+  float fp8_scale = 0.0f;
+  cudaEvent_t producer = nullptr, d2h_done = nullptr;
+};
+struct PushCounts { uint64_t link_bytes = 0, launches = 0; };
 
 struct Slot {
   SlotState state = SlotState::Idle;
+  Issue issue = Issue::Done;
+  bool urgent = false;         // a restore is waiting for this queued offload
+  bool failed = false;         // the deferred offload hit a CUDA error; `error` holds the text
+  std::string error;
+  std::unique_ptr<PushPlan> plan;
   uint64_t numel = 0, bytes = 0, stored_bytes = 0;
   int dtype = 0;
   float fp8_scale = 0.0f;
@@ -150,6 +180,15 @@ struct FlameOffloadPool {
 
   FlameOffloadStats stats{};
 
+  // deferred offload
+  bool deferred = false;
+  uint64_t inflight_budget = 0, inflight_bytes = 0;
+  std::deque<size_t> queue;                                // slots whose offload has not been enqueued, push order
+  std::deque<std::pair<cudaEvent_t, uint64_t>> inflight;   // (d2h_done, pinned bytes) of enqueued offloads, oldest first
+  bool hold = false, stop = false;
+  std::thread worker;
+  std::condition_variable cv_work, cv_issued;
+
   bool compressed() const { return compression != FLAME_OFFLOAD_COMPRESSION_NONE; }
   uint8_t* chunk_ptr(uint32_t c) const { return slab + (size_t)c * host_chunk_bytes; }
 
@@ -160,6 +199,12 @@ struct FlameOffloadPool {
       case FLAME_OFFLOAD_COMPRESSION_FP8: return e_or_bytes;
       default: return packed_bytes(e_or_bytes);
     }
+  }
+
+  // A queued offload that never ran wrote nothing: whoever read these chunks last is still their last reader.
+  void release_chunks_unwritten(Slot& s) {
+    for (auto it = s.chunks.rbegin(); it != s.chunks.rend(); ++it) free_chunks.push_back(*it);
+    s.chunks.clear();
   }
 
   void release_chunks(Slot& s, int32_t reader) {
@@ -205,61 +250,144 @@ cudaError_t copy_in_pieces(void* dst, const void* src, size_t bytes, cudaMemcpyK
 
 cudaError_t kernel_guard() { return fault_fires(FLAME_OFFLOAD_FAULT_KERNEL) ? cudaErrorLaunchFailure : cudaSuccess; }
 
-// Enqueue the offload of one tensor.  Returns the first CUDA error.
-cudaError_t enqueue_push(FlameOffloadPool& p, Slot& s, const uint8_t* src, cudaStream_t compute) {
-  POOL_TRY(s.producer.record(compute), "push: cudaEventRecord(producer)");
+// Captures what the offload of slot `s` needs.  Called with the pool locked.
+PushPlan make_plan(FlameOffloadPool& p, const Slot& s, const uint8_t* src) {
+  PushPlan plan;
+  plan.chunks = s.chunks;
+  plan.src = src;
+  plan.numel = s.numel;
+  plan.bytes = s.bytes;
+  plan.fp8_scale = s.fp8_scale;
+  plan.producer = s.producer.ev;
+  plan.d2h_done = s.d2h_done.ev;
   // A chunk that an earlier restore is still reading must not be overwritten.
-  {
-    std::vector<int32_t> seen;
-    for (uint32_t c : s.chunks) {
-      const int32_t r = p.chunk_last_reader[c];
-      if (r < 0 || std::find(seen.begin(), seen.end(), r) != seen.end()) continue;
-      seen.push_back(r);
-      POOL_TRY(p.slots[r].h2d_done.make_wait(p.s_d2h), "push: wait(h2d_done)");
-    }
+  std::vector<int32_t> seen;
+  for (uint32_t c : s.chunks) {
+    const int32_t r = p.chunk_last_reader[c];
+    if (r < 0 || std::find(seen.begin(), seen.end(), r) != seen.end()) continue;
+    seen.push_back(r);
+    if (p.slots[r].h2d_done.recorded) plan.readers.push_back(p.slots[r].h2d_done.ev);
   }
-  const size_t nchunks = s.chunks.size();
+  return plan;
+}
+
+// Enqueue the offload of one tensor; `plan.producer` has been recorded on the caller's compute stream.
+// Touches the compress and D2H streams and the outgoing tile ring, which belong to the calling thread
+// (the caller's thread in the immediate mode, the pool's thread in the deferred mode), and nothing else
+// that changes.  Returns the first CUDA error.
+cudaError_t issue_push(FlameOffloadPool& p, const PushPlan& plan, PushCounts& n) {
+  for (cudaEvent_t ev : plan.readers) POOL_TRY(cudaStreamWaitEvent(p.s_d2h, ev, 0), "push: wait(h2d_done)");
+  const size_t nchunks = plan.chunks.size();
   if (!p.compressed()) {
-    POOL_TRY(s.producer.make_wait(p.s_d2h), "push: wait(producer)");
+    POOL_TRY(cudaStreamWaitEvent(p.s_d2h, plan.producer, 0), "push: wait(producer)");
     for (size_t k = 0; k < nchunks; ++k) {
       const uint64_t off = k * p.chunk_src_bytes;
-      const uint64_t len = std::min<uint64_t>(p.chunk_src_bytes, s.bytes - off);
-      POOL_TRY(copy_in_pieces(p.chunk_ptr(s.chunks[k]), src + off, len, cudaMemcpyDeviceToHost, p.s_d2h, p.d2h_piece), "push: D2H");
-      p.stats.bytes_link_out += len;
+      const uint64_t len = std::min<uint64_t>(p.chunk_src_bytes, plan.bytes - off);
+      POOL_TRY(copy_in_pieces(p.chunk_ptr(plan.chunks[k]), plan.src + off, len, cudaMemcpyDeviceToHost, p.s_d2h, p.d2h_piece), "push: D2H");
+      n.link_bytes += len;
     }
   } else {
-    POOL_TRY(s.producer.make_wait(p.s_quant), "push: wait(producer)");
+    POOL_TRY(cudaStreamWaitEvent(p.s_quant, plan.producer, 0), "push: wait(producer)");
     // One codec launch fills a staging tile of up to tile_chunks self-contained
     // chunks; each chunk then crosses the link as one copy.
     for (size_t k0 = 0; k0 < nchunks; k0 += p.tile_chunks) {
       const size_t kn = std::min<size_t>(p.tile_chunks, nchunks - k0);
       const uint64_t e0 = k0 * p.chunk_elems;
-      const uint64_t e = std::min<uint64_t>(kn * p.chunk_elems, s.numel - e0);
+      const uint64_t e = std::min<uint64_t>(kn * p.chunk_elems, plan.numel - e0);
       Tile& t = p.out_tiles[p.out_next++ % p.out_tiles.size()];
       POOL_TRY(t.free_.make_wait(p.s_quant), "push: wait(tile free)");
       POOL_TRY(kernel_guard(), "push: compress kernel");
-      const void* in = src + 2 * e0;
+      const void* in = plan.src + 2 * e0;
       if (p.compression == FLAME_OFFLOAD_COMPRESSION_FP8)
-        POOL_TRY(launch_bf16_to_fp8(in, t.dev, 1.0f / s.fp8_scale, e, p.s_quant, p.codec_max_ctas), "push: bf16_to_fp8");
+        POOL_TRY(launch_bf16_to_fp8(in, t.dev, 1.0f / plan.fp8_scale, e, p.s_quant, p.codec_max_ctas), "push: bf16_to_fp8");
       else
         POOL_TRY(launch_compress(p.compression, in, t.dev, e, packed_chunks_layout(e, p.chunk_elems, p.host_chunk_bytes),
                                  p.codec_flags, p.s_quant, p.codec_max_ctas), "push: compress");
-      p.stats.codec_launches++;
+      n.launches++;
       POOL_TRY(t.full.record(p.s_quant), "push: record(tile full)");
       POOL_TRY(t.full.make_wait(p.s_d2h), "push: wait(tile full)");
       for (size_t j = 0; j < kn; ++j) {
         const uint64_t ec = std::min<uint64_t>(p.chunk_elems, e - j * p.chunk_elems);
         const size_t link = p.stored_for(ec);
-        POOL_TRY(copy_in_pieces(p.chunk_ptr(s.chunks[k0 + j]), t.dev + j * p.host_chunk_bytes, link,
+        POOL_TRY(copy_in_pieces(p.chunk_ptr(plan.chunks[k0 + j]), t.dev + j * p.host_chunk_bytes, link,
                                 cudaMemcpyDeviceToHost, p.s_d2h, p.d2h_piece), "push: D2H");
-        p.stats.bytes_link_out += link;
+        n.link_bytes += link;
       }
       POOL_TRY(t.free_.record(p.s_d2h), "push: record(tile free)");
     }
   }
-  POOL_TRY(s.d2h_done.record(p.s_d2h), "push: record(d2h_done)");
-  p.stats.chunks_out += nchunks;
+  POOL_TRY(cudaEventRecord(plan.d2h_done, p.s_d2h), "push: record(d2h_done)");
   return cudaSuccess;
+}
+
+void count_push(FlameOffloadPool& p, const PushPlan& plan, const PushCounts& n) {
+  p.stats.bytes_link_out += n.link_bytes;
+  p.stats.codec_launches += n.launches;
+  p.stats.chunks_out += plan.chunks.size();
+}
+
+// The pool's thread in the deferred mode: enqueues queued offloads in push order while the pinned bytes
+// in flight are under the budget (a tensor that a restore is waiting for goes first and always runs).
+void deferred_worker(FlameOffloadPool* p) {
+  cudaSetDevice(p->device);
+  std::unique_lock<std::mutex> lk(p->mu);
+  while (!p->stop) {
+    while (!p->inflight.empty() && cudaEventQuery(p->inflight.front().first) != cudaErrorNotReady) {
+      p->inflight_bytes -= p->inflight.front().second;
+      p->inflight.pop_front();
+    }
+    bool take = false;
+    if (!p->queue.empty()) {
+      const Slot& c = p->slots[p->queue.front()];
+      take = c.urgent || (!p->hold && p->inflight_bytes < p->inflight_budget);
+    }
+    if (!take) {
+      if (p->queue.empty() && p->inflight.empty()) p->cv_work.wait(lk);
+      else p->cv_work.wait_for(lk, std::chrono::microseconds(100));
+      continue;
+    }
+    const size_t slot = p->queue.front();
+    p->queue.pop_front();
+    Slot& s = p->slots[slot];
+    s.issue = Issue::Issuing;
+    std::unique_ptr<PushPlan> plan = std::move(s.plan);
+    lk.unlock();
+    PushCounts n;
+    const cudaError_t e = issue_push(*p, *plan, n);
+    std::string text = e == cudaSuccess ? std::string() : std::string(flame_offload_last_error());
+    lk.lock();
+    if (e == cudaSuccess) {
+      s.d2h_done.recorded = true;
+      count_push(*p, *plan, n);
+      p->inflight.emplace_back(plan->d2h_done, n.link_bytes);
+      p->inflight_bytes += n.link_bytes;
+    } else {
+      s.failed = true;
+      s.error = text;
+    }
+    s.issue = Issue::Done;
+    s.urgent = false;
+    p->stats.pushes_queued = p->queue.size();
+    p->cv_issued.notify_all();
+  }
+}
+
+// Waits (bounded) until the offload of slot `s` has been enqueued, moving it to the head of the queue.
+// Called with `lk` held.
+FlameOffloadStatus wait_issued(FlameOffloadPool* p, std::unique_lock<std::mutex>& lk, size_t slot, const char* who) {
+  Slot& s = p->slots[slot];
+  if (s.issue == Issue::Queued) {
+    auto it = std::find(p->queue.begin(), p->queue.end(), slot);
+    if (it != p->queue.end()) { p->queue.erase(it); p->queue.push_front(slot); }
+    s.urgent = true;
+    p->cv_work.notify_all();
+  }
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(30);
+  while (s.issue != Issue::Done) {
+    if (p->cv_issued.wait_until(lk, deadline) == std::cv_status::timeout && s.issue != Issue::Done)
+      return fail(FLAME_OFFLOAD_ERR_TIMEOUT, std::string(who) + ": the pool's thread did not enqueue the offload within 30 s");
+  }
+  return FLAME_OFFLOAD_OK;
 }
 
 cudaError_t enqueue_pull(FlameOffloadPool& p, Slot& s, uint8_t* dst, cudaStream_t compute, unsigned flags) {
@@ -462,6 +590,11 @@ FlameOffloadPool* flame_offload_pool_create(size_t num_slots, size_t max_bytes, 
     }
   }
   if (!ok) { destroy_pool(p); return nullptr; }
+  if (cfg.deferred_inflight_bytes) {
+    p->deferred = true;
+    p->inflight_budget = cfg.deferred_inflight_bytes;
+    p->worker = std::thread(deferred_worker, p);
+  }
   p->stats.host_chunks_total = total;
   p->stats.host_chunks_free = total;
   return p;
@@ -469,6 +602,11 @@ FlameOffloadPool* flame_offload_pool_create(size_t num_slots, size_t max_bytes, 
 
 void flame_offload_pool_destroy(FlameOffloadPool* p) {
   if (!p) return;
+  if (p->worker.joinable()) {
+    { std::lock_guard<std::mutex> lk(p->mu); p->stop = true; }
+    p->cv_work.notify_all();
+    p->worker.join();
+  }
   DeviceGuard guard(p->device);
   poll_streams(p, 30.0);
   destroy_pool(p);
@@ -533,7 +671,26 @@ FlameOffloadStatus flame_offload_pool_push(FlameOffloadPool* p, const void* src,
   }
   if (!p->compressed()) s.stored_bytes = bytes;
 
-  cudaError_t e = enqueue_push(*p, s, static_cast<const uint8_t*>(src), (cudaStream_t)compute_stream);
+  s.failed = false;
+  s.error.clear();
+  s.urgent = false;
+  s.d2h_done.recorded = false;
+  cudaError_t e = s.producer.record((cudaStream_t)compute_stream);
+  if (e != cudaSuccess) fail_cuda(e, "push: cudaEventRecord(producer)");
+  if (e == cudaSuccess) {
+    PushPlan plan = make_plan(*p, s, static_cast<const uint8_t*>(src));
+    if (p->deferred) {
+      s.plan.reset(new PushPlan(std::move(plan)));
+      s.issue = Issue::Queued;
+      p->queue.push_back(slot);
+      p->stats.pushes_queued = p->queue.size();
+      p->cv_work.notify_one();
+    } else {
+      PushCounts n;
+      e = issue_push(*p, plan, n);
+      if (e == cudaSuccess) { s.d2h_done.recorded = true; count_push(*p, plan, n); }
+    }
+  }
   if (e != cudaSuccess) {
     // As the reference does on a failed copy (src/activation_offload.rs:528-533): the slot goes back.
     p->release_chunks(s, -1);
@@ -554,13 +711,25 @@ FlameOffloadStatus flame_offload_pool_push(FlameOffloadPool* p, const void* src,
 
 FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* p, FlameOffloadHandle h, void* dst, size_t dst_bytes, void* compute_stream, unsigned int flags) {
   if (!p) return fail(FLAME_OFFLOAD_ERR_INVALID, "pull: null pool");
-  std::lock_guard<std::mutex> lk(p->mu);
+  std::unique_lock<std::mutex> lk(p->mu);
   FlameOffloadStatus st = p->check_handle(h, "ActivationOffloadPool::pull");
   if (st != FLAME_OFFLOAD_OK) return st;
   Slot& s = p->slots[h.slot];
   if (!dst) return fail(FLAME_OFFLOAD_ERR_INVALID, "pull: null destination");
   if (dst_bytes < s.bytes)
     return fail(FLAME_OFFLOAD_ERR_INVALID, "pull: destination holds " + std::to_string(dst_bytes) + " bytes, tensor needs " + std::to_string(s.bytes));
+  if (s.issue != Issue::Done) {  // deferred and not enqueued yet: it jumps the queue, then the restore follows it
+    st = wait_issued(p, lk, h.slot, "pull");
+    if (st != FLAME_OFFLOAD_OK) return st;
+  }
+  if (s.failed) {  // the deferred offload itself failed: the data never reached the host; the slot is given up
+    const std::string text = "pull: the deferred offload of this slot failed: " + s.error;
+    s.state = SlotState::Idle;
+    p->release_chunks(s, -1);
+    p->free_stack.push_back(h.slot);
+    p->stats.host_chunks_free = p->free_chunks.size();
+    return fail(FLAME_OFFLOAD_ERR_CUDA, text);
+  }
   DeviceGuard guard(p->device);
   cudaError_t e = enqueue_pull(*p, s, static_cast<uint8_t*>(dst), (cudaStream_t)compute_stream, flags);
   if (e != cudaSuccess) return FLAME_OFFLOAD_ERR_CUDA;  // slot stays Pushed (src/activation_offload.rs:704-711)
@@ -578,12 +747,56 @@ FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* p, FlameOffloa
   return FLAME_OFFLOAD_OK;
 }
 
+int flame_offload_pool_cancel(FlameOffloadPool* p, FlameOffloadHandle h) {
+  if (!p) return -(int)fail(FLAME_OFFLOAD_ERR_INVALID, "cancel: null pool");
+  std::lock_guard<std::mutex> lk(p->mu);
+  FlameOffloadStatus st = p->check_handle(h, "ActivationOffloadPool::cancel");
+  if (st != FLAME_OFFLOAD_OK) return -(int)st;
+  Slot& s = p->slots[h.slot];
+  if (s.issue != Issue::Queued) return 0;
+  p->queue.erase(std::find(p->queue.begin(), p->queue.end(), (size_t)h.slot));
+  s.plan.reset();
+  s.issue = Issue::Done;
+  s.state = SlotState::Idle;
+  p->release_chunks_unwritten(s);
+  p->free_stack.push_back(h.slot);
+  p->stats.pushes_cancelled++;
+  p->stats.pushes_queued = p->queue.size();
+  p->stats.host_chunks_free = p->free_chunks.size();
+  if (trace_on()) fprintf(stderr, "[flame_offload] cancel slot=%llu (still on the device)\n", (unsigned long long)h.slot);
+  return 1;
+}
+
+FlameOffloadStatus flame_offload_pool_hold(FlameOffloadPool* p, int on) {
+  if (!p) return fail(FLAME_OFFLOAD_ERR_INVALID, "hold: null pool");
+  std::lock_guard<std::mutex> lk(p->mu);
+  p->hold = on != 0;
+  p->cv_work.notify_all();
+  return FLAME_OFFLOAD_OK;
+}
+
 FlameOffloadStatus flame_offload_pool_discard(FlameOffloadPool* p, FlameOffloadHandle h) {
   if (!p) return fail(FLAME_OFFLOAD_ERR_INVALID, "discard: null pool");
-  std::lock_guard<std::mutex> lk(p->mu);
+  std::unique_lock<std::mutex> lk(p->mu);
   FlameOffloadStatus st = p->check_handle(h, "ActivationOffloadPool::discard");
   if (st != FLAME_OFFLOAD_OK) return st;
   Slot& s = p->slots[h.slot];
+  if (s.issue == Issue::Queued) {  // never enqueued: nothing was written
+    p->queue.erase(std::find(p->queue.begin(), p->queue.end(), (size_t)h.slot));
+    s.plan.reset();
+    s.issue = Issue::Done;
+    s.state = SlotState::Idle;
+    p->release_chunks_unwritten(s);
+    p->free_stack.push_back(h.slot);
+    p->stats.pushes_cancelled++;
+    p->stats.pushes_queued = p->queue.size();
+    p->stats.host_chunks_free = p->free_chunks.size();
+    return FLAME_OFFLOAD_OK;
+  }
+  if (s.issue == Issue::Issuing) {
+    st = wait_issued(p, lk, h.slot, "discard");
+    if (st != FLAME_OFFLOAD_OK) return st;
+  }
   s.state = SlotState::Idle;
   // An offload that is still writing these chunks runs on the D2H stream, the
   // stream every later offload into them is queued on, so reuse stays ordered.
@@ -606,12 +819,27 @@ FlameOffloadStatus flame_offload_pool_wait_ready(FlameOffloadPool* p, size_t slo
 
 FlameOffloadStatus flame_offload_pool_clear(FlameOffloadPool* p) {
   if (!p) return fail(FLAME_OFFLOAD_ERR_INVALID, "clear: null pool");
-  std::lock_guard<std::mutex> lk(p->mu);
+  std::unique_lock<std::mutex> lk(p->mu);
+  for (size_t i = 0; i < p->slots.size(); ++i) {  // an offload the pool's thread is enqueueing right now finishes first
+    if (p->slots[i].issue == Issue::Issuing) {
+      FlameOffloadStatus st = wait_issued(p, lk, i, "clear");
+      if (st != FLAME_OFFLOAD_OK) return st;
+    }
+  }
   for (size_t i = 0; i < p->slots.size(); ++i) {
     Slot& s = p->slots[i];
     s.state = SlotState::Idle;
-    p->release_chunks(s, s.h2d_done.recorded ? (int32_t)i : -1);
+    if (s.issue == Issue::Queued) {
+      s.plan.reset();
+      s.issue = Issue::Done;
+      p->release_chunks_unwritten(s);
+      p->stats.pushes_cancelled++;
+    } else {
+      p->release_chunks(s, s.h2d_done.recorded ? (int32_t)i : -1);
+    }
   }
+  p->queue.clear();
+  p->stats.pushes_queued = 0;
   p->free_stack.clear();
   for (size_t i = p->num_slots; i-- > 0;) p->free_stack.push_back(i);
   p->epoch += 1;
@@ -628,6 +856,11 @@ int flame_offload_pool_source_released(FlameOffloadPool* p, FlameOffloadHandle h
     return -(int)FLAME_OFFLOAD_ERR_STATE;
   }
   Slot& s = p->slots[h.slot];
+  if (s.issue != Issue::Done) return 0;  // deferred and not enqueued yet: the source has not been read
+  if (s.failed) {
+    fail(FLAME_OFFLOAD_ERR_CUDA, "source_released: the deferred offload of this slot failed: " + s.error);
+    return -(int)FLAME_OFFLOAD_ERR_CUDA;
+  }
   if (!s.d2h_done.recorded) return 1;
   DeviceGuard guard(p->device);
   cudaError_t e = cudaEventQuery(s.d2h_done.ev);
@@ -650,8 +883,24 @@ FlameOffloadStatus flame_offload_pool_slot_info(FlameOffloadPool* p, FlameOffloa
 
 FlameOffloadStatus flame_offload_pool_synchronize(FlameOffloadPool* p, double timeout_s) {
   if (!p) return fail(FLAME_OFFLOAD_ERR_INVALID, "synchronize: null pool");
+  const auto t0 = std::chrono::steady_clock::now();
+  if (p->deferred) {  // queued offloads first (unless they are being held back), then what the streams hold
+    std::unique_lock<std::mutex> lk(p->mu);
+    const auto deadline = t0 + std::chrono::duration_cast<std::chrono::steady_clock::duration>(std::chrono::duration<double>(timeout_s));
+    auto busy = [&] {
+      if (!p->hold && !p->queue.empty()) return true;
+      for (auto& s : p->slots) if (s.issue == Issue::Issuing) return true;
+      return false;
+    };
+    while (busy()) {
+      if (std::chrono::steady_clock::now() >= deadline)
+        return fail(FLAME_OFFLOAD_ERR_TIMEOUT, "synchronize: deferred offloads still queued after the timeout");
+      p->cv_issued.wait_for(lk, std::chrono::milliseconds(1));
+    }
+  }
+  const double left = timeout_s - std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
   DeviceGuard guard(p->device);
-  return poll_streams(p, timeout_s);
+  return poll_streams(p, std::max(left, 0.001));
 }
 
 FlameOffloadStatus flame_offload_pool_read_slot(FlameOffloadPool* p, FlameOffloadHandle h, void* codes_out, void* scales_out, double timeout_s) {
@@ -660,6 +909,11 @@ FlameOffloadStatus flame_offload_pool_read_slot(FlameOffloadPool* p, FlameOffloa
   FlameOffloadStatus st = p->check_handle(h, "read_slot");
   if (st != FLAME_OFFLOAD_OK) return st;
   Slot& s = p->slots[h.slot];
+  if (s.issue != Issue::Done) {
+    st = wait_issued(p, lk, h.slot, "read_slot");
+    if (st != FLAME_OFFLOAD_OK) return st;
+  }
+  if (s.failed) return fail(FLAME_OFFLOAD_ERR_CUDA, "read_slot: the deferred offload of this slot failed: " + s.error);
   DeviceGuard guard(p->device);
   st = poll_event(s.d2h_done.ev, timeout_s, "read_slot: waiting for the offload");
   if (st != FLAME_OFFLOAD_OK) return st;

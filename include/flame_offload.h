@@ -191,6 +191,14 @@ typedef struct {
                                  50 % and more; 1-2 MiB pieces leave gaps that cut this to ~10-20 % at ~85 %
                                  of the copy rate.  Use small pieces when offload overlaps training compute. */
   uint64_t h2d_piece_bytes;   /* the same for host-to-device copies; 0 = whole chunk */
+  uint64_t deferred_inflight_bytes; /* 0 = push() enqueues its copies at once (the reference's behaviour).  > 0 = deferred
+                                 offload: push() only queues the tensor; a thread owned by the pool enqueues
+                                 compress + device-to-host work in push order while less than this many pinned
+                                 bytes are in flight.  A tensor whose turn has not come when backward needs it
+                                 is still on the device: flame_offload_pool_cancel() takes it out of the queue
+                                 and the caller uses the source as it is, so the link never holds backward up
+                                 with round trips that free no memory.  About one block's stored bytes
+                                 (1-4 x 100 MB) keeps the link busy. */
 } FlameOffloadPoolConfig;
 
 typedef struct {
@@ -201,6 +209,8 @@ typedef struct {
   uint64_t codec_launches;                      /* compress + dequantise kernel launches */
   uint64_t host_chunks_total, host_chunks_free;
   uint64_t push_rejected_full;                  /* pushes refused: no slot or no pinned chunk left */
+  uint64_t pushes_cancelled;                    /* deferred pushes taken back before their copies were enqueued */
+  uint64_t pushes_queued;                       /* deferred pushes waiting for their turn right now */
 } FlameOffloadStats;
 
 /* new(device, num_slots, max_bytes, compression): src/activation_offload.rs:365-427.
@@ -239,6 +249,16 @@ FlameOffloadStatus flame_offload_pool_push(FlameOffloadPool* pool, const void* s
 FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* pool, FlameOffloadHandle handle, void* dst_device, size_t dst_bytes, void* compute_stream, unsigned int flags);
 /* Makes `stream` wait for the most recent restore issued from `slot`. */
 FlameOffloadStatus flame_offload_pool_wait_ready(FlameOffloadPool* pool, size_t slot, void* stream);
+
+/* Deferred offload only (deferred_inflight_bytes > 0).  1: the tensor was still waiting for its turn; its slot
+ * and chunks are free again, nothing was or will be read from the source, which the caller goes on using.
+ * 0: its copies are already enqueued (or the pool is not deferred): restore it with pull_into as usual.
+ * Negative: -FlameOffloadStatus (stale or invalid handle). */
+int flame_offload_pool_cancel(FlameOffloadPool* pool, FlameOffloadHandle handle);
+/* Deferred offload only: while `on` is non-zero the pool's thread enqueues nothing new (backward has begun:
+ * what is still queued is about to be needed and will be cancelled); tensors pulled while queued are still
+ * enqueued at once.  0 resumes. */
+FlameOffloadStatus flame_offload_pool_hold(FlameOffloadPool* pool, int on);
 
 /* Gives the slot of `handle` back without restoring it (the reference releases
  * the slots of an abandoned block by pulling every handle,

@@ -153,6 +153,39 @@ def test_restore_arena_serves_destinations_and_gets_them_back(cuda_device, model
         ckpt.set_restore_arena(None)
 
 
+def test_deferred_pool_uses_queued_activations_in_place(cuda_device, model_and_input):
+    """A deferred pool with a tiny in-flight budget: most of the blocks' activations are still queued when backward
+    reaches them and are used where they are; the rest come back from the host.  Gradients are bit-identical."""
+    model, x = model_and_input
+    want = _grads(model, x, ["resident"] * 4)
+    pool = ActivationOffloadPool(cuda_device, 64, 2 * 1024 * 2048 * 2 * 2, OffloadCompression.NONE, chunk_bytes=1 << 20,
+                                 deferred_inflight_bytes=1 << 20)
+    ckpt.set_activation_offload_pool(pool)
+    for _ in range(3):
+        got = _grads(model, x, ["offload"] * 4)
+        assert all(torch.equal(a, b) for a, b in zip(want, got))
+        assert pool.in_flight() == 0
+    st = pool.stats()
+    assert st["pushes_cancelled"] + st["pulls"] == st["pushes"] and st["pushes_queued"] == 0
+    assert st["host_chunks_free"] == st["host_chunks_total"]
+    # the same with int8: cancelled tensors are exact, restored ones quantised, so gradients are close
+    ckpt.clear_activation_offload_pool()
+    pool8 = ActivationOffloadPool(cuda_device, 64, 2 * 1024 * 2048 * 2 * 2, OffloadCompression.INT8_B128, chunk_bytes=1 << 20,
+                                  deferred_inflight_bytes=8 << 20)
+    ckpt.set_activation_offload_pool(pool8)
+    got = _grads(model, x, ["offload"] * 4)
+    for a, b in zip(want, got):
+        assert (a.float() - b.float()).norm() / a.float().norm().clamp_min(1e-12) < 0.05
+    # a graph dropped without backward gives queued slots back as well
+    y = x.clone().requires_grad_(True)
+    for blk in model:
+        y = ckpt.checkpoint_offload([y], blk, min_bytes=1 << 12)
+    del y
+    import gc
+    gc.collect()
+    assert pool8.in_flight() == 0
+
+
 def test_without_a_pool_checkpoint_offload_is_checkpoint(cuda_device, model_and_input):
     model, x = model_and_input
     ckpt.clear_activation_offload_pool()

@@ -265,6 +265,111 @@ def test_random_interleaving_of_pushes_and_pulls(cuda_device, mode):
     assert pool.in_flight() == 0
 
 
+# ---- deferred offload: queued tensors, cancel, hold ---------------------------------------------------
+
+def test_deferred_offload_queue_cancel_and_hold(cuda_device):
+    pool = ActivationOffloadPool(cuda_device, 6, 1 << 20, INT8B, chunk_bytes=64 << 10, deferred_inflight_bytes=1 << 20)
+    bits = [synthetic.normal_with_outliers(40000 + 1000 * i, seed=50 + i) for i in range(6)]
+    want = [capi.dequant_int8_b128(*capi.quant_int8_b128(b)) for b in bits]
+    xs = [G.to_dev(b, cuda_device) for b in bits]
+    assert pool.cancel(pool.push(xs[0])) is None or True      # may or may not have been enqueued yet: both are legal
+    pool.synchronize(10.0)
+    pool.clear()
+    pool.hold_offloads(True)                                    # nothing is enqueued from here on
+    hs = [pool.push(x) for x in xs]
+    st = pool.stats()
+    assert st["pushes_queued"] == 6 and pool.in_flight() == 6
+    assert not pool.source_released(hs[0])
+    pool.synchronize(5.0)                                       # held tensors do not count as pending work
+    # cancel: the source comes back untouched, the slot and its chunks are free
+    src = pool.cancel(hs[5])
+    assert src is not None and src.data_ptr() == xs[5].data_ptr() and pool.in_flight() == 5
+    with pytest.raises(InvalidOperation):
+        pool.pull(hs[5])
+    # a pull of a queued tensor sends it out at once, hold or not
+    out = pool.pull(hs[4])
+    torch.cuda.synchronize()
+    assert np.array_equal(G.bits_of(out), want[4])
+    assert pool.cancel(hs[3]) is not None
+    pool.discard(hs[2])                                         # a queued tensor can be discarded too
+    st = pool.stats()
+    assert st["pushes_cancelled"] == 3 and st["pushes_queued"] == 2 and pool.in_flight() == 2
+    # release the hold: the rest goes out in push order
+    pool.hold_offloads(False)
+    pool.synchronize(10.0)
+    assert pool.stats()["pushes_queued"] == 0 and pool.source_released(hs[0]) and pool.source_released(hs[1])
+    assert pool.cancel(hs[0]) is None                           # too late: it is on the host now
+    for i in (1, 0):
+        out = pool.pull(hs[i])
+        torch.cuda.synchronize()
+        assert np.array_equal(G.bits_of(out), want[i])
+    st = pool.stats()
+    assert pool.in_flight() == 0 and st["host_chunks_free"] == st["host_chunks_total"]
+    # clear() with queued tensors
+    pool.hold_offloads(True)
+    hs = [pool.push(x) for x in xs[:3]]
+    pool.clear()
+    assert pool.in_flight() == 0 and pool.stats()["pushes_queued"] == 0
+    with pytest.raises(InvalidOperation):
+        pool.pull(hs[0])
+    pool.hold_offloads(False)
+    h = pool.push(xs[0])
+    out = pool.pull(h)
+    torch.cuda.synchronize()
+    assert np.array_equal(G.bits_of(out), want[0])
+    pool.close()
+
+
+@pytest.mark.parametrize("mode", [INT8B, NONE])
+def test_deferred_random_interleaving_with_cancels(cuda_device, mode):
+    """The random schedule above on a deferred pool with a small in-flight budget; a third of the restores try
+    cancel() first.  A cancelled tensor must be the source itself; everything else must equal the oracle."""
+    rng = np.random.default_rng(7)
+    sizes = [int(v) for v in rng.integers(1000, 400000, size=32)]
+    pool = ActivationOffloadPool(cuda_device, 8, 2 * max(sizes), mode, chunk_bytes=64 << 10, staging_tiles=2, tile_chunks=3,
+                                 deferred_inflight_bytes=256 << 10)
+    want, live, done = {}, {}, []
+    next_i = cancelled = 0
+    for step in range(400):
+        do_push = next_i < len(sizes) and (not live or rng.random() < 0.55)
+        if do_push:
+            bits = synthetic.normal_with_outliers(sizes[next_i], seed=4000 + next_i)
+            x = G.to_dev(bits, cuda_device)
+            try:
+                h = pool.push(x)
+            except InvalidOperation:
+                do_push = False
+            else:
+                want[next_i] = (bits, capi.dequant_int8_b128(*capi.quant_int8_b128(bits)) if mode == INT8B else bits)
+                live[h] = next_i
+                next_i += 1
+                del x
+        if not do_push and live:
+            h = list(live)[int(rng.integers(0, len(live)))]
+            i = live.pop(h)
+            src = pool.cancel(h) if rng.random() < 0.34 else None
+            if src is not None:
+                cancelled += 1
+                done.append((src, i, True))
+            else:
+                dst = torch.full((sizes[i],), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+                pool.pull_into(h, dst)
+                done.append((dst, i, False))
+        if step % 50 == 25:
+            pool.hold_offloads(bool((step // 50) % 2))
+        if not live and next_i >= len(sizes):
+            break
+    pool.hold_offloads(False)
+    torch.cuda.synchronize()
+    assert len(done) == len(sizes)
+    for t, i, was_cancelled in done:
+        assert np.array_equal(G.bits_of(t), want[i][0] if was_cancelled else want[i][1]), (i, was_cancelled)
+    st = pool.stats()
+    assert st["pushes_cancelled"] == cancelled and st["pulls"] + cancelled == st["pushes"] == len(sizes)
+    assert pool.in_flight() == 0 and st["host_chunks_free"] == st["host_chunks_total"]
+    pool.close()
+
+
 def test_host_budget_smaller_than_slots_rejects_then_recovers(cuda_device):
     n = 1 << 18
     x = torch.randn(n, device=cuda_device).to(torch.bfloat16)
