@@ -120,6 +120,7 @@ SIGNATURES = {
     "flame_offload_inject_fault": (None, [_i, _i]),
     "flame_offload_pool_cancel": (_i, [_vp, Handle]),
     "flame_offload_pool_hold": (_i, [_vp, _i]),
+    "flame_offload_pool_hold_after": (_i, [_vp, _vp]),
     "flame_restore_arena_create": (_vp, [_vp, _sz, _sz]),
     "flame_restore_arena_destroy": (None, [_vp]),
     "flame_restore_arena_alloc": (_i, [_vp, _sz, C.POINTER(_vp), C.POINTER(C.c_uint64)]),

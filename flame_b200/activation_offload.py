@@ -201,6 +201,11 @@ class ActivationOffloadPool:
         cancelled or pulled)."""
         raise_for_status(self._lib.flame_offload_pool_hold(self._h, 1 if on else 0), _lib.last_error())
 
+    def hold_offloads_after_current_work(self) -> None:
+        """Deferred pools: the hold begins when the device has finished what the current stream holds now (called when
+        the host starts backward, it stops new offloads once the device has finished the forward pass)."""
+        raise_for_status(self._lib.flame_offload_pool_hold_after(self._h, self._stream()), _lib.last_error())
+
     def discard(self, handle: OffloadHandle) -> None:
         """Frees the slot of `handle` without restoring it (an abandoned block, src/autograd.rs:1742-1769)."""
         raise_for_status(self._lib.flame_offload_pool_discard(self._h, handle._c()), _lib.last_error())

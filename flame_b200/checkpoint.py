@@ -269,11 +269,15 @@ class _Scheduler:
 
     @staticmethod
     def _hold(on: bool) -> None:
-        # deferred pools: nothing new goes out once backward has begun; what is still queued is used in place
+        # deferred pools: nothing new goes out once the DEVICE has finished the forward pass (the host is ahead of
+        # it when it gets here); what is still queued when backward reaches it is used in place
         pool = _ACTIVATION_POOL
         if pool is not None and getattr(pool, "deferred", False):
             try:
-                pool.hold_offloads(on)
+                if on:
+                    pool.hold_offloads_after_current_work()
+                else:
+                    pool.hold_offloads(False)
             except OffloadError:
                 pass
 

@@ -186,6 +186,8 @@ struct FlameOffloadPool {
   std::deque<size_t> queue;                                // slots whose offload has not been enqueued, push order
   std::deque<std::pair<cudaEvent_t, uint64_t>> inflight;   // (d2h_done, pinned bytes) of enqueued offloads, oldest first
   bool hold = false, stop = false;
+  Event hold_after;          // the hold begins when this event (recorded on the caller's stream) has completed
+  bool hold_armed = false;
   std::thread worker;
   std::condition_variable cv_work, cv_issued;
 
@@ -336,13 +338,17 @@ void deferred_worker(FlameOffloadPool* p) {
       p->inflight_bytes -= p->inflight.front().second;
       p->inflight.pop_front();
     }
+    if (p->hold_armed && cudaEventQuery(p->hold_after.ev) != cudaErrorNotReady) {
+      p->hold = true;
+      p->hold_armed = false;
+    }
     bool take = false;
     if (!p->queue.empty()) {
       const Slot& c = p->slots[p->queue.front()];
       take = c.urgent || (!p->hold && p->inflight_bytes < p->inflight_budget);
     }
     if (!take) {
-      if (p->queue.empty() && p->inflight.empty()) p->cv_work.wait(lk);
+      if (p->queue.empty() && p->inflight.empty() && !p->hold_armed) p->cv_work.wait(lk);
       else p->cv_work.wait_for(lk, std::chrono::microseconds(100));
       continue;
     }
@@ -440,6 +446,7 @@ cudaError_t enqueue_pull(FlameOffloadPool& p, Slot& s, uint8_t* dst, cudaStream_
 }
 
 void destroy_pool(FlameOffloadPool* p) {
+  p->hold_after.destroy();
   for (auto& s : p->slots) { s.producer.destroy(); s.d2h_done.destroy(); s.consumer.destroy(); s.h2d_done.destroy(); s.ready.destroy(); }
   for (auto* ring : {&p->out_tiles, &p->in_tiles})
     for (auto& t : *ring) { t.full.destroy(); t.free_.destroy(); if (t.dev) cudaFree(t.dev); }
@@ -591,6 +598,7 @@ FlameOffloadPool* flame_offload_pool_create(size_t num_slots, size_t max_bytes, 
   }
   if (!ok) { destroy_pool(p); return nullptr; }
   if (cfg.deferred_inflight_bytes) {
+    if (p->hold_after.create() != cudaSuccess) { fail(FLAME_OFFLOAD_ERR_CUDA, "cudaEventCreate(hold_after)"); destroy_pool(p); return nullptr; }
     p->deferred = true;
     p->inflight_budget = cfg.deferred_inflight_bytes;
     p->worker = std::thread(deferred_worker, p);
@@ -771,6 +779,19 @@ FlameOffloadStatus flame_offload_pool_hold(FlameOffloadPool* p, int on) {
   if (!p) return fail(FLAME_OFFLOAD_ERR_INVALID, "hold: null pool");
   std::lock_guard<std::mutex> lk(p->mu);
   p->hold = on != 0;
+  p->hold_armed = false;
+  p->cv_work.notify_all();
+  return FLAME_OFFLOAD_OK;
+}
+
+FlameOffloadStatus flame_offload_pool_hold_after(FlameOffloadPool* p, void* stream) {
+  if (!p) return fail(FLAME_OFFLOAD_ERR_INVALID, "hold_after: null pool");
+  std::lock_guard<std::mutex> lk(p->mu);
+  if (!p->deferred) return FLAME_OFFLOAD_OK;
+  DeviceGuard guard(p->device);
+  cudaError_t e = p->hold_after.record((cudaStream_t)stream);
+  if (e != cudaSuccess) return fail_cuda(e, "hold_after: cudaEventRecord");
+  p->hold_armed = true;
   p->cv_work.notify_all();
   return FLAME_OFFLOAD_OK;
 }

@@ -204,7 +204,8 @@ def _block_times(model, x, cos, sin):
 COPY_PIECE_BYTES = 2 << 20  # copies overlapped with training are issued in 2 MiB pieces (see FlameOffloadPoolConfig.d2h_piece_bytes)
 
 
-def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20, arms=("offload_int8", "offload_bf16", "recompute"),
+def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
+                     arms=("offload_int8", "deferred", "offload_bf16", "recompute"),
                      resident_budget_blocks: int = 8) -> dict:
     """Step time of each arm relative to resident activations.  Returns a JSON-ready dict."""
     torch.manual_seed(0)
@@ -224,13 +225,13 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20, 
     out["resident"] = {"ms_per_step": round(base_ms, 3), "peak_mem_gb": round(base_mem / 1e9, 2),
                        "held_after_forward_gb": round(base_held / 1e9, 2)}
 
-    def run_arm(name, decisions, mode):
+    def run_arm(name, decisions, mode, deferred_bytes=0, d2h_piece=COPY_PIECE_BYTES):
         pool = None
         if mode is not None:
             # sized for every block offloaded at once; the plan decides how many really are
             sizes = [saved_bytes] * blocks
-            pool = ActivationOffloadPool(dev, 16 * blocks, max(saved_bytes, 1 << 20), mode, d2h_piece_bytes=COPY_PIECE_BYTES,
-                                         h2d_piece_bytes=2 * COPY_PIECE_BYTES,
+            pool = ActivationOffloadPool(dev, 16 * blocks, max(saved_bytes, 1 << 20), mode, d2h_piece_bytes=d2h_piece,
+                                         h2d_piece_bytes=2 * COPY_PIECE_BYTES, deferred_inflight_bytes=deferred_bytes,
                                          host_budget_bytes=int(ActivationOffloadPool.host_bytes_needed(sizes, mode) * 1.5))
             ckpt.set_activation_offload_pool(pool)
         model.decisions = decisions
@@ -244,6 +245,10 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20, 
                 n = max(1, steps + warmup + 1)
                 res["offloaded_gb_per_step"] = round(st["bytes_logical_out"] / n / 1e9, 3)
                 res["link_gb_per_step"] = round(st["bytes_link_out"] / n / 1e9, 3)
+                if deferred_bytes:
+                    res["tensors_used_in_place_per_step"] = round(st["pushes_cancelled"] / n, 1)
+                    res["tensors_pushed_per_step"] = round(st["pushes"] / n, 1)
+                    res["deferred_inflight_bytes"] = int(deferred_bytes)
         finally:
             model.decisions = None
             if pool is not None:
@@ -267,6 +272,14 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20, 
             curve.append({"offloaded_blocks": k, "overhead_pct": r["overhead_pct"], "ms_per_step": r["ms_per_step"],
                           "held_after_forward_gb": r["held_after_forward_gb"], "offloaded_gb_per_step": r.get("offloaded_gb_per_step")})
         out["offload_int8_curve"] = curve
+    if "deferred" in arms:
+        # Every block handed to the pool; a deferred pool sends out what the link carries beside the forward pass
+        # and backward uses the rest where it is.  No plan, no budget: the link decides.
+        one_block = int(saved_bytes * 0.52)
+        out["offload_int8_all_deferred"] = run_arm("offload_int8_all_deferred", [Decision.OFFLOAD_INT8] * blocks,
+                                                   OffloadCompression.INT8_B128, deferred_bytes=one_block)
+        out["offload_bf16_all_deferred"] = run_arm("offload_bf16_all_deferred", [Decision.OFFLOAD_BF16] * blocks,
+                                                   OffloadCompression.NONE, deferred_bytes=saved_bytes)
     if "offload_bf16" in arms:
         p = plan_blocks(blk, d2h_gbs=link.d2h_gbs, h2d_gbs=link.h2d_gbs, device_budget_bytes=budget, offload=Decision.OFFLOAD_BF16)
         out["offload_bf16_planned"] = run_arm("offload_bf16_planned", p.decisions, OffloadCompression.NONE)

@@ -259,6 +259,12 @@ int flame_offload_pool_cancel(FlameOffloadPool* pool, FlameOffloadHandle handle)
  * what is still queued is about to be needed and will be cancelled); tensors pulled while queued are still
  * enqueued at once.  0 resumes. */
 FlameOffloadStatus flame_offload_pool_hold(FlameOffloadPool* pool, int on);
+/* Deferred offload only: the hold begins when the work submitted to `stream` so far has finished on the device.
+ * The host runs ahead of the device, so "backward has begun" on the host says little; called when the host
+ * starts backward, this stops new offloads when the DEVICE has finished the forward pass (after which sending
+ * tensors out no longer lowers the peak), while tensors the host reaches earlier are cancelled as usual.
+ * flame_offload_pool_hold(pool, 0) ends it. */
+FlameOffloadStatus flame_offload_pool_hold_after(FlameOffloadPool* pool, void* stream);
 
 /* Gives the slot of `handle` back without restoring it (the reference releases
  * the slots of an abandoned block by pulling every handle,
