@@ -201,11 +201,15 @@ def _block_times(model, x, cos, sin):
     return fwd, bwd, saved
 
 
-COPY_PIECE_BYTES = 2 << 20  # copies overlapped with training are issued in 2 MiB pieces (see FlameOffloadPoolConfig.d2h_piece_bytes)
+# Copies overlapped with training are issued in pieces (see FlameOffloadPoolConfig.d2h_piece_bytes): 2 MiB when the
+# training thread issues them itself, 1 MiB for device-to-host copies that the pool's own thread issues (deferred pools).
+COPY_PIECE_BYTES = 2 << 20
+DEFERRED_D2H_PIECE_BYTES = 1 << 20
+ISSUE_OFF_THREAD = 1 << 40   # a deferred pool with this in-flight budget never queues: it only moves the issuing off the training thread
 
 
 def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
-                     arms=("offload_int8", "deferred", "offload_bf16", "recompute"),
+                     arms=("offload_int8", "deferred", "offload_bf16", "recompute"), custom=(),
                      resident_budget_blocks: int = 8) -> dict:
     """Step time of each arm relative to resident activations.  Returns a JSON-ready dict."""
     torch.manual_seed(0)
@@ -225,13 +229,13 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
     out["resident"] = {"ms_per_step": round(base_ms, 3), "peak_mem_gb": round(base_mem / 1e9, 2),
                        "held_after_forward_gb": round(base_held / 1e9, 2)}
 
-    def run_arm(name, decisions, mode, deferred_bytes=0, d2h_piece=COPY_PIECE_BYTES):
+    def run_arm(name, decisions, mode, deferred_bytes=0, d2h_piece=COPY_PIECE_BYTES, **pool_kwargs):
         pool = None
         if mode is not None:
             # sized for every block offloaded at once; the plan decides how many really are
             sizes = [saved_bytes] * blocks
             pool = ActivationOffloadPool(dev, 16 * blocks, max(saved_bytes, 1 << 20), mode, d2h_piece_bytes=d2h_piece,
-                                         h2d_piece_bytes=2 * COPY_PIECE_BYTES, deferred_inflight_bytes=deferred_bytes,
+                                         h2d_piece_bytes=2 * COPY_PIECE_BYTES, deferred_inflight_bytes=deferred_bytes, **pool_kwargs,
                                          host_budget_bytes=int(ActivationOffloadPool.host_bytes_needed(sizes, mode) * 1.5))
             ckpt.set_activation_offload_pool(pool)
         model.decisions = decisions
@@ -261,14 +265,16 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
     budget = resident_budget_blocks * saved_bytes
     if "offload_int8" in arms:
         p = plan_blocks(blk, d2h_gbs=link.d2h_gbs, h2d_gbs=link.h2d_gbs, device_budget_bytes=budget, offload=Decision.OFFLOAD_INT8)
-        out["offload_int8_planned"] = run_arm("offload_int8_planned", p.decisions, OffloadCompression.INT8_B128)
+        out["offload_int8_planned"] = run_arm("offload_int8_planned", p.decisions, OffloadCompression.INT8_B128,
+                                              deferred_bytes=ISSUE_OFF_THREAD, d2h_piece=DEFERRED_D2H_PIECE_BYTES)
         out["offload_int8_planned"]["plan_est_stall_ms"] = round(p.est_stall_ms, 2)
         out["offload_int8_planned"]["plan_est_interference_ms"] = round(p.est_interference_ms, 2)
         out["offload_int8_all"] = run_arm("offload_int8_all", [Decision.OFFLOAD_INT8] * blocks, OffloadCompression.INT8_B128)
         # overhead against how much is offloaded: the first k blocks go out, the rest stay resident
         curve = []
         for k in sorted({blocks * 2 // 5, blocks * 3 // 5, blocks * 3 // 4}):
-            r = run_arm(f"int8_{k}", [Decision.OFFLOAD_INT8] * k + [Decision.RESIDENT] * (blocks - k), OffloadCompression.INT8_B128)
+            r = run_arm(f"int8_{k}", [Decision.OFFLOAD_INT8] * k + [Decision.RESIDENT] * (blocks - k), OffloadCompression.INT8_B128,
+                        deferred_bytes=ISSUE_OFF_THREAD, d2h_piece=DEFERRED_D2H_PIECE_BYTES)
             curve.append({"offloaded_blocks": k, "overhead_pct": r["overhead_pct"], "ms_per_step": r["ms_per_step"],
                           "held_after_forward_gb": r["held_after_forward_gb"], "offloaded_gb_per_step": r.get("offloaded_gb_per_step")})
         out["offload_int8_curve"] = curve
@@ -277,19 +283,34 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
         # and backward uses the rest where it is.  No plan, no budget: the link decides.
         one_block = int(saved_bytes * 0.52)
         out["offload_int8_all_deferred"] = run_arm("offload_int8_all_deferred", [Decision.OFFLOAD_INT8] * blocks,
-                                                   OffloadCompression.INT8_B128, deferred_bytes=one_block)
+                                                   OffloadCompression.INT8_B128, deferred_bytes=one_block, d2h_piece=DEFERRED_D2H_PIECE_BYTES)
         out["offload_bf16_all_deferred"] = run_arm("offload_bf16_all_deferred", [Decision.OFFLOAD_BF16] * blocks,
-                                                   OffloadCompression.NONE, deferred_bytes=saved_bytes)
+                                                   OffloadCompression.NONE, deferred_bytes=saved_bytes, d2h_piece=DEFERRED_D2H_PIECE_BYTES)
     if "offload_bf16" in arms:
         p = plan_blocks(blk, d2h_gbs=link.d2h_gbs, h2d_gbs=link.h2d_gbs, device_budget_bytes=budget, offload=Decision.OFFLOAD_BF16)
-        out["offload_bf16_planned"] = run_arm("offload_bf16_planned", p.decisions, OffloadCompression.NONE)
+        out["offload_bf16_planned"] = run_arm("offload_bf16_planned", p.decisions, OffloadCompression.NONE,
+                                              deferred_bytes=ISSUE_OFF_THREAD, d2h_piece=DEFERRED_D2H_PIECE_BYTES)
         out["offload_bf16_all"] = run_arm("offload_bf16_all", [Decision.OFFLOAD_BF16] * blocks, OffloadCompression.NONE)
     if "recompute" in arms:
         out["recompute"] = run_arm("recompute", [Decision.RECOMPUTE] * blocks, None)
+    # experiments: (name, leading blocks offloaded, "int8" | "bf16", deferred_inflight_bytes, d2h_piece_bytes)
+    for name, k, codec, deferred_bytes, piece, *rest in custom:
+        dec = Decision.OFFLOAD_INT8 if codec == "int8" else Decision.OFFLOAD_BF16
+        mode = OffloadCompression.INT8_B128 if codec == "int8" else OffloadCompression.NONE
+        out[name] = run_arm(name, [dec] * k + [Decision.RESIDENT] * (blocks - k), mode, deferred_bytes=deferred_bytes, d2h_piece=piece,
+                            **(rest[0] if rest else {}))
     out["resident_budget_blocks"] = resident_budget_blocks
-    out["copy_piece_bytes"] = COPY_PIECE_BYTES
+    out["copy_piece_bytes"] = {"d2h": DEFERRED_D2H_PIECE_BYTES, "d2h_immediate_pools": COPY_PIECE_BYTES, "h2d": 2 * COPY_PIECE_BYTES}
+    out["arms"] = {"planned / curve": "pool issues offloads from its own thread at once (deferred pool, unbounded in-flight budget)",
+                   "all": "immediate pool: every block sent out and fetched back, as the reference's pool would",
+                   "all_deferred": "deferred pool, one block in flight: sends out what the link carries beside the forward pass, the "
+                                   "rest is used where it is (tensors_used_in_place_per_step)"}
     # the baseline again, last: run-to-run drift of the step time shows up as the difference to the first measurement
     model.decisions = None
     again_ms, _, _ = _time_steps(model, opt, x, cos, sin, steps, 1)
     out["resident"]["ms_per_step_rerun"] = round(again_ms, 3)
+    mean_base = 0.5 * (base_ms + again_ms)
+    for v in list(out.values()) + list(out.get("offload_int8_curve", [])):
+        if isinstance(v, dict) and "overhead_pct" in v:
+            v["overhead_pct_vs_mean_baseline"] = round(100.0 * (v["ms_per_step"] - mean_base) / mean_base, 2)
     return out
