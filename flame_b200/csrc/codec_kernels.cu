@@ -431,15 +431,27 @@ struct CompressOccupancy { static constexpr int kMinBlocks = 5; };
 
 template <int kCodec, bool kFlag, bool kStaged>
 __global__ void __launch_bounds__(kThreads, CompressOccupancy<kCodec>::kMinBlocks)
-compress_b128_kernel(const __grid_constant__ JobTable T, unsigned rounds) {
+compress_b128_kernel(const __grid_constant__ JobTable T, unsigned rounds, unsigned multi_ctas, unsigned multi_tiles) {
   // staged variant only: two buffers of (codes tile | scales tile) in dynamic shared memory
   extern __shared__ __align__(128) uint8_t smem_tiles[];
   const int tid = threadIdx.x;
   int buf = 0;
   uint32_t j = 0;
 
+  // Blocks below multi_ctas take `rounds` tiles each out of the first multi_tiles (tile k*multi_ctas + b in
+  // round k, so blocks that run side by side read neighbouring tiles); the blocks after them take one tile
+  // each of the rest.  Blocks start in index order, so the launch ends on short blocks and the SMs run dry
+  // within one tile's time of each other instead of one long block's.
+  const bool multi = blockIdx.x < multi_ctas;
   for (unsigned k = 0; k < rounds; ++k) {
-    const uint32_t g = k * gridDim.x + blockIdx.x;
+    uint32_t g;
+    if (multi) {
+      g = k * multi_ctas + blockIdx.x;
+      if (g >= multi_tiles) break;
+    } else {
+      if (k) break;
+      g = multi_tiles + (blockIdx.x - multi_ctas);
+    }
     if (g >= T.total_tiles) break;
     while (j + 1 < T.count && g >= T.jobs[j + 1].tile0) ++j;
     const CodecJob& J = T.jobs[j];
@@ -732,6 +744,7 @@ int resident_ctas_per_sm(K kernel, size_t dyn_smem = 0) {
 // A grid in which every thread block takes the same number of consecutive tiles
 // and all blocks are resident at once: no second wave, no ragged last round.
 struct Grid { int ctas; unsigned tiles_per_cta; };
+constexpr int kTaperWaves = 2;  // waves of single-tile blocks at the end of an oversubscribed compress launch
 int env_int(const char* name) {
   const char* e = getenv(name);
   return e ? (atoi(e) < 1 ? 1 : atoi(e)) : 0;
@@ -740,7 +753,8 @@ int env_int(const char* name) {
 // of rounds for all, no second wave and no ragged last round.  Large launches: `max_rounds` rounds
 // per block and many more blocks than fit at once, so that the hardware block scheduler evens out
 // SM speed differences, which add up over hundreds of rounds of a static assignment.  The two
-// thresholds were swept on a B200 per kernel kind (compress 16 / 4, dequantise 2 / 2);
+// thresholds were swept on a B200 per kernel kind (compress 8 / 6 with two closing waves of single-tile
+// blocks, dequantise 2 / 2);
 // FLAME_ACT_BALANCE_LIMIT and FLAME_ACT_MAX_ROUNDS override them for tuning.
 Grid grid_balanced(size_t tiles, int ctas_per_sm, int max_ctas, int balance_limit, int max_rounds) {
   static int env_limit = -1, env_rounds = -1;
@@ -805,8 +819,20 @@ template <int kCodec, bool kFlag, bool kStaged>
 cudaError_t launch_compress_table(const JobTable& T, cudaStream_t stream, int max_ctas) {
   auto kern = compress_b128_kernel<kCodec, kFlag, kStaged>;
   const size_t smem = kStaged ? 2 * kStagedBufBytes : 0;
-  const Grid g = grid_balanced(T.total_tiles, resident_ctas_per_sm(kern, smem), max_ctas, 16, 4);
-  kern<<<g.ctas, kThreads, smem, stream>>>(T, g.tiles_per_cta);
+  const int per_sm = resident_ctas_per_sm(kern, smem);
+  const Grid g = grid_balanced(T.total_tiles, per_sm, max_ctas, 8, 6);
+  // Oversubscribed launches (several waves of blocks) end on single-tile blocks: `taper` waves of them.
+  static int taper = -1;
+  if (taper < 0) { const char* e = getenv("FLAME_ACT_TAPER_WAVES"); taper = e ? atoi(e) : kTaperWaves; if (taper < 0) taper = 0; }
+  unsigned ctas = (unsigned)g.ctas, multi_ctas = (unsigned)g.ctas, multi_tiles = T.total_tiles;
+  const size_t resident = (size_t)sm_count() * (size_t)per_sm;
+  const size_t singles = (size_t)taper * resident;
+  if (taper > 0 && g.tiles_per_cta > 1 && (size_t)g.ctas > 2 * resident && T.total_tiles > 2 * singles) {
+    multi_tiles = T.total_tiles - (uint32_t)singles;
+    multi_ctas = (multi_tiles + g.tiles_per_cta - 1) / g.tiles_per_cta;
+    ctas = multi_ctas + (unsigned)singles;
+  }
+  kern<<<ctas, kThreads, smem, stream>>>(T, g.tiles_per_cta, multi_ctas, multi_tiles);
   return cudaGetLastError();
 }
 
