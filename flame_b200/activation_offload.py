@@ -61,6 +61,15 @@ def _dtype_tag(t) -> int:
     raise Unsupported(f"ActivationOffloadPool::push: dtype {t.dtype} not supported (BF16/F32 only)")
 
 
+class _Prepacked:
+    """Keep-alive record of a tensor pushed in compressed form: its device codes and scales."""
+
+    __slots__ = ("codes", "scales", "numel", "shape")
+
+    def __init__(self, codes, scales, numel, shape):
+        self.codes, self.scales, self.numel, self.shape = codes, scales, numel, shape
+
+
 class ActivationOffloadPool:
     def __init__(self, device, num_slots: int, max_bytes: int,
                  compression: OffloadCompression = OffloadCompression.NONE, *,
@@ -156,6 +165,28 @@ class ActivationOffloadPool:
         self._keep_alive[h.slot] = (h, tensor.detach())
         return handle
 
+    def push_packed(self, codes, scales, shape, dtype=None) -> OffloadHandle:
+        """Offload a BF16 tensor of `shape` that its producer already compressed on the device (uint8 `codes`, one per
+        element, and float32 `scales`, one per 128 elements, as flame_act_quant_*_b128 lay them out).  No compress launch;
+        the restore gives BF16 as for any other slot."""
+        torch = self._torch
+        numel = 1
+        for d in shape:
+            numel *= int(d)
+        if codes.dtype != torch.uint8 or scales.dtype != torch.float32 or not codes.is_contiguous() or not scales.is_contiguous():
+            raise InvalidInput("ActivationOffloadPool::push_packed: codes must be contiguous uint8 and scales contiguous float32")
+        if codes.numel() < numel or scales.numel() < (numel + 127) // 128 or codes.device != self.device or scales.device != self.device:
+            raise InvalidInput("ActivationOffloadPool::push_packed: codes / scales do not cover the tensor or live on another device")
+        self._sweep_keep_alive()
+        h = _lib.Handle()
+        st = self._lib.flame_offload_pool_push_packed(self._h, codes.data_ptr(), scales.data_ptr(), numel, self._stream(), C.byref(h))
+        if st != 0:
+            raise_for_status(st, _lib.last_error())
+        self._meta[h.slot] = (tuple(shape), dtype or torch.bfloat16)
+        self._keep_alive.pop(h.slot, None)
+        self._keep_alive[h.slot] = (h, _Prepacked(codes, scales, numel, tuple(shape)))
+        return OffloadHandle(h.slot, h.epoch)
+
     def pull_into(self, handle: OffloadHandle, dst, defer_wait: bool = False, keep: bool = False) -> None:
         """Restore into `dst` (contiguous, same dtype, at least as many bytes).
 
@@ -194,7 +225,19 @@ class ActivationOffloadPool:
         if r == 0:
             return None
         self._meta.pop(handle.slot, None)
-        return self._keep_alive.pop(handle.slot)[1]
+        src = self._keep_alive.pop(handle.slot)[1]
+        if isinstance(src, _Prepacked):
+            # only the compressed form was kept on the device: dequantise it here, without a trip over the link
+            out = self._torch.empty(src.numel, dtype=self._torch.bfloat16, device=self.device)
+            fn = (self._lib.flame_act_dequant_int8_b128 if self.compression == OffloadCompression.INT8_B128
+                  else self._lib.flame_act_dequant_fp8_b128)
+            rc = fn(src.codes.data_ptr(), src.scales.data_ptr(), out.data_ptr(), src.numel, self._stream())
+            if rc != 0:
+                raise CudaError(f"dequantise of a cancelled pre-compressed tensor failed ({rc}): {_lib.last_error()}")
+            src.codes.record_stream(self._torch.cuda.current_stream(self.device))
+            src.scales.record_stream(self._torch.cuda.current_stream(self.device))
+            return out.view(src.shape)
+        return src
 
     def hold_offloads(self, on: bool) -> None:
         """Deferred pools: while on, queued offloads are not enqueued (backward has begun; they are about to be

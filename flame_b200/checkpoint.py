@@ -31,7 +31,8 @@ from typing import Callable, Optional, Sequence
 import torch
 from torch.utils.checkpoint import checkpoint as _torch_checkpoint
 
-from .activation_offload import ActivationOffloadPool
+from . import fused_producers
+from .activation_offload import ActivationOffloadPool, OffloadCompression
 from .errors import InvalidInput, InvalidOperation, OffloadError
 from .policy import Decision
 
@@ -111,14 +112,14 @@ def offloadable(t: torch.Tensor, min_bytes: int) -> bool:
 
 def saved_bytes_of(f: Callable[..., torch.Tensor], inputs: Sequence[torch.Tensor], min_bytes: int = 1 << 20) -> int:
     """BF16 bytes ``checkpoint_offload(inputs, f)`` would push: a dry run of ``f`` with counting hooks."""
-    seen, total = set(), 0
+    seen, total = {}, 0
 
     def pack(t):
         nonlocal total
         if offloadable(t, min_bytes):
             key = (t.data_ptr(), t.numel(), t._version)
             if key not in seen:
-                seen.add(key)
+                seen[key] = t          # held, so that its address cannot be given to another tensor during the run
                 total += t.numel() * 2
         return t
 
@@ -169,6 +170,8 @@ class _Block:
         self.failed = False
         self.bytes_offloaded = 0
         self.restores_issued = False
+        # per-128-block pools: producers that can emit codes beside their output do so while this block runs
+        self.emit = int(pool.compression) if pool.compression in (OffloadCompression.INT8_B128, OffloadCompression.FP8_B128) else 0
 
     # -- forward -----------------------------------------------------------------------------
     def pack(self, t: torch.Tensor):
@@ -185,11 +188,13 @@ class _Block:
         # the same memory is often saved several times under different shapes (a norm output
         # and its 2-D view in the following linear): one offload, many views
         key = (t.data_ptr(), t.numel(), t._version)
-        e = self._by_key.get(key)
-        if e is not None:
-            return _View(e, tuple(base.shape), inverse)
+        hit = self._by_key.get(key)
+        if hit is not None:
+            return _View(hit[0], tuple(base.shape), inverse)
         try:
-            h = self.pool.push(base)
+            pre = fused_producers.take(t) if self.emit else None
+            # a producer with the compress step built in already wrote this tensor's codes: no compress launch
+            h = self.pool.push_packed(pre[0], pre[1], (t.numel(),)) if pre is not None else self.pool.push(base)
         except OffloadError as exc:  # pool exhausted: abandon offload for this block
             log.warning("checkpoint_offload: pool push failed (%s), falling back to recompute; %d handles already pushed",
                         exc, len(self.entries))
@@ -197,7 +202,10 @@ class _Block:
             return t.detach() if t.grad_fn is not None else t
         e = _Entry(h, (t.numel(),), t.dtype, self)
         self.entries.append(weakref.ref(e))
-        self._by_key[key] = e
+        # The source is held until the block's forward ends: if it were freed earlier (the pool lets go of it once
+        # it has been copied out), the allocator could give its address to another tensor of the same size, which
+        # would then be taken for a view of this one.
+        self._by_key[key] = (e, base)
         self._handles.append(h)
         self.bytes_offloaded += t.numel() * 2
         return _View(e, tuple(base.shape), inverse)
@@ -325,7 +333,7 @@ def checkpoint_offload(inputs: Sequence[torch.Tensor], f: Callable[..., torch.Te
             out.register_hook(lambda g, pos=pos: _SCHEDULER.on_backward_reach(pos))
         return out
     block = _Block(pool, len(_SCHEDULER.blocks), min_bytes)
-    with torch.autograd.graph.saved_tensors_hooks(block.pack, block.unpack):
+    with torch.autograd.graph.saved_tensors_hooks(block.pack, block.unpack), fused_producers.emit_codes(block.emit):
         out = f(*inputs)
     block.finish_forward()
     if block.failed:

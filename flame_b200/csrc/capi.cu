@@ -158,6 +158,20 @@ int flame_act_dequant_b128_multi(int codec, const FlameActTensor* tensors, size_
   return multi_entry(false, codec, tensors, count, 0, stream);
 }
 
+int flame_act_rmsnorm_quant_b128(const void* x_bf16, const void* weight_bf16, void* y_bf16, void* codes_u8, void* scales_f32,
+                                 void* rstd_f32, size_t rows, size_t cols, float eps, int codec, unsigned int flags, void* stream) {
+  cudaError_t e = launch_rmsnorm_quant(codec, flags, x_bf16, weight_bf16, y_bf16, codes_u8, scales_f32, rstd_f32, rows, cols, eps, (cudaStream_t)stream);
+  if (e == cudaErrorInvalidValue) set_last_error("flame_act_rmsnorm_quant_b128: needs cols % 128 == 0, cols <= 16384, 32-byte aligned rows and a known codec");
+  return (int)e;
+}
+
+int flame_act_swiglu_quant_b128(const void* gate_up_bf16, void* h_bf16, void* codes_u8, void* scales_f32, size_t rows, size_t hidden,
+                                int codec, unsigned int flags, void* stream) {
+  cudaError_t e = launch_swiglu_quant(codec, flags, gate_up_bf16, h_bf16, codes_u8, scales_f32, rows, hidden, (cudaStream_t)stream, 0);
+  if (e == cudaErrorInvalidValue) set_last_error("flame_act_swiglu_quant_b128: needs hidden % 128 == 0, 32-byte aligned rows and a known codec");
+  return (int)e;
+}
+
 size_t flame_act_packed_scales_offset(size_t n) { return (n + 255u) & ~(size_t)255u; }
 size_t flame_act_packed_bytes(size_t n) { return flame_act_packed_scales_offset(n) + 4u * ((n + 127u) / 128u); }
 

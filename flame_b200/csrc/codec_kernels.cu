@@ -35,6 +35,8 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+#include <type_traits>
+
 #include "codec_kernels.cuh"
 
 namespace flame_b200 {
@@ -940,6 +942,160 @@ cudaError_t launch_dequant(int codec, const void* in, void* out, size_t n, const
   if (!in || !out) return cudaErrorInvalidValue;
   const TensorJob j{out, const_cast<void*>(in), n, L};
   return launch_dequant_multi(codec, &j, 1, stream, max_ctas);
+}
+
+// ---- producers that emit the packed form beside their BF16 output -----------
+// The saved tensor of a checkpointed block is usually the output of a
+// normalisation or the input of a gated activation.  These two kernels are those
+// producers with the compress step built in: the codes and scales they write
+// are, bit for bit, what compress_b128_kernel gives for the same BF16 tensor,
+// and that tensor is never read again by a compress launch.
+
+namespace {
+
+__device__ __forceinline__ void st_plain32(void* p, const U32x8& r) {  // the next kernel reads it: no streaming hint
+  uint4* q = reinterpret_cast<uint4*>(p);
+  q[0] = make_uint4(r.v[0], r.v[1], r.v[2], r.v[3]);
+  q[1] = make_uint4(r.v[4], r.v[5], r.v[6], r.v[7]);
+}
+
+// RMSNorm of src/cuda/fused_rms_norm.cu:26-80: rstd = rsqrt(mean(x^2) + eps), y = bf16((x * rstd) * w), fp32
+// arithmetic.  One thread block per row; lane t keeps elements [16t, 16t+16) in registers from the one load to
+// the stores.  kCodec 0 writes y only.
+template <int kCodec, bool kFlag>
+__global__ void __launch_bounds__(1024)
+rmsnorm_quant_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, uint16_t* __restrict__ y,
+                     uint8_t* __restrict__ codes, float* __restrict__ scales, float* __restrict__ rstd_out, uint32_t cols, float eps) {
+  __shared__ float warp_sums[32];
+  const int tid = threadIdx.x;
+  const bool live = (uint32_t)tid < cols / kLaneElems;
+  const size_t e0 = (size_t)blockIdx.x * cols + (size_t)tid * kLaneElems;
+  U32x8 r;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) r.v[i] = 0u;
+  if (live) r = ld_stream32(x + e0);
+  float v[kLaneElems];
+  unpack16(r, v);
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kLaneElems; ++i) s = __fmaf_rn(v[i], v[i], s);
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, d);
+  if ((tid & 31) == 0) warp_sums[tid >> 5] = s;
+  __syncthreads();
+  float tot = 0.0f;  // every thread adds the warp sums in the same order: one value for the whole row
+  for (int k = 0; k < (int)(blockDim.x >> 5); ++k) tot += warp_sums[k];
+  const float rstd = rsqrtf(__fadd_rn(__fdiv_rn(tot, (float)cols), eps));
+  if (rstd_out && tid == 0) rstd_out[blockIdx.x] = rstd;
+  U32x8 wr;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) wr.v[i] = 0u;
+  if (live) {
+    const uint4* wp = reinterpret_cast<const uint4*>(w + (size_t)tid * kLaneElems);
+    const uint4 a = __ldg(wp), b = __ldg(wp + 1);
+    wr.v[0] = a.x; wr.v[1] = a.y; wr.v[2] = a.z; wr.v[3] = a.w; wr.v[4] = b.x; wr.v[5] = b.y; wr.v[6] = b.z; wr.v[7] = b.w;
+  }
+  float wv[kLaneElems];
+  unpack16(wr, wv);
+  U32x8 o;
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    o.v[i] = pack_bf16x2(__fmul_rn(__fmul_rn(v[2 * i], rstd), wv[2 * i]), __fmul_rn(__fmul_rn(v[2 * i + 1], rstd), wv[2 * i + 1]));
+  if (live) st_plain32(y + e0, o);
+  if (kCodec != 0) {
+    float scale;
+    const uint4 c = compress_lane<kCodec == 0 ? kCodecInt8 : kCodec, kFlag>(o, scale);  // dead lanes hold zeros and sit in groups of their own
+    if (live) {
+      __stcs(reinterpret_cast<uint4*>(codes + e0), c);
+      if ((tid & (kLanesPerBlock - 1)) == 0) scales[e0 / 128] = scale;
+    }
+  }
+}
+
+// SwiGLU: gate_up is [rows, 2*hidden] (gate columns, then up columns); h = bf16(silu(gate) * up) in fp32 arithmetic.
+// The codes and scales are those of gate_up, the tensor the backward pass needs (src/autograd.rs:326-331).
+template <int kCodec, bool kFlag>
+__global__ void __launch_bounds__(kThreads)
+swiglu_quant_kernel(const uint16_t* __restrict__ gu, uint16_t* __restrict__ h, uint8_t* __restrict__ codes,
+                    float* __restrict__ scales, size_t rows, uint32_t hidden) {
+  const uint32_t lanes_per_row = hidden / kLaneElems;
+  const size_t total = rows * lanes_per_row;
+  const size_t stride = (size_t)gridDim.x * kThreads;
+  const int tid = threadIdx.x;
+  for (size_t base = (size_t)blockIdx.x * kThreads + (tid & ~31); base < total; base += stride) {  // whole warps together
+    const size_t L = base + (tid & 31);
+    const bool live = L < total;
+    const size_t row = live ? L / lanes_per_row : 0;
+    const uint32_t c0 = live ? (uint32_t)(L - row * lanes_per_row) * kLaneElems : 0;
+    const size_t eg = row * 2 * (size_t)hidden + c0, eu = eg + hidden;
+    U32x8 g, u;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g.v[i] = u.v[i] = 0u;
+    if (live) { g = ld_stream32(gu + eg); u = ld_stream32(gu + eu); }
+    float gv[kLaneElems], uv[kLaneElems];
+    unpack16(g, gv);
+    unpack16(u, uv);
+    U32x8 o;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float a = __fmul_rn(__fmul_rn(gv[2 * i], __frcp_rn(1.0f + __expf(-gv[2 * i]))), uv[2 * i]);
+      const float b = __fmul_rn(__fmul_rn(gv[2 * i + 1], __frcp_rn(1.0f + __expf(-gv[2 * i + 1]))), uv[2 * i + 1]);
+      o.v[i] = pack_bf16x2(a, b);
+    }
+    if (live) st_plain32(h + row * (size_t)hidden + c0, o);
+    if (kCodec != 0) {
+      float sg, su;
+      const uint4 cg = compress_lane<kCodec == 0 ? kCodecInt8 : kCodec, kFlag>(g, sg);
+      const uint4 cu = compress_lane<kCodec == 0 ? kCodecInt8 : kCodec, kFlag>(u, su);
+      if (live) {
+        __stcs(reinterpret_cast<uint4*>(codes + eg), cg);
+        __stcs(reinterpret_cast<uint4*>(codes + eu), cu);
+        if ((tid & (kLanesPerBlock - 1)) == 0) { scales[eg / 128] = sg; scales[eu / 128] = su; }
+      }
+    }
+  }
+}
+
+template <typename F>
+cudaError_t by_codec(int codec, unsigned flags, F&& f) {
+  const bool fl = (flags & 1u) != 0;
+  if (codec == 0) return f(std::integral_constant<int, 0>(), std::false_type());
+  if (codec == kCodecInt8) return fl ? f(std::integral_constant<int, kCodecInt8>(), std::true_type()) : f(std::integral_constant<int, kCodecInt8>(), std::false_type());
+  if (codec == kCodecFp8) return fl ? f(std::integral_constant<int, kCodecFp8>(), std::true_type()) : f(std::integral_constant<int, kCodecFp8>(), std::false_type());
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+cudaError_t launch_rmsnorm_quant(int codec, unsigned flags, const void* x, const void* w, void* y, void* codes, void* scales,
+                                 void* rstd_out, size_t rows, size_t cols, float eps, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return cudaSuccess;
+  if (!x || !w || !y || (codec != 0 && (!codes || !scales))) return cudaErrorInvalidValue;
+  if (cols % 128 != 0 || cols > 16384 || rows > 0x7FFFFFFFull) return cudaErrorInvalidValue;
+  if (!aligned(x, 32) || !aligned(w, 16) || !aligned(y, 16) || (codec != 0 && (!aligned(codes, 16) || !aligned(scales, 4)))) return cudaErrorInvalidValue;
+  const int threads = (int)((cols / kLaneElems + 31) / 32 * 32);
+  return by_codec(codec, flags, [&](auto c, auto f) {
+    rmsnorm_quant_kernel<decltype(c)::value, decltype(f)::value><<<(unsigned)rows, threads, 0, stream>>>(
+        static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(w), static_cast<uint16_t*>(y),
+        static_cast<uint8_t*>(codes), static_cast<float*>(scales), static_cast<float*>(rstd_out), (uint32_t)cols, eps);
+    return cudaGetLastError();
+  });
+}
+
+cudaError_t launch_swiglu_quant(int codec, unsigned flags, const void* gate_up, void* h, void* codes, void* scales,
+                                size_t rows, size_t hidden, cudaStream_t stream, int max_ctas) {
+  if (rows == 0 || hidden == 0) return cudaSuccess;
+  if (!gate_up || !h || (codec != 0 && (!codes || !scales))) return cudaErrorInvalidValue;
+  if (hidden % 128 != 0 || hidden > 0x7FFFFFFFull / 2) return cudaErrorInvalidValue;
+  if (!aligned(gate_up, 32) || !aligned(h, 16) || (codec != 0 && (!aligned(codes, 16) || !aligned(scales, 4)))) return cudaErrorInvalidValue;
+  const size_t lanes = rows * (hidden / kLaneElems);
+  const int grid = grid_for((lanes + kThreads - 1) / kThreads, 4, max_ctas);
+  return by_codec(codec, flags, [&](auto c, auto f) {
+    swiglu_quant_kernel<decltype(c)::value, decltype(f)::value><<<grid, kThreads, 0, stream>>>(
+        static_cast<const uint16_t*>(gate_up), static_cast<uint16_t*>(h), static_cast<uint8_t*>(codes), static_cast<float*>(scales),
+        rows, (uint32_t)hidden);
+    return cudaGetLastError();
+  });
 }
 
 cudaError_t launch_bf16_to_fp8(const void* in, void* out, float inv_scale, size_t n, cudaStream_t stream, int max_ctas) {

@@ -53,6 +53,11 @@ cudaError_t launch_dequant(int codec, const void* in_base, void* out_bf16, size_
                            cudaStream_t stream, int max_ctas);
 cudaError_t launch_bf16_to_fp8(const void* in, void* out, float inv_scale, size_t n, cudaStream_t stream, int max_ctas);
 cudaError_t launch_fp8_to_bf16(const void* in, void* out, float scale, size_t n, cudaStream_t stream, int max_ctas);
+// Producers with the compress step built in (codec 0 = plain producer, no codes).
+cudaError_t launch_rmsnorm_quant(int codec, unsigned flags, const void* x, const void* w, void* y, void* codes, void* scales,
+                                 void* rstd_out, size_t rows, size_t cols, float eps, cudaStream_t stream);
+cudaError_t launch_swiglu_quant(int codec, unsigned flags, const void* gate_up, void* h, void* codes, void* scales,
+                                size_t rows, size_t hidden, cudaStream_t stream, int max_ctas);
 int set_max_ctas(int v);
 
 }  // namespace flame_b200

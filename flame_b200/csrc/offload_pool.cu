@@ -82,6 +82,7 @@ struct PushPlan {
   std::vector<uint32_t> chunks;
   std::vector<cudaEvent_t> readers;  // restores that may still be reading these chunks
   const uint8_t* src = nullptr;
+  const uint8_t* scales_src = nullptr;  // non-null: `src` holds codes and this the scales, already compressed on the device
   uint64_t numel = 0, bytes = 0;
   float fp8_scale = 0.0f;
   cudaEvent_t producer = nullptr, d2h_done = nullptr;
@@ -280,7 +281,20 @@ PushPlan make_plan(FlameOffloadPool& p, const Slot& s, const uint8_t* src) {
 cudaError_t issue_push(FlameOffloadPool& p, const PushPlan& plan, PushCounts& n) {
   for (cudaEvent_t ev : plan.readers) POOL_TRY(cudaStreamWaitEvent(p.s_d2h, ev, 0), "push: wait(h2d_done)");
   const size_t nchunks = plan.chunks.size();
-  if (!p.compressed()) {
+  if (plan.scales_src) {
+    // Compressed by its producer: each chunk's codes and scales go straight to their places in the pinned chunk.
+    POOL_TRY(cudaStreamWaitEvent(p.s_d2h, plan.producer, 0), "push: wait(producer)");
+    for (size_t k = 0; k < nchunks; ++k) {
+      const uint64_t e0 = k * p.chunk_elems;
+      const uint64_t ec = std::min<uint64_t>(p.chunk_elems, plan.numel - e0);
+      const uint64_t sb = 4u * ((ec + 127u) / 128u);
+      uint8_t* dst = p.chunk_ptr(plan.chunks[k]);
+      POOL_TRY(copy_in_pieces(dst, plan.src + e0, ec, cudaMemcpyDeviceToHost, p.s_d2h, p.d2h_piece), "push: D2H(codes)");
+      POOL_TRY(memcpy_async_checked(dst + packed_scales_offset(ec), plan.scales_src + 4u * (e0 / 128u), sb, cudaMemcpyDeviceToHost, p.s_d2h),
+               "push: D2H(scales)");
+      n.link_bytes += ec + sb;
+    }
+  } else if (!p.compressed()) {
     POOL_TRY(cudaStreamWaitEvent(p.s_d2h, plan.producer, 0), "push: wait(producer)");
     for (size_t k = 0; k < nchunks; ++k) {
       const uint64_t off = k * p.chunk_src_bytes;
@@ -634,7 +648,21 @@ size_t flame_offload_pool_in_flight(const FlameOffloadPool* pc) {
   return n;
 }
 
+static FlameOffloadStatus push_impl(FlameOffloadPool* p, const void* src, const void* packed_scales, size_t numel, int dtype, void* compute_stream, FlameOffloadHandle* out);
+
 FlameOffloadStatus flame_offload_pool_push(FlameOffloadPool* p, const void* src, size_t numel, int dtype, void* compute_stream, FlameOffloadHandle* out) {
+  return push_impl(p, src, nullptr, numel, dtype, compute_stream, out);
+}
+
+FlameOffloadStatus flame_offload_pool_push_packed(FlameOffloadPool* p, const void* codes, const void* scales, size_t numel, void* compute_stream, FlameOffloadHandle* out) {
+  if (!p || !out) return fail(FLAME_OFFLOAD_ERR_INVALID, "push_packed: null pool or handle pointer");
+  if (p->compression != FLAME_OFFLOAD_COMPRESSION_INT8_B128 && p->compression != FLAME_OFFLOAD_COMPRESSION_FP8_B128)
+    return fail(FLAME_OFFLOAD_ERR_UNSUPPORTED, "push_packed: the pool is not in a per-128-block mode");
+  if (!scales) return fail(FLAME_OFFLOAD_ERR_INVALID, "push_packed: null scales pointer");
+  return push_impl(p, codes, scales, numel, FLAME_OFFLOAD_DTYPE_BF16, compute_stream, out);
+}
+
+static FlameOffloadStatus push_impl(FlameOffloadPool* p, const void* src, const void* packed_scales, size_t numel, int dtype, void* compute_stream, FlameOffloadHandle* out) {
   if (!p || !out) return fail(FLAME_OFFLOAD_ERR_INVALID, "push: null pool or handle pointer");
   // Dtype gate, src/activation_offload.rs:467-476.
   if (dtype != FLAME_OFFLOAD_DTYPE_BF16 && dtype != FLAME_OFFLOAD_DTYPE_F32)
@@ -687,6 +715,7 @@ FlameOffloadStatus flame_offload_pool_push(FlameOffloadPool* p, const void* src,
   if (e != cudaSuccess) fail_cuda(e, "push: cudaEventRecord(producer)");
   if (e == cudaSuccess) {
     PushPlan plan = make_plan(*p, s, static_cast<const uint8_t*>(src));
+    plan.scales_src = static_cast<const uint8_t*>(packed_scales);
     if (p->deferred) {
       s.plan.reset(new PushPlan(std::move(plan)));
       s.issue = Issue::Queued;

@@ -19,12 +19,16 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from . import checkpoint as ckpt
+from . import fused_producers
 from .activation_offload import ActivationOffloadPool, OffloadCompression
 from .policy import Block, Decision, plan_blocks, probe
 
 HIDDEN, HEADS, HEAD_DIM, MLP_HIDDEN = 3072, 24, 128, 9216
 IMG_TOKENS, TXT_TOKENS, GRID = 4096, 512, 64
 TOKENS = IMG_TOKENS + TXT_TOKENS
+# True: RMSNorm and SwiGLU run as this library's kernels, which also emit the codes of the tensor the block saves
+# while a block is being offloaded (flame_b200/fused_producers.py); False: PyTorch ops, compress launches read the tensors.
+FUSED_PRODUCERS = False
 
 
 def rope_tables(device):
@@ -65,8 +69,12 @@ class RMSNormFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w, eps):
-        rstd = torch.rsqrt(x.pow(2).sum(-1, keepdim=True, dtype=torch.float32) / x.shape[-1] + eps).to(x.dtype)
-        y = x * rstd * w
+        if FUSED_PRODUCERS:
+            y, rstd = fused_producers.rmsnorm(x, w, eps)
+            rstd = rstd.view(*x.shape[:-1], 1).to(x.dtype)
+        else:
+            rstd = torch.rsqrt(x.pow(2).sum(-1, keepdim=True, dtype=torch.float32) / x.shape[-1] + eps).to(x.dtype)
+            y = x * rstd * w
         ctx.save_for_backward(y, rstd, w)
         return y
 
@@ -88,6 +96,8 @@ class SwiGLUDownFn(torch.autograd.Function):
     def forward(ctx, gu, wd):
         g, u = gu.chunk(2, dim=-1)
         ctx.save_for_backward(gu, wd)
+        if FUSED_PRODUCERS:
+            return fused_producers.swiglu(gu) @ wd.t()
         return (F.silu(g) * u) @ wd.t()
 
     @staticmethod

@@ -97,6 +97,22 @@ int flame_act_dequant_int8_b128(const void* codes_i8, const void* scales_f32, vo
 int flame_act_quant_fp8_b128(const void* in_bf16, void* codes_u8, void* scales_f32, size_t n, unsigned int flags, void* stream);
 int flame_act_dequant_fp8_b128(const void* codes_u8, const void* scales_f32, void* out_bf16, size_t n, void* stream);
 
+/* Producers with the compress step built in: the tensor a checkpointed block saves is written once, together
+ * with its codes and scales, and no compress launch reads it again.  The codes and scales are bit for bit what
+ * flame_act_quant_*_b128 gives for the BF16 tensor these kernels write (y) or read (gate_up).
+ * codec: 0 (BF16 output only), FLAME_OFFLOAD_COMPRESSION_INT8_B128 or _FP8_B128; flags as for the quantisers.
+ *
+ * RMSNorm, the arithmetic of src/cuda/fused_rms_norm.cu:26-80: y = bf16((x * rsqrt(mean(x^2) + eps)) * weight), fp32
+ * inside; x, y [rows, cols], weight [cols], cols % 128 == 0, cols <= 16384; codes [rows*cols], scales [rows*cols/128]
+ * describe y; rstd_f32 [rows] (may be NULL) receives rsqrt(mean(x^2) + eps) for a backward pass that works from y. */
+int flame_act_rmsnorm_quant_b128(const void* x_bf16, const void* weight_bf16, void* y_bf16, void* codes_u8, void* scales_f32,
+                                 void* rstd_f32, size_t rows, size_t cols, float eps, int codec, unsigned int flags, void* stream);
+/* SwiGLU: gate_up [rows, 2*hidden] = gate columns then up columns, h [rows, hidden] = bf16(silu(gate) * up), hidden % 128
+ * == 0; codes [rows*2*hidden] and scales describe gate_up, the pair the backward pass needs
+ * (Op::FusedSwiGLU{gate, up}, src/autograd.rs:326-331). */
+int flame_act_swiglu_quant_b128(const void* gate_up_bf16, void* h_bf16, void* codes_u8, void* scales_f32, size_t rows, size_t hidden,
+                                int codec, unsigned int flags, void* stream);
+
 /* Several tensors in one launch: the saved activations of a checkpointed block
  * are pushed together (the loop at src/autograd.rs:1714-1741), and one launch over
  * all of them avoids a launch gap and a ragged last wave per tensor.  Results are
@@ -249,6 +265,12 @@ FlameOffloadStatus flame_offload_pool_push(FlameOffloadPool* pool, const void* s
 FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* pool, FlameOffloadHandle handle, void* dst_device, size_t dst_bytes, void* compute_stream, unsigned int flags);
 /* Makes `stream` wait for the most recent restore issued from `slot`. */
 FlameOffloadStatus flame_offload_pool_wait_ready(FlameOffloadPool* pool, size_t slot, void* stream);
+
+/* push of a tensor that is already compressed on the device (by the producers above, or by flame_act_quant_*_b128):
+ * `codes_device` [numel] and `scales_device` [ceil(numel/128)] go to the pinned slab as they are, no compress launch.
+ * The pool must be in the matching block mode (INT8_B128 / FP8_B128); numel counts BF16 elements; both buffers
+ * must stay alive until flame_offload_pool_source_released() reports 1.  pull_into restores BF16 as usual. */
+FlameOffloadStatus flame_offload_pool_push_packed(FlameOffloadPool* pool, const void* codes_device, const void* scales_device, size_t numel, void* compute_stream, FlameOffloadHandle* out_handle);
 
 /* Deferred offload only (deferred_inflight_bytes > 0).  1: the tensor was still waiting for its turn; its slot
  * and chunks are free again, nothing was or will be read from the source, which the caller goes on using.

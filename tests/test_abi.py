@@ -74,3 +74,33 @@ def test_missing_library_is_an_import_error(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "absent.so"))
     with pytest.raises(ImportError, match="no CPU fallback"):
         _lib.lib()
+
+
+def _cc(*args):
+    import subprocess
+    return subprocess.run(list(args), capture_output=True, text=True)
+
+
+def test_header_is_valid_c99_and_cxx():
+    """The boundary is a C header: it must compile on its own as pedantic C99 and as C++."""
+    hdr = os.path.join(ROOT, "include", "flame_offload.h")
+    r = _cc("gcc", "-std=c99", "-pedantic", "-Wall", "-Wextra", "-Werror", "-fsyntax-only", "-x", "c", hdr)
+    assert r.returncode == 0, r.stderr
+    r = _cc("g++", "-std=c++11", "-Wall", "-Wextra", "-Werror", "-fsyntax-only", "-x", "c++", hdr)
+    assert r.returncode == 0, r.stderr
+
+
+def build_c_caller(out_path: str):
+    """Compiles tests/helpers/abi_roundtrip.c (a caller in plain C) against the header and both libraries."""
+    from oracle import capi
+    capi.build()
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    return _cc("gcc", "-std=c99", "-Wall", "-Wextra", "-Werror", os.path.join(ROOT, "tests", "helpers", "abi_roundtrip.c"),
+               "-I", os.path.join(ROOT, "include"), "-I", os.path.join(cuda, "include"),
+               "-L", os.path.join(ROOT, "flame_b200"), "-lflame_offload", "-L", os.path.join(ROOT, "oracle"), "-loracle",
+               "-L", os.path.join(cuda, "lib64"), "-lcudart", "-lm", "-o", out_path)
+
+
+def test_plain_c_caller_compiles_and_links(tmp_path):
+    r = build_c_caller(str(tmp_path / "abi_roundtrip"))
+    assert r.returncode == 0, r.stderr

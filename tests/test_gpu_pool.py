@@ -506,3 +506,20 @@ def test_probe_reports_positive_rates(cuda_device):
 
     p = probe(64 << 20, 2)
     assert p.d2h_gbs > 1 and p.h2d_gbs > 1 and p.hbm_copy_gbs > 100 and p.quant_gbs > 100 and p.dequant_gbs > 100
+
+
+def test_plain_c_caller_round_trips(cuda_device, tmp_path):
+    """tests/helpers/abi_roundtrip.c: the reference's pool tests and an int8 round trip from a caller written in C."""
+    import os
+    import subprocess
+
+    from tests.test_abi import ROOT, build_c_caller
+    exe = str(tmp_path / "abi_roundtrip")
+    r = build_c_caller(exe)
+    assert r.returncode == 0, r.stderr
+    env = dict(os.environ)
+    env["LD_LIBRARY_PATH"] = os.pathsep.join([os.path.join(ROOT, "flame_b200"), os.path.join(ROOT, "oracle"),
+                                              "/usr/local/cuda/lib64", env.get("LD_LIBRARY_PATH", "")])
+    env["CUDA_VISIBLE_DEVICES"] = str(cuda_device.index or 0)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=120, env=env)
+    assert r.returncode == 0 and "abi_roundtrip: ok" in r.stdout, (r.stdout, r.stderr)
