@@ -219,7 +219,7 @@ ISSUE_OFF_THREAD = 1 << 40   # a deferred pool with this in-flight budget never 
 
 
 def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
-                     arms=("offload_int8", "deferred", "offload_bf16", "recompute"), custom=(),
+                     arms=("offload_int8", "deferred", "offload_bf16", "recompute", "fused"), custom=(),
                      resident_budget_blocks: int = 8) -> dict:
     """Step time of each arm relative to resident activations.  Returns a JSON-ready dict."""
     torch.manual_seed(0)
@@ -239,7 +239,8 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
     out["resident"] = {"ms_per_step": round(base_ms, 3), "peak_mem_gb": round(base_mem / 1e9, 2),
                        "held_after_forward_gb": round(base_held / 1e9, 2)}
 
-    def run_arm(name, decisions, mode, deferred_bytes=0, d2h_piece=COPY_PIECE_BYTES, **pool_kwargs):
+    def run_arm(name, decisions, mode, deferred_bytes=0, d2h_piece=COPY_PIECE_BYTES, base=None, **pool_kwargs):
+        base = base_ms if base is None else base
         pool = None
         if mode is not None:
             # sized for every block offloaded at once; the plan decides how many really are
@@ -251,7 +252,7 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
         model.decisions = decisions
         try:
             ms, mem, held = _time_steps(model, opt, x, cos, sin, steps, warmup)
-            res = {"ms_per_step": round(ms, 3), "overhead_pct": round(100.0 * (ms - base_ms) / base_ms, 2), "peak_mem_gb": round(mem / 1e9, 2),
+            res = {"ms_per_step": round(ms, 3), "overhead_pct": round(100.0 * (ms - base) / base, 2), "peak_mem_gb": round(mem / 1e9, 2),
                    "held_after_forward_gb": round(held / 1e9, 2),
                    "blocks": "".join({Decision.RESIDENT: "R", Decision.RECOMPUTE: "C"}.get(d, "O") for d in decisions)}
             if pool is not None:
@@ -303,6 +304,29 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
         out["offload_bf16_all"] = run_arm("offload_bf16_all", [Decision.OFFLOAD_BF16] * blocks, OffloadCompression.NONE)
     if "recompute" in arms:
         out["recompute"] = run_arm("recompute", [Decision.RECOMPUTE] * blocks, None)
+    fused_names = ()
+    if "fused" in arms:
+        # The same step with RMSNorm and SwiGLU as this library's kernels (in the baseline too), which emit the codes of
+        # the tensors a block saves while that block is being offloaded: three of seven tensors need no compress launch.
+        global FUSED_PRODUCERS
+        FUSED_PRODUCERS = True
+        try:
+            model.decisions = None
+            f_ms, f_mem, f_held = _time_steps(model, opt, x, cos, sin, steps, warmup)
+            out["resident_fused_producers"] = {"ms_per_step": round(f_ms, 3), "peak_mem_gb": round(f_mem / 1e9, 2),
+                                               "held_after_forward_gb": round(f_held / 1e9, 2)}
+            p = plan_blocks(blk, d2h_gbs=link.d2h_gbs, h2d_gbs=link.h2d_gbs, device_budget_bytes=budget, offload=Decision.OFFLOAD_INT8)
+            out["offload_int8_planned_fused_producers"] = run_arm("offload_int8_planned_fused_producers", p.decisions, OffloadCompression.INT8_B128,
+                                                                  deferred_bytes=ISSUE_OFF_THREAD, d2h_piece=DEFERRED_D2H_PIECE_BYTES, base=f_ms)
+            model.decisions = None
+            f_again, _, _ = _time_steps(model, opt, x, cos, sin, steps, 1)
+            out["resident_fused_producers"]["ms_per_step_rerun"] = round(f_again, 3)
+            fm = 0.5 * (f_ms + f_again)
+            v = out["offload_int8_planned_fused_producers"]
+            v["overhead_pct_vs_mean_baseline"] = round(100.0 * (v["ms_per_step"] - fm) / fm, 2)
+            fused_names = ("offload_int8_planned_fused_producers",)
+        finally:
+            FUSED_PRODUCERS = False
     # experiments: (name, leading blocks offloaded, "int8" | "bf16", deferred_inflight_bytes, d2h_piece_bytes)
     for name, k, codec, deferred_bytes, piece, *rest in custom:
         dec = Decision.OFFLOAD_INT8 if codec == "int8" else Decision.OFFLOAD_BF16
@@ -320,7 +344,9 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
     again_ms, _, _ = _time_steps(model, opt, x, cos, sin, steps, 1)
     out["resident"]["ms_per_step_rerun"] = round(again_ms, 3)
     mean_base = 0.5 * (base_ms + again_ms)
-    for v in list(out.values()) + list(out.get("offload_int8_curve", [])):
+    for k, v in list(out.items()) + [(None, c) for c in out.get("offload_int8_curve", [])]:
+        if k in fused_names:
+            continue
         if isinstance(v, dict) and "overhead_pct" in v:
             v["overhead_pct_vs_mean_baseline"] = round(100.0 * (v["ms_per_step"] - mean_base) / mean_base, 2)
     return out
