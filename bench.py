@@ -552,6 +552,69 @@ def run_weights(args, torch, dev):
     off.close()
 
 
+def run_producers(args, torch, lib, dev):
+    """RMSNorm and SwiGLU with the compress step built in, at the DiT block's shapes: CUDA-event time per launch with
+    and without codes, against the PyTorch ops they replace and against the separate compress launch they save."""
+    import torch.nn.functional as F
+
+    hbm_peak, peak_kind = measured_peaks()
+    st = torch.cuda.current_stream()
+    sp = st.cuda_stream
+    g = torch.Generator(device=dev).manual_seed(0)
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=30):
+        for _ in range(5):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()                                  # cold L2: the inputs come from HBM, as in a training step
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st); fn(); e1.record(st)
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    out = {"mode": "producers", "unit": "GB/s of algorithmic bytes", "peak": hbm_peak, "peak_kind": f"of {peak_kind}", "l2": "flushed before every launch"}
+    rows, cols, hidden = TOKENS, HIDDEN, 3 * HIDDEN
+    x = torch.randn(rows, cols, device=dev, generator=g).to(torch.bfloat16)
+    w = torch.ones(cols, device=dev, dtype=torch.bfloat16)
+    y = torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device=dev)
+    codes = torch.empty(rows * 2 * hidden, dtype=torch.uint8, device=dev)
+    scales = torch.empty(rows * 2 * hidden // 128, dtype=torch.float32, device=dev)
+    gu = torch.randn(rows, 2 * hidden, device=dev, generator=g).to(torch.bfloat16)
+    h = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev)
+
+    def rms(codec):
+        assert lib.flame_act_rmsnorm_quant_b128(x.data_ptr(), w.data_ptr(), y.data_ptr(), codes.data_ptr(), scales.data_ptr(), rstd.data_ptr(),
+                                                rows, cols, 1e-6, codec, 0, sp) == 0
+
+    def swi(codec):
+        assert lib.flame_act_swiglu_quant_b128(gu.data_ptr(), h.data_ptr(), codes.data_ptr(), scales.data_ptr(), rows, hidden, codec, 0, sp) == 0
+
+    def torch_rms():
+        r = torch.rsqrt(x.pow(2).sum(-1, keepdim=True, dtype=torch.float32) / cols + 1e-6).to(x.dtype)
+        return x * r * w
+
+    def torch_swiglu():
+        a, b = gu.chunk(2, dim=-1)
+        return F.silu(a) * b
+
+    n_r, n_s = rows * cols, rows * 2 * hidden
+    for name, fn, alg in (("rmsnorm", lambda: rms(0), 4.0 * n_r), ("rmsnorm+int8", lambda: rms(2), (4.0 + 1.03125) * n_r),
+                          ("rmsnorm+fp8", lambda: rms(3), (4.0 + 1.03125) * n_r), ("rmsnorm, PyTorch ops", torch_rms, 4.0 * n_r),
+                          ("compress int8 of the norm output, separate launch", lambda: lib.flame_act_quant_int8_b128(y.data_ptr(), codes.data_ptr(), scales.data_ptr(), n_r, 0, sp), 3.03125 * n_r),
+                          ("swiglu", lambda: swi(0), 3.0 * n_s), ("swiglu+int8", lambda: swi(2), (3.0 + 1.03125) * n_s),
+                          ("swiglu+fp8", lambda: swi(3), (3.0 + 1.03125) * n_s), ("swiglu, PyTorch ops", torch_swiglu, 3.0 * n_s),
+                          ("compress int8 of gate+up, separate launch", lambda: lib.flame_act_quant_int8_b128(gu.data_ptr(), codes.data_ptr(), scales.data_ptr(), n_s, 0, sp), 3.03125 * n_s)):
+        us = timed(fn)
+        out[name] = {"us": round(us, 2), "gbs": round(alg / us * 1e-3, 1), "frac": round(alg / us * 1e-3 / hbm_peak, 3), "alg_bytes": int(alg)}
+    out["shapes"] = {"rmsnorm": [rows, cols], "swiglu gate_up": [rows, 2 * hidden]}
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -566,7 +629,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-ref-gpu", action="store_true", help="--impl reference: skip timing the reference's own compiled CUDA files")
     ap.add_argument("--only", choices=["all", "value", "e2e"], default="all", help="profiling: run only one timed region")
-    ap.add_argument("--mode", choices=["bench", "sweep", "interference", "weights"], default="bench",
+    ap.add_argument("--mode", choices=["bench", "sweep", "interference", "weights", "producers"], default="bench",
                     help="sweep: 1 MB..4 GB single tensor x codec x chunk size; interference: copies against HBM-bound kernels; "
                          "weights: block weights streamed host->device through the same pool")
     ap.add_argument("--sweep-max-mb", type=int, default=4096)
@@ -604,6 +667,12 @@ def main():
 
     if args.mode == "sweep":
         run_sweep(args, torch, lib, dev, rank)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.mode == "producers":
+        if rank == 0:
+            run_producers(args, torch, lib, dev)
         if world > 1:
             dist.destroy_process_group()
         return
