@@ -369,9 +369,10 @@ def workload_config(args, world):
             "l2": "inputs larger than L2 (6.79 GB of distinct tensors per step)", "replicas": world, "parallelism": f"dp{world} independent replicas, no collective"}
 
 
-def _event_ms(torch, stream, fn, reps: int):
-    """Median CUDA-event milliseconds of fn() on `stream` after one warm-up call."""
-    fn()
+def _event_ms(torch, stream, fn, reps: int, warmup: int = 1, spread: bool = False):
+    """Median CUDA-event milliseconds of fn() on `stream` after `warmup` calls; with `spread`, (median, p10, p90)."""
+    for _ in range(max(1, warmup)):
+        fn()
     torch.cuda.synchronize()
     ts = []
     for _ in range(reps):
@@ -382,6 +383,8 @@ def _event_ms(torch, stream, fn, reps: int):
         torch.cuda.synchronize()
         ts.append(e0.elapsed_time(e1))
     ts.sort()
+    if spread:
+        return ts[len(ts) // 2], ts[len(ts) // 10], ts[min(len(ts) - 1, (9 * len(ts)) // 10)]
     return ts[len(ts) // 2]
 
 
@@ -409,11 +412,14 @@ def run_sweep(args, torch, lib, dev, rank):
                 def round_trip():
                     pool.pull_into(pool.push(x), dst)
 
-                reps = 7 if mb <= 256 else 3
-                ms = _event_ms(torch, stream, round_trip, reps)
+                # the reference's own convention (benches/activation_bwd.rs:16-18: 20 warm-up, 100 timed, median with
+                # p10/p90) where a round trip is short; fewer repetitions where one takes tens of milliseconds
+                reps, warm = (100, 20) if mb <= 64 else (20, 3) if mb <= 512 else (5, 1)
+                ms, p10, p90 = _event_ms(torch, stream, round_trip, reps, warm, spread=True)
                 st = pool.stats()
                 link_bytes = st["bytes_link_out"] // st["pushes"]
                 point = {"mode": "sweep", "tensor_mb": mb, "codec": codec, "chunk_mb": chunk_mb, "round_trip_ms": round(ms, 4),
+                         "round_trip_ms_p10": round(p10, 4), "round_trip_ms_p90": round(p90, 4), "reps": reps, "warmup": warm,
                          "gbs_bf16_equiv": round(2 * nbytes / (ms * 1e-3) * 1e-9, 2),
                          # the round trip is one offload followed by one restore: each direction gets about half the time
                          "link_gbs_per_direction": round(link_bytes / (ms * 1e-3 / 2) * 1e-9, 2),
@@ -424,8 +430,8 @@ def run_sweep(args, torch, lib, dev, rank):
                     codes = torch.empty(n, dtype=torch.uint8, device=dev)
                     scales = torch.empty((n + 127) // 128, dtype=torch.float32, device=dev)
                     sp = stream.cuda_stream
-                    qms = _event_ms(torch, stream, lambda: q(x.data_ptr(), codes.data_ptr(), scales.data_ptr(), n, 0, sp), reps)
-                    dms = _event_ms(torch, stream, lambda: d(codes.data_ptr(), scales.data_ptr(), dst.data_ptr(), n, sp), reps)
+                    qms = _event_ms(torch, stream, lambda: q(x.data_ptr(), codes.data_ptr(), scales.data_ptr(), n, 0, sp), reps, warm)
+                    dms = _event_ms(torch, stream, lambda: d(codes.data_ptr(), scales.data_ptr(), dst.data_ptr(), n, sp), reps, warm)
                     alg = ALG_BYTES_PER_ELEM * n
                     point["compress_gbs"] = round(alg / (qms * 1e-3) * 1e-9, 1)
                     point["dequant_gbs"] = round(alg / (dms * 1e-3) * 1e-9, 1)
