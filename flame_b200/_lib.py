@@ -121,6 +121,7 @@ SIGNATURES = {
     "flame_offload_pool_push_packed": (_i, [_vp, _vp, _vp, _sz, _vp, C.POINTER(Handle)]),
     "flame_act_rmsnorm_quant_b128": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, C.c_float, _i, _u, _vp]),
     "flame_act_swiglu_quant_b128": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _i, _u, _vp]),
+    "flame_offload_pool_prefetch": (_i, [_vp, Handle, _vp, _sz, _vp]),
     "flame_offload_pool_cancel": (_i, [_vp, Handle]),
     "flame_offload_pool_hold": (_i, [_vp, _i]),
     "flame_offload_pool_hold_after": (_i, [_vp, _vp]),

@@ -133,6 +133,10 @@ class ActivationOffloadPool:
     def _stream(self) -> int:
         return self._torch.cuda.current_stream(self.device).cuda_stream
 
+    def release_finished_sources(self) -> None:
+        """Lets go of every source tensor whose device-to-host copy has completed (push does this on its way in)."""
+        self._sweep_keep_alive()
+
     def _sweep_keep_alive(self) -> None:
         """Drops source tensors whose device-to-host copy has completed.
 
@@ -203,6 +207,10 @@ class ActivationOffloadPool:
         if not defer_wait:
             self._keep_alive.pop(handle.slot, None)
         self._meta.pop(handle.slot, None)
+
+    def prefetch(self, handle: OffloadHandle, dst) -> None:
+        """Start the restore into `dst` now; call wait_ready(handle.slot) before the first read."""
+        self.pull_into(handle, dst, defer_wait=True)
 
     def pull(self, handle: OffloadHandle):
         """Restore into a freshly allocated tensor (activation_offload.rs:619-731)."""

@@ -73,7 +73,7 @@ class BlockOffloader:
             self._handles.append([self._pool.push(flat[g0:g0 + gb].view(dtype)) for dtype, g0, gb in groups])
             del flat
         self._pool.synchronize(600.0)
-        self._pool._sweep_keep_alive()
+        self._pool.release_finished_sources()
         self._n_slots = gpu_slots
         self._bufs: List[Optional[object]] = [None] * gpu_slots
         self._resident: List[Optional[int]] = [None] * gpu_slots    # block index held (or being loaded) per device slot

@@ -784,6 +784,10 @@ FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* p, FlameOffloa
   return FLAME_OFFLOAD_OK;
 }
 
+FlameOffloadStatus flame_offload_pool_prefetch(FlameOffloadPool* p, FlameOffloadHandle h, void* dst, size_t dst_bytes, void* compute_stream) {
+  return flame_offload_pool_pull_into(p, h, dst, dst_bytes, compute_stream, FLAME_OFFLOAD_PULL_DEFER_WAIT);
+}
+
 int flame_offload_pool_cancel(FlameOffloadPool* p, FlameOffloadHandle h) {
   if (!p) return -(int)fail(FLAME_OFFLOAD_ERR_INVALID, "cancel: null pool");
   std::lock_guard<std::mutex> lk(p->mu);

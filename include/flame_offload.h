@@ -263,6 +263,10 @@ FlameOffloadStatus flame_offload_pool_push(FlameOffloadPool* pool, const void* s
 #define FLAME_OFFLOAD_PULL_DEFER_WAIT 1u
 #define FLAME_OFFLOAD_PULL_KEEP 2u
 FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* pool, FlameOffloadHandle handle, void* dst_device, size_t dst_bytes, void* compute_stream, unsigned int flags);
+/* prefetch(handle): the restore is started now and nothing waits for it yet; the consumer calls
+ * flame_offload_pool_wait_ready(pool, handle.slot, stream) before its first read.  Same as pull_into with
+ * FLAME_OFFLOAD_PULL_DEFER_WAIT; the reference pulls just in time (src/autograd.rs:2470-2479). */
+FlameOffloadStatus flame_offload_pool_prefetch(FlameOffloadPool* pool, FlameOffloadHandle handle, void* dst_device, size_t dst_bytes, void* compute_stream);
 /* Makes `stream` wait for the most recent restore issued from `slot`. */
 FlameOffloadStatus flame_offload_pool_wait_ready(FlameOffloadPool* pool, size_t slot, void* stream);
 

@@ -180,6 +180,12 @@ def test_pull_into_deferred_wait_and_source_release(cuda_device):
     torch.cuda.synchronize()
     wc, ws = capi.quant_int8_b128(bits)
     assert np.array_equal(G.bits_of(dst), capi.dequant_int8_b128(wc, ws))
+    h = pool.push(x)                      # the same through the entry point named for it
+    dst.fill_(3.0)
+    pool.prefetch(h, dst)
+    pool.wait_ready(h.slot)
+    torch.cuda.synchronize()
+    assert np.array_equal(G.bits_of(dst), capi.dequant_int8_b128(wc, ws)) and pool.in_flight() == 0
     with pytest.raises(InvalidInput, match="destination"):
         pool.pull_into(pool.push(x), torch.empty(n - 1, dtype=torch.bfloat16, device=cuda_device))
 
