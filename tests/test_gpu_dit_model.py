@@ -88,13 +88,16 @@ def test_uncompressed_offload_reproduces_resident_gradients(cuda_device, dit, fl
         pool.close()
 
 
+@pytest.mark.parametrize("budget", [1 << 40, 64 << 20])
 @pytest.mark.parametrize("fused", [False, True])
-def test_int8_offload_keeps_the_large_gradients_close(cuda_device, dit, fused):
+def test_int8_offload_keeps_the_large_gradients_close(cuda_device, dit, fused, budget):
+    """budget 64 MB: most tensors are still queued when backward arrives; those that a producer compressed are
+    dequantised on the device from their codes, the others are used as they are."""
     grads, want, saved = dit
     W.FUSED_PRODUCERS = fused
     try:
         base = grads(None) if fused else want
-        pool = ActivationOffloadPool(cuda_device, 64, saved, OffloadCompression.INT8_B128, deferred_inflight_bytes=1 << 40,
+        pool = ActivationOffloadPool(cuda_device, 64, saved, OffloadCompression.INT8_B128, deferred_inflight_bytes=budget,
                                      d2h_piece_bytes=1 << 20, h2d_piece_bytes=4 << 20)
         ckpt.set_activation_offload_pool(pool)
         got = grads([Decision.OFFLOAD_INT8] * 5)
@@ -102,7 +105,10 @@ def test_int8_offload_keeps_the_large_gradients_close(cuda_device, dit, fused):
         assert len(big) >= 5
         for i in big:
             assert _rel(base[i], got[i]) < 0.06, (i, _rel(base[i], got[i]))
-        assert pool.stats()["pushes"] == 35 and pool.in_flight() == 0
+        st = pool.stats()
+        assert st["pushes"] == 35 and pool.in_flight() == 0 and st["pulls"] + st["pushes_cancelled"] == 35
+        if budget < (1 << 30):
+            assert st["pushes_cancelled"] > 0
     finally:
         W.FUSED_PRODUCERS = False
         ckpt.clear_activation_offload_pool()
