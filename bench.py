@@ -48,7 +48,7 @@ ALG_BYTES_PER_ELEM = 3.03125  # 2 B read + 1 B code + 4/128 B scale (and the mir
 # (one launch = one DiT block, 169,869,312 elements: 486.1 MB compress, 458.1 MB dequantise); traffic grows in
 # proportion to the elements of a launch.  Below the algorithmic figure because the L2 still holds part of the
 # output when the kernel ends.
-NCU_TRAFFIC_PER_ELEM = {"compress": 486.1e6 / 169869312, "dequant": 458.1e6 / 169869312}
+NCU_TRAFFIC_PER_ELEM = {"compress": 479.7e6 / 169869312, "dequant": 458.1e6 / 169869312}
 PCIE_GEN5_X16_GBS = 63.0      # 32 GT/s x 16 lanes x 128/130 / 8
 TOKENS, HIDDEN, BLOCKS = 4608, 3072, 20
 # saved set of one block, as last dims: norm1 out, QKV, attention out, norm2 out, SwiGLU gate+up

@@ -505,6 +505,77 @@ compress_b128_kernel(const __grid_constant__ JobTable T, unsigned rounds, unsign
   if (kStaged && tid == 0) bulk_wait_all<0>();
 }
 
+// Software-pipelined form of the direct-store kernel: the loads of a block's next tile are issued before the
+// current tile is encoded, so a thread always has a tile's worth of loads in flight.  Twice the input registers
+// (four resident blocks per SM instead of five).  Same tile order, same results.
+template <int kCodec, bool kFlag>
+__global__ void __launch_bounds__(kThreads, 4)
+compress_b128_pipelined_kernel(const __grid_constant__ JobTable T, unsigned rounds, unsigned multi_ctas, unsigned multi_tiles) {
+  const int tid = threadIdx.x;
+  const bool multi = blockIdx.x < multi_ctas;
+  uint32_t j = 0;
+  // tile of round k for this block, or false
+  auto tile_of = [&](unsigned k, uint32_t& g) -> bool {
+    if (k >= rounds) return false;
+    if (multi) {
+      g = k * multi_ctas + blockIdx.x;
+      if (g >= multi_tiles) return false;
+    } else {
+      if (k) return false;
+      g = multi_tiles + (blockIdx.x - multi_ctas);
+    }
+    return g < T.total_tiles;
+  };
+  // A tile is remembered as (job, tile within the job); the job's pointers and layout stay in the parameter bank.
+  struct Where { uint32_t job, tile; bool ok, full; };
+  auto resolve = [&](unsigned k) -> Where {
+    Where w{0u, 0u, false, false};
+    uint32_t g = 0;
+    w.ok = tile_of(k, g);
+    if (!w.ok) return w;
+    while (j + 1 < T.count && g >= T.jobs[j + 1].tile0) ++j;
+    w.job = j;
+    w.tile = g - T.jobs[j].tile0;
+    w.full = ((size_t)w.tile + 1) * kTileElems <= T.jobs[j].n;
+    return w;
+  };
+  auto in_of = [&](const Where& w) { return static_cast<const uint16_t*>(T.jobs[w.job].in) + (size_t)w.tile * kTileElems; };
+  Where cur = resolve(0);
+  U32x8 nxt[kUnroll];
+  if (cur.ok && cur.full) {
+    const uint16_t* tin = in_of(cur);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) nxt[u] = ld_stream32(tin + (size_t)(u * kThreads + tid) * kLaneElems);
+  }
+  for (unsigned k = 0; cur.ok; ++k) {
+    U32x8 raw[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) raw[u] = nxt[u];
+    const Where next = resolve(k + 1);
+    if (next.ok && next.full) {
+      const uint16_t* tin = in_of(next);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) nxt[u] = ld_stream32(tin + (size_t)(u * kThreads + tid) * kLaneElems);
+    }
+    const CodecJob& J = T.jobs[cur.job];
+    const size_t e_tile = (size_t)cur.tile * kTileElems;
+    const OutAddr o = locate(static_cast<uint8_t*>(J.out), J.L, e_tile);
+    if (cur.full) {
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        float scale;
+        const uint4 c = compress_lane<kCodec, kFlag>(raw[u], scale);
+        const int v = u * kThreads + tid;
+        __stcs(reinterpret_cast<uint4*>(o.codes + v * kLaneElems), c);
+        if ((tid & (kLanesPerBlock - 1)) == 0) o.scales[v / kLanesPerBlock] = scale;
+      }
+    } else {
+      compress_ragged_tile<kCodec, kFlag>(in_of(cur), o, J.n - e_tile, tid);
+    }
+    cur = next;
+  }
+}
+
 // Any alignment, any n: one warp per 128-element block, scalar accesses.
 template <int kCodec, bool kFlag>
 __global__ void __launch_bounds__(kThreads)
@@ -746,7 +817,8 @@ int resident_ctas_per_sm(K kernel, size_t dyn_smem = 0) {
 // A grid in which every thread block takes the same number of consecutive tiles
 // and all blocks are resident at once: no second wave, no ragged last round.
 struct Grid { int ctas; unsigned tiles_per_cta; };
-constexpr int kTaperWaves = 2;  // waves of single-tile blocks at the end of an oversubscribed compress launch
+constexpr int kTaperWaves = 2;
+constexpr int kPipelinedBalanceLimit = 8, kPipelinedRounds = 6;  // grid policy of the software-pipelined compress kernel  // waves of single-tile blocks at the end of an oversubscribed compress launch
 int env_int(const char* name) {
   const char* e = getenv(name);
   return e ? (atoi(e) < 1 ? 1 : atoi(e)) : 0;
@@ -819,10 +891,18 @@ void add_job(JobTable& T, const void* in, void* out, const TensorJob& j) {
 
 template <int kCodec, bool kFlag, bool kStaged>
 cudaError_t launch_compress_table(const JobTable& T, cudaStream_t stream, int max_ctas) {
+  // int8: the software-pipelined kernel (0.91 -> 0.93-0.95 of the HBM rate on a DiT block, 0.96 -> 1.0 at 1 Gi
+  // elements); FP8 is bound by its encoder's ALU work and loses more to four resident blocks than it gains
+  // (0.75 -> 0.68).  FLAME_ACT_PIPELINED=0/1 overrides.
+  static int pipelined = -1;
+  if (pipelined < 0) { const char* e = getenv("FLAME_ACT_PIPELINED"); pipelined = e ? (atoi(e) != 0) : 2; }
+  const bool use_pipelined = !kStaged && (pipelined == 2 ? (kCodec == kCodecInt8) : pipelined != 0);
   auto kern = compress_b128_kernel<kCodec, kFlag, kStaged>;
+  auto kern_p = compress_b128_pipelined_kernel<kCodec, kFlag>;
   const size_t smem = kStaged ? 2 * kStagedBufBytes : 0;
-  const int per_sm = resident_ctas_per_sm(kern, smem);
-  const Grid g = grid_balanced(T.total_tiles, per_sm, max_ctas, 8, 6);
+  const int per_sm = use_pipelined ? resident_ctas_per_sm(kern_p, 0) : resident_ctas_per_sm(kern, smem);
+  const Grid g = use_pipelined ? grid_balanced(T.total_tiles, per_sm, max_ctas, kPipelinedBalanceLimit, kPipelinedRounds)
+                               : grid_balanced(T.total_tiles, per_sm, max_ctas, 8, 6);
   // Oversubscribed launches (several waves of blocks) end on single-tile blocks: `taper` waves of them.
   static int taper = -1;
   if (taper < 0) { const char* e = getenv("FLAME_ACT_TAPER_WAVES"); taper = e ? atoi(e) : kTaperWaves; if (taper < 0) taper = 0; }
@@ -834,7 +914,8 @@ cudaError_t launch_compress_table(const JobTable& T, cudaStream_t stream, int ma
     multi_ctas = (multi_tiles + g.tiles_per_cta - 1) / g.tiles_per_cta;
     ctas = multi_ctas + (unsigned)singles;
   }
-  kern<<<ctas, kThreads, smem, stream>>>(T, g.tiles_per_cta, multi_ctas, multi_tiles);
+  if (use_pipelined) kern_p<<<ctas, kThreads, 0, stream>>>(T, g.tiles_per_cta, multi_ctas, multi_tiles);
+  else kern<<<ctas, kThreads, smem, stream>>>(T, g.tiles_per_cta, multi_ctas, multi_tiles);
   return cudaGetLastError();
 }
 
