@@ -260,6 +260,8 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
                 n = max(1, steps + warmup + 1)
                 res["offloaded_gb_per_step"] = round(st["bytes_logical_out"] / n / 1e9, 3)
                 res["link_gb_per_step"] = round(st["bytes_link_out"] / n / 1e9, 3)
+                if st["push_rejected_full"]:      # a block that found the pool full was recomputed instead: the arm is not what it says
+                    res["pushes_rejected_pool_full"] = int(st["push_rejected_full"])
                 if deferred_bytes:
                     res["tensors_used_in_place_per_step"] = round(st["pushes_cancelled"] / n, 1)
                     res["tensors_pushed_per_step"] = round(st["pushes"] / n, 1)
