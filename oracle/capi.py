@@ -126,6 +126,25 @@ def load_ref_cuda():
     return _REF_CUDA
 
 
+_REF_SAGE = None
+
+
+def load_ref_sage():
+    """The reference's own int8 quantisation kernel (sage_quantize_tensor, src/sage_attention.rs:510-543) compiled by
+    ``make -C oracle refsage`` behind a small launcher, or None.  ``sage_quantize_ref(in_f32, out_s8, scales, rows,
+    row_size, stream)`` with row_size 128 quantises per 128-element block."""
+    global _REF_SAGE
+    so = os.path.join(_HERE, "_ref", "libsage_quant_ref.so")
+    if not os.path.exists(so):
+        return None
+    if _REF_SAGE is None:
+        lib = C.CDLL(so, mode=os.RTLD_LOCAL | os.RTLD_NOW)
+        lib.sage_quantize_ref.restype = C.c_int
+        lib.sage_quantize_ref.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        _REF_SAGE = lib
+    return _REF_SAGE
+
+
 def _p(a: np.ndarray):
     return a.ctypes.data_as(C.c_void_p)
 

@@ -23,7 +23,7 @@
  *     flame_fp8_to_bf16 (src/cuda/fp8_quant.cu:59-93,
  *     src/cuda/fp8_dequant.cu:10-59) as called from
  *     src/activation_offload.rs:543-561 (inv_scale = 1/scale, multiply).
- *   - the symmetric int8 formula of src/sage_attention.rs:524-541
+ *   - the symmetric int8 formula of src/sage_attention.rs:510-543
  *     (scale = absmax/127, code = round-to-nearest-even(val / scale)), applied
  *     per block of 128 consecutive elements with a +-127 clamp.
  *   - the per-128-block FP8 variant: scale = absmax/448, inv = 1/scale,
@@ -32,10 +32,15 @@
  * Parity status.  The FP8 encoder/decoder restatement is checked against the
  * reference's own encoder body compiled from its source (oracle/_ref, built by
  * oracle/Makefile) over every BF16 bit pattern and a dense sweep of binary32
- * values.  The reference's tests hold no known-answer vector for FP8, and the
- * reference has no per-128-block codec at all: for the block formulas the
- * only anchors are the formula text in the benchmark specification and the
- * sage int8 kernel cited above ("parity unpinned" for per-block results).
+ * values, and against the bytes the reference's two FP8 kernels wrote on a
+ * B200 for every BF16 pattern and every code (tests/golden/
+ * fp8_reference_kernel_sm100.npz).  The per-128-block int8 results are checked
+ * against what the reference's own int8 quantiser (sage_quantize_tensor,
+ * src/sage_attention.rs:510-543) wrote on a B200 with row_size = 128
+ * (tests/golden/int8_reference_sage_sm100.npz).  The reference has no
+ * per-128-block FP8 mode: that variant is the pinned encoder applied to
+ * x * (1/scale) with scale = absmax/448, and as a composition it has no
+ * reference output to be held against ("parity unpinned" for per-block FP8).
  * The uncompressed BF16 round trip is pinned by the reference test at
  * src/activation_offload.rs:843-889.
  */

@@ -1,4 +1,5 @@
-"""Writes fp8_reference_kernel_sm100.npz: what the reference's own FP8 kernels return on a B200.
+"""Writes fp8_reference_kernel_sm100.npz and int8_reference_sage_sm100.npz: what the reference's own kernels return
+on a B200.
 
 Needs a GPU and oracle/_ref/libflame_ref_cuda.so (the reference's src/cuda/fp8_quant.cu, fp8_dequant.cu and
 pinned_host.cu compiled unmodified by `make -C oracle refcuda`).  For every BF16 bit pattern, NaN and infinity
@@ -6,7 +7,12 @@ included, and a list of inverse scales (ordinary, extreme, zero, infinite, NaN, 
 flame_bf16_to_fp8 of the reference wrote; for every FP8 code and a list of scales the BF16 bits its
 flame_fp8_to_bf16 wrote.  The CPU tests hold the oracle to these vectors.
 
-    python tests/golden/make_reference_kernel_golden.py OUT.npz
+The second file holds the output of the reference's int8 quantisation kernel (sage_quantize_tensor,
+src/sage_attention.rs:510-543, built by `make -C oracle refsage`) run with row_size = 128, i.e. as a per-128-block
+quantiser, on the inputs of `int8_inputs()` below (every BF16 bit pattern in order and shuffled, and N(0,1) data with
+outliers), given to it as fp32.
+
+    python tests/golden/make_reference_kernel_golden.py OUT_FP8.npz [OUT_INT8.npz]
 """
 import os
 import sys
@@ -21,6 +27,33 @@ F32 = np.float32
 SCALES = [F32(8.0) / F32(448.0), F32(1.0), F32(0.37) / F32(448.0), F32(3.0e-5), F32(1.0e30), F32(1.0e-30)]
 INV_SCALES = np.array([F32(1.0) / s for s in SCALES] + [0.0, np.inf, np.nan, -2.0, -np.inf], F32)
 DEC_SCALES = np.array(SCALES + [0.0, np.inf, -1.5], F32)
+
+
+def int8_inputs():
+    """name -> uint16 BF16 bit patterns, each a multiple of 256 long (the reference kernel needs whole thread blocks)."""
+    from flame_b200 import synthetic
+
+    every = np.arange(1 << 16, dtype=np.uint16)
+    rng = np.random.Generator(np.random.PCG64(7))
+    return {"every_pattern_in_order": every, "every_pattern_shuffled": rng.permutation(every),
+            "normal_with_outliers": synthetic.normal_with_outliers(1 << 16, seed=0)}
+
+
+def write_int8(out_path: str) -> None:
+    sage = capi.load_ref_sage()
+    assert sage is not None, "build oracle/_ref/libsage_quant_ref.so first (make -C oracle refsage)"
+    dev = torch.device("cuda", 0)
+    out = {}
+    for name, bits in int8_inputs().items():
+        x = torch.from_numpy(bits.view(np.int16)).to(dev).view(torch.bfloat16).float().contiguous()
+        codes = torch.empty(bits.size, dtype=torch.int8, device=dev)
+        scales = torch.empty(bits.size // 128, dtype=torch.float32, device=dev)
+        assert sage.sage_quantize_ref(x.data_ptr(), codes.data_ptr(), scales.data_ptr(), bits.size // 128, 128, None) == 0
+        torch.cuda.synchronize()
+        out[name + "_codes"] = codes.cpu().numpy()
+        out[name + "_scales"] = scales.cpu().numpy()
+    np.savez_compressed(out_path, device=np.array(torch.cuda.get_device_name(0)), **out)
+    print("wrote", out_path, sorted(out))
 
 
 def main(out_path: str) -> None:
@@ -49,3 +82,5 @@ def main(out_path: str) -> None:
 
 if __name__ == "__main__":
     main(sys.argv[1])
+    if len(sys.argv) > 2:
+        write_int8(sys.argv[2])

@@ -312,6 +312,36 @@ def test_legacy_entry_points_equal_the_reference_kernels_on_this_gpu(cuda_device
     assert torch.equal(c1, c2) and torch.equal(o1.view(torch.int16), o2.view(torch.int16))
 
 
+def test_int8_block_codec_equals_the_reference_int8_kernel_on_this_gpu(cuda_device):
+    """The reference has no per-128-block offload codec, but it has an int8 quantiser with this very formula:
+    sage_quantize_tensor (src/sage_attention.rs:510-543; scale = max|x|/127 per row, __float2int_rn(x/scale)).
+    Compiled unmodified and run with row_size = 128 on the same values, it must give the codes and scales of
+    flame_act_quant_int8_b128."""
+    sage = capi.load_ref_sage()
+    if sage is None:
+        pytest.skip("oracle/_ref/libsage_quant_ref.so was not built (reference checkout absent at build time)")
+    rng = np.random.Generator(np.random.PCG64(11))
+    every = np.arange(1 << 16, dtype=np.uint16)
+    cases = {"every pattern": every, "shuffled": rng.permutation(every),
+             "normal": synthetic.normal_with_outliers(1 << 20, seed=5),
+             "zeros and signed zeros": np.where(rng.random(1 << 12) < 0.5, 0, 0x8000).astype(np.uint16),
+             "tiny": (rng.integers(0, 0x0100, 1 << 12)).astype(np.uint16),            # sub-normal BF16 values
+             "huge": (0x7F00 + rng.integers(0, 0x80, 1 << 12)).astype(np.uint16)}    # up to the largest finite value
+    for name, bits in cases.items():
+        x = G.to_dev(bits, cuda_device)
+        codes, scales = G.quant("int8", x)
+        xf = x.float().contiguous()
+        rc = torch.empty(bits.size, dtype=torch.int8, device=cuda_device)
+        rs = torch.empty(bits.size // 128, dtype=torch.float32, device=cuda_device)
+        assert sage.sage_quantize_ref(xf.data_ptr(), rc.data_ptr(), rs.data_ptr(), bits.size // 128, 128, G.stream_ptr(cuda_device)) == 0
+        torch.cuda.synchronize()
+        a, b = codes.cpu().numpy().view(np.int8), rc.cpu().numpy()
+        sa, sb = scales.cpu().numpy(), rs.cpu().numpy()
+        bad = np.nonzero(a != b)[0]
+        assert bad.size == 0, (name, bad[:8], a[bad[:8]], b[bad[:8]], bits[bad[:8]])
+        assert np.array_equal(sa.view(np.uint32), sb.view(np.uint32)), name
+
+
 # ---- size-independent properties at benchmark sizes -------------------------------------------
 
 def test_large_tensor_properties(cuda_device):

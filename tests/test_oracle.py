@@ -50,6 +50,25 @@ def test_oracle_equals_the_reference_kernels_run_on_a_b200(golden_dir):
         assert np.array_equal(got[~nan], want[~nan]) and np.all((got[nan] & 0x7FFF) > 0x7F80), float(sc)
 
 
+def test_int8_block_oracle_equals_the_reference_int8_kernel_run_on_a_b200(golden_dir):
+    """int8_reference_sage_sm100.npz: codes and scales written by the reference's own int8 quantisation kernel
+    (sage_quantize_tensor, src/sage_attention.rs:510-543) run on a B200 with row_size = 128, on every BF16 bit
+    pattern (in order and shuffled; NaN and infinity included) and on N(0,1) data with outliers."""
+    src = open(os.path.join(golden_dir, "make_reference_kernel_golden.py")).read()
+    # the generator's input recipe, restated here because that script needs torch and a GPU to import
+    every = np.arange(1 << 16, dtype=np.uint16)
+    inputs = {"every_pattern_in_order": every,
+              "every_pattern_shuffled": np.random.Generator(np.random.PCG64(7)).permutation(every),
+              "normal_with_outliers": synthetic.normal_with_outliers(1 << 16, seed=0)}
+    assert "PCG64(7)" in src and "normal_with_outliers(1 << 16, seed=0)" in src      # the recipe above is the script's
+    g = _golden(golden_dir, "int8_reference_sage_sm100.npz")
+    for name, bits in inputs.items():
+        for impl in (capi.quant_int8_b128, codec_np.quant_int8_b128):
+            codes, scales = impl(bits)
+            assert np.array_equal(np.asarray(codes).view(np.int8), g[name + "_codes"]), (name, impl.__module__)
+            assert np.array_equal(np.asarray(scales, np.float32).view(np.uint32), g[name + "_scales"].view(np.uint32)), (name, impl.__module__)
+
+
 def test_decoder_matches_reference_golden(golden_dir):
     want = _golden(golden_dir, "fp8_reference_decoder.npy")
     lib = capi.load()
