@@ -342,6 +342,41 @@ def test_int8_block_codec_equals_the_reference_int8_kernel_on_this_gpu(cuda_devi
         assert np.array_equal(sa.view(np.uint32), sb.view(np.uint32)), name
 
 
+def test_fp8_block_codec_equals_the_reference_kernel_called_block_by_block(cuda_device):
+    """The reference has no per-block FP8 mode.  What it has is flame_bf16_to_fp8(x, inv_scale) and the rule of its
+    pool (src/activation_offload.rs:543-561): scale = absmax / 448, inv_scale = 1 / scale, both in fp32.  Calling the
+    reference's own kernel once per 128-element block with that block's inv_scale must give the bytes of
+    flame_act_quant_fp8_b128, and the scales must be absmax / 448."""
+    ref = capi.load_ref_cuda()
+    if ref is None:
+        pytest.skip("oracle/_ref/libflame_ref_cuda.so was not built (reference checkout absent at build time)")
+    rng = np.random.Generator(np.random.PCG64(13))
+    finite = synthetic.edge_values()
+    cases = {"normal": synthetic.normal_with_outliers(128 * 300, seed=9),
+             "every finite value, shuffled": rng.permutation(np.resize(finite, (finite.size + 127) // 128 * 128)),
+             "tiny": rng.integers(0x0500, 0x0C00, 128 * 40).astype(np.uint16)}      # 1e-36 .. 1e-31: 1/scale still finite
+    sp = G.stream_ptr(cuda_device)
+    for name, bits in cases.items():
+        x = G.to_dev(bits, cuda_device)
+        codes, scales = G.quant("fp8", x)
+        absmax = x.float().abs().view(-1, 128).amax(dim=1)
+        want_scales = absmax.cpu().numpy() / np.float32(448.0)           # IEEE fp32 division, as the pool does it (torch would multiply by 1/448)
+        assert np.array_equal(scales.cpu().numpy().view(np.uint32), want_scales.view(np.uint32)), name
+        theirs = torch.zeros(bits.size, dtype=torch.uint8, device=cuda_device)
+        with np.errstate(all="ignore"):
+            invs = (np.float32(1.0) / want_scales).astype(np.float32)
+        for b in range(bits.size // 128):
+            if not np.isfinite(invs[b]):
+                continue                                                 # an all-zero block, or a scale whose reciprocal overflows
+            assert ref.flame_bf16_to_fp8(x.data_ptr() + 256 * b, theirs.data_ptr() + 128 * b, float(invs[b]), 128, sp) == 0
+        torch.cuda.synchronize()
+        a, r = codes.cpu().numpy().reshape(-1, 128), theirs.cpu().numpy().reshape(-1, 128)
+        ok = np.isfinite(invs)
+        bad = np.nonzero((a[ok] != r[ok]).any(axis=1))[0]
+        assert bad.size == 0, (name, bad[:5])
+        assert ok.sum() >= 0.9 * ok.size, name
+
+
 # ---- size-independent properties at benchmark sizes -------------------------------------------
 
 def test_large_tensor_properties(cuda_device):
