@@ -122,6 +122,8 @@ def load_ref_cuda():
         lib.flame_cuda_alloc_pinned_host.restype, lib.flame_cuda_alloc_pinned_host.argtypes = vp, [sz, u]
         lib.flame_cuda_free_pinned_host.restype, lib.flame_cuda_free_pinned_host.argtypes = i, [vp]
         lib.flame_cuda_memcpy_async.restype, lib.flame_cuda_memcpy_async.argtypes = i, [vp, vp, sz, i, vp]
+        if hasattr(lib, "flame_fused_rms_norm_bf16"):      # src/cuda/fused_rms_norm.cu, built into the same library
+            lib.flame_fused_rms_norm_bf16.restype, lib.flame_fused_rms_norm_bf16.argtypes = i, [vp, vp, vp, i, i, f, vp]
         _REF_CUDA = lib
     return _REF_CUDA
 

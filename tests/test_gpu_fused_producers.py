@@ -47,6 +47,24 @@ def test_rmsnorm_with_codes(cuda_device, rows, cols, codec):
     assert fused_producers.take(y) is None              # handed out once
 
 
+@pytest.mark.parametrize("rows,cols", [(64, 3072), (9, 128), (17, 4096)])
+def test_rmsnorm_against_the_reference_kernel_on_this_gpu(cuda_device, rows, cols):
+    """src/cuda/fused_rms_norm.cu compiled unmodified: the same formula with another summation order, so the two BF16
+    outputs may differ by one unit in the last place where the fp32 values straddle a rounding boundary."""
+    ref = capi.load_ref_cuda()
+    if ref is None or not hasattr(ref, "flame_fused_rms_norm_bf16"):
+        pytest.skip("oracle/_ref/libflame_ref_cuda.so with the RMSNorm kernel was not built")
+    g = torch.Generator(device=cuda_device).manual_seed(cols)
+    x = (torch.randn(rows, cols, device=cuda_device, generator=g) * 2).to(torch.bfloat16)
+    w = (1 + 0.2 * torch.randn(cols, device=cuda_device, generator=g)).to(torch.bfloat16)
+    y, _ = fused_producers.rmsnorm(x, w, 1e-6)
+    theirs = torch.empty_like(x)
+    assert ref.flame_fused_rms_norm_bf16(x.data_ptr(), w.data_ptr(), theirs.data_ptr(), rows, cols, 1e-6, G.stream_ptr(cuda_device)) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(y.float(), theirs.float(), rtol=ONE_ULP, atol=1e-30)
+    assert (y != theirs).float().mean() < 0.02
+
+
 @pytest.mark.parametrize("rows,hidden", [(33, 9216), (7, 128), (129, 512)])
 @pytest.mark.parametrize("codec", [0, INT8, FP8])
 def test_swiglu_with_codes(cuda_device, rows, hidden, codec):
