@@ -271,6 +271,26 @@ def reference_gpu_path(args):
                           "frac_of_hbm": [round(qg / hbm_peak, 3), round(dg / hbm_peak, 3)],
                           "device_roundtrip_bf16eq_gbs": round(2 * step_bytes / (e0.elapsed_time(e2) * 1e-3) * 1e-9, 1)}
         del codes, back
+        if hasattr(ref, "flame_fused_rms_norm_bf16"):      # the producer of two of a block's saved tensors (src/cuda/fused_rms_norm.cu)
+            xr = tensors[0].view(TOKENS, HIDDEN)
+            wr = torch.ones(HIDDEN, dtype=torch.bfloat16, device=dev)
+            yr = torch.empty_like(xr)
+            flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+            ts = []
+            for k in range(25):
+                flush.zero_()
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record(transfer)
+                assert ref.flame_fused_rms_norm_bf16(xr.data_ptr(), wr.data_ptr(), yr.data_ptr(), TOKENS, HIDDEN, 1e-6, tp) == 0
+                a1.record(transfer)
+                torch.cuda.synchronize()
+                if k >= 5:
+                    ts.append(a0.elapsed_time(a1) * 1e3)
+            ts.sort()
+            us = ts[len(ts) // 2]
+            out["kernels"]["fused_rms_norm_bf16_us"] = round(us, 2)
+            out["kernels"]["fused_rms_norm_bf16_gbs"] = round(4.0 * TOKENS * HIDDEN / us * 1e-3, 1)
+            del flush, yr
         for mode in ("fp8", "none"):
             slot_bytes = (max_bytes + 1) // 2 if mode == "fp8" else max_bytes
             host = [ref.flame_cuda_alloc_pinned_host(slot_bytes, 0) for _ in tensors]       # cudaHostAllocDefault, as the pool does
