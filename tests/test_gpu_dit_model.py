@@ -5,6 +5,7 @@ that the allocator hands out again within a block, restores issued blocks ahead 
 when backward arrives."""
 import gc
 
+import numpy as np
 import pytest
 import torch
 
@@ -112,3 +113,51 @@ def test_int8_offload_keeps_the_large_gradients_close(cuda_device, dit, fused, b
     finally:
         W.FUSED_PRODUCERS = False
         ckpt.clear_activation_offload_pool()
+
+
+def test_many_training_steps_leave_nothing_behind(cuda_device):
+    """Thirty optimiser steps with everything switched on (deferred int8 pool with a small budget, producers that
+    emit codes, restore arena, prefetch): the loss falls, and afterwards no slot, pinned chunk, arena region or device
+    memory is still held."""
+    import gc
+
+    torch.manual_seed(1)
+    model = W.DiT(4).to(cuda_device, torch.bfloat16)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
+    x = torch.randn(1, W.TOKENS, W.HIDDEN, device=cuda_device, dtype=torch.bfloat16)
+    cos, sin = W.rope_tables(cuda_device)
+    saved = ckpt.saved_bytes_of(model.blocks[0], [x.detach().requires_grad_(True), cos, sin])
+    pool = ActivationOffloadPool(cuda_device, 64, saved, OffloadCompression.INT8_B128, deferred_inflight_bytes=96 << 20,
+                                 d2h_piece_bytes=1 << 20, h2d_piece_bytes=4 << 20)
+    arena = RestoreArena(cuda_device, 3 * saved)
+    ckpt.set_activation_offload_pool(pool)
+    ckpt.set_restore_arena(arena)
+    W.FUSED_PRODUCERS = True
+    model.decisions = [Decision.OFFLOAD_INT8] * 4
+    try:
+        losses, mem = [], []
+        for step in range(30):
+            loss = model(x, cos, sin).float().pow(2).mean()
+            loss.backward()
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+            losses.append(loss.detach())
+            if step in (9, 29):
+                del loss
+                gc.collect()
+                torch.cuda.synchronize()
+                mem.append(torch.cuda.memory_allocated())
+        losses = [float(v) for v in losses]
+        assert all(np.isfinite(losses)) and losses[-1] < losses[0]
+        assert mem[1] <= mem[0] + (8 << 20), mem                 # no growth between step 10 and step 30
+        st = pool.stats()
+        assert pool.in_flight() == 0 and st["pushes_queued"] == 0 and st["host_chunks_free"] == st["host_chunks_total"]
+        assert st["pushes"] == 30 * 4 * 7 == st["pulls"] + st["pushes_cancelled"] and st["push_rejected_full"] == 0
+        a = arena.stats()
+        assert a["live_regions"] == 0 and a["in_use_bytes"] == 0 and a["allocs"] == a["releases"] > 0
+    finally:
+        W.FUSED_PRODUCERS = False
+        model.decisions = None
+        ckpt.set_restore_arena(None)
+        ckpt.clear_activation_offload_pool()
+        pool.close()
