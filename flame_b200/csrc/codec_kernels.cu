@@ -1119,8 +1119,10 @@ swiglu_quant_kernel(const uint16_t* __restrict__ gu, uint16_t* __restrict__ h, u
     U32x8 o;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float a = __fmul_rn(__fmul_rn(gv[2 * i], __frcp_rn(1.0f + __expf(-gv[2 * i]))), uv[2 * i]);
-      const float b = __fmul_rn(__fmul_rn(gv[2 * i + 1], __frcp_rn(1.0f + __expf(-gv[2 * i + 1]))), uv[2 * i + 1]);
+      // sigmoid by the hardware exponential and reciprocal (each within a few units in the last place of fp32,
+      // far below the BF16 rounding of the result)
+      const float a = __fmul_rn(__fmul_rn(gv[2 * i], __fdividef(1.0f, 1.0f + __expf(-gv[2 * i]))), uv[2 * i]);
+      const float b = __fmul_rn(__fmul_rn(gv[2 * i + 1], __fdividef(1.0f, 1.0f + __expf(-gv[2 * i + 1]))), uv[2 * i + 1]);
       o.v[i] = pack_bf16x2(a, b);
     }
     if (live) st_plain32(h + row * (size_t)hidden + c0, o);
