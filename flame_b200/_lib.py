@@ -118,6 +118,7 @@ SIGNATURES = {
     "flame_offload_pool_read_slot": (_i, [_vp, Handle, _vp, _vp, _d]),
     "flame_offload_pool_stats": (_i, [_vp, C.POINTER(Stats)]),
     "flame_offload_inject_fault": (None, [_i, _i]),
+    "flame_offload_pool_pull_packed": (_i, [_vp, Handle, _vp, _vp, _vp, _u]),
     "flame_offload_pool_push_packed": (_i, [_vp, _vp, _vp, _sz, _vp, C.POINTER(Handle)]),
     "flame_act_rmsnorm_quant_b128": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, C.c_float, _i, _u, _vp]),
     "flame_act_swiglu_quant_b128": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _i, _u, _vp]),

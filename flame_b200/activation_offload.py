@@ -208,6 +208,23 @@ class ActivationOffloadPool:
             self._keep_alive.pop(handle.slot, None)
         self._meta.pop(handle.slot, None)
 
+    def pull_packed(self, handle: OffloadHandle, codes, scales, defer_wait: bool = False) -> None:
+        """Restore the compressed form itself into `codes` (uint8, one per element) and `scales` (float32, one per 128
+        elements): no dequantise launch; the caller expands it, e.g. several tensors with one launch."""
+        torch = self._torch
+        if codes.dtype != torch.uint8 or scales.dtype != torch.float32 or not codes.is_contiguous() or not scales.is_contiguous():
+            raise InvalidInput("ActivationOffloadPool::pull_packed: codes must be contiguous uint8 and scales contiguous float32")
+        info = self.slot_info(handle)
+        if codes.numel() < info["numel"] or scales.numel() < (info["numel"] + 127) // 128:
+            raise InvalidInput("ActivationOffloadPool::pull_packed: codes / scales are smaller than the tensor")
+        st = self._lib.flame_offload_pool_pull_packed(self._h, handle._c(), codes.data_ptr(), scales.data_ptr(), self._stream(),
+                                                     1 if defer_wait else 0)
+        if st != 0:
+            raise_for_status(st, _lib.last_error())
+        if not defer_wait:
+            self._keep_alive.pop(handle.slot, None)
+        self._meta.pop(handle.slot, None)
+
     def prefetch(self, handle: OffloadHandle, dst) -> None:
         """Start the restore into `dst` now; call wait_ready(handle.slot) before the first read."""
         self.pull_into(handle, dst, defer_wait=True)

@@ -61,6 +61,15 @@ def activation_offload_pool() -> Optional[ActivationOffloadPool]:
 
 
 _RESTORE_ARENA = None
+_BATCHED_CODEC = False
+
+
+def set_batched_codec(on: bool) -> None:
+    """Per-128-block pools: compress a block's saved tensors with one launch when its forward ends and expand them
+    with one launch when its backward begins (the pool then moves compressed bytes only, `push_packed` /
+    `pull_packed`), instead of one launch per tensor and staging tile inside the pool."""
+    global _BATCHED_CODEC
+    _BATCHED_CODEC = bool(on)
 
 
 def set_restore_arena(arena) -> None:
@@ -131,17 +140,18 @@ def saved_bytes_of(f: Callable[..., torch.Tensor], inputs: Sequence[torch.Tensor
 class _Entry:
     """One offloaded saved tensor (OffloadedTapeEntry's handle plus what restore needs)."""
 
-    __slots__ = ("handle", "shape", "dtype", "restored", "waited", "block", "__weakref__")
+    __slots__ = ("handle", "shape", "dtype", "restored", "waited", "block", "packed", "__weakref__")
 
     def __init__(self, handle, shape, dtype, block):
         self.handle, self.shape, self.dtype, self.block = handle, shape, dtype, block
         self.restored = None
         self.waited = False
+        self.packed = None      # (codes, scales) on the device while a batched restore waits to be expanded
 
     def __del__(self):
         # The graph was dropped without a backward pass (an evaluation step, an exception): the
         # slot must not stay Pushed for ever.
-        if self.restored is None:
+        if self.restored is None and self.packed is None and self.handle is not None:
             try:
                 self.block.pool.discard(self.handle)
             except Exception:
@@ -172,6 +182,10 @@ class _Block:
         self.restores_issued = False
         # per-128-block pools: producers that can emit codes beside their output do so while this block runs
         self.emit = int(pool.compression) if pool.compression in (OffloadCompression.INT8_B128, OffloadCompression.FP8_B128) else 0
+        # batched codec: the block's tensors are compressed by ONE launch when its forward ends and expanded by ONE
+        # launch when its backward begins, instead of one small launch per tensor and staging tile inside the pool
+        self.batch = bool(self.emit) and _BATCHED_CODEC
+        self._pending: list = []    # (entry, contiguous source) waiting for that one compress launch
 
     # -- forward -----------------------------------------------------------------------------
     def pack(self, t: torch.Tensor):
@@ -193,6 +207,13 @@ class _Block:
             return _View(hit[0], tuple(base.shape), inverse)
         try:
             pre = fused_producers.take(t) if self.emit else None
+            if pre is None and self.batch:
+                e = _Entry(None, (t.numel(),), t.dtype, self)      # pushed by finish_forward, with the rest of the block
+                self.entries.append(weakref.ref(e))
+                self._by_key[key] = (e, base)
+                self._pending.append((e, base))
+                self.bytes_offloaded += t.numel() * 2
+                return _View(e, tuple(base.shape), inverse)
             # a producer with the compress step built in already wrote this tensor's codes: no compress launch
             h = self.pool.push_packed(pre[0], pre[1], (t.numel(),)) if pre is not None else self.pool.push(base)
         except OffloadError as exc:  # pool exhausted: abandon offload for this block
@@ -211,7 +232,32 @@ class _Block:
         return _View(e, tuple(base.shape), inverse)
 
     def finish_forward(self) -> None:
+        if self._pending and not self.failed:
+            try:
+                self._compress_pending()
+            except OffloadError as exc:
+                log.warning("checkpoint_offload: pool push failed (%s), falling back to recompute", exc)
+                self.failed = True
+        self._pending = []
         self._by_key.clear()
+
+    def _compress_pending(self) -> None:
+        """One compress launch for every tensor of the block that no producer compressed, then their pushes."""
+        from . import _lib
+        lib = _lib.lib()
+        dev = self.pool.device
+        bufs = []
+        for e, base in self._pending:
+            n = base.numel()
+            bufs.append((torch.empty(n, dtype=torch.uint8, device=dev), torch.empty((n + 127) // 128, dtype=torch.float32, device=dev)))
+        arr = (_lib.ActTensor * len(bufs))(*[_lib.ActTensor(base.data_ptr(), c.data_ptr(), s_.data_ptr(), base.numel())
+                                             for (e, base), (c, s_) in zip(self._pending, bufs)])
+        rc = lib.flame_act_quant_b128_multi(self.emit, arr, len(bufs), 0, torch.cuda.current_stream(dev).cuda_stream)
+        if rc != 0:
+            raise OffloadError(f"flame_act_quant_b128_multi failed ({rc}): {_lib.last_error()}")
+        for (e, base), (c, s_) in zip(self._pending, bufs):
+            e.handle = self.pool.push_packed(c, s_, (base.numel(),))
+            self._handles.append(e.handle)
 
     def abandon(self) -> None:
         handles, self._handles = self._handles, []
@@ -228,7 +274,7 @@ class _Block:
         self.restores_issued = True
         for ref in reversed(self.entries):
             e = ref()
-            if e is not None and e.restored is None:
+            if e is not None and e.restored is None and e.packed is None:
                 self._restore(e)
 
     def _restore(self, e: "_Entry") -> None:
@@ -239,9 +285,33 @@ class _Block:
             e.restored = src.reshape(e.shape)
             e.waited = True
             return
+        if self.batch:     # the compressed form comes back now; it is expanded with the rest of the block, when first needed
+            n = e.shape[0]
+            codes = torch.empty(n, dtype=torch.uint8, device=self.pool.device)
+            scales = torch.empty((n + 127) // 128, dtype=torch.float32, device=self.pool.device)
+            self.pool.pull_packed(e.handle, codes, scales, defer_wait=True)
+            e.packed = (codes, scales)
+            return
         dst = _destination(e.shape, e.dtype, self.pool.device)
         self.pool.pull_into(e.handle, dst, defer_wait=True)
         e.restored = dst
+
+    def _expand(self) -> None:
+        """One dequantise launch for every entry of the block whose compressed form has come back."""
+        from . import _lib
+        live = [e for e in (r() for r in self.entries) if e is not None and e.packed is not None and e.restored is None]
+        if not live:
+            return
+        for e in live:
+            self.pool.wait_ready(e.handle.slot)
+        dsts = [_destination(e.shape, e.dtype, self.pool.device) for e in live]
+        arr = (_lib.ActTensor * len(live))(*[_lib.ActTensor(d.data_ptr(), e.packed[0].data_ptr(), e.packed[1].data_ptr(), d.numel())
+                                             for e, d in zip(live, dsts)])
+        rc = _lib.lib().flame_act_dequant_b128_multi(self.emit, arr, len(live), torch.cuda.current_stream(self.pool.device).cuda_stream)
+        if rc != 0:
+            raise OffloadError(f"flame_act_dequant_b128_multi failed ({rc}): {_lib.last_error()}")
+        for e, d in zip(live, dsts):
+            e.restored, e.waited, e.packed = d, True, None
 
     def unpack(self, obj):
         if isinstance(obj, _View):
@@ -252,8 +322,10 @@ class _Block:
             _SCHEDULER.on_backward_reach(self.index)
             if not self.restores_issued:
                 self.issue_restores()
-        if obj.restored is None:  # pushed after the block's restores were issued: cannot happen, but stay correct
+        if obj.restored is None and obj.packed is None:  # pushed after the block's restores were issued: cannot happen, but stay correct
             self._restore(obj)
+        if obj.restored is None and obj.packed is not None:
+            self._expand()
         if not obj.waited:
             self.pool.wait_ready(obj.handle.slot)
             obj.waited = True

@@ -410,11 +410,27 @@ FlameOffloadStatus wait_issued(FlameOffloadPool* p, std::unique_lock<std::mutex>
   return FLAME_OFFLOAD_OK;
 }
 
-cudaError_t enqueue_pull(FlameOffloadPool& p, Slot& s, uint8_t* dst, cudaStream_t compute, unsigned flags) {
+cudaError_t enqueue_pull(FlameOffloadPool& p, Slot& s, uint8_t* dst, uint8_t* scales_dst, cudaStream_t compute, unsigned flags) {
   POOL_TRY(s.consumer.record(compute), "pull: cudaEventRecord(consumer)");
   POOL_TRY(s.d2h_done.make_wait(p.s_h2d), "pull: wait(d2h_done)");
   const size_t nchunks = s.chunks.size();
-  if (!p.compressed()) {
+  if (scales_dst) {
+    // The compressed form itself is wanted (the caller dequantises it, several tensors to a launch): each chunk's
+    // codes and scales go straight to their places in the caller's two buffers; no staging tile, no kernel.
+    POOL_TRY(s.consumer.make_wait(p.s_h2d), "pull: wait(consumer)");
+    for (size_t k = 0; k < nchunks; ++k) {
+      const uint64_t e0 = k * p.chunk_elems;
+      const uint64_t ec = std::min<uint64_t>(p.chunk_elems, s.numel - e0);
+      const uint64_t sb = 4u * ((ec + 127u) / 128u);
+      const uint8_t* src = p.chunk_ptr(s.chunks[k]);
+      POOL_TRY(copy_in_pieces(dst + e0, src, ec, cudaMemcpyHostToDevice, p.s_h2d, p.h2d_piece), "pull: H2D(codes)");
+      POOL_TRY(memcpy_async_checked(scales_dst + 4u * (e0 / 128u), src + packed_scales_offset(ec), sb, cudaMemcpyHostToDevice, p.s_h2d),
+               "pull: H2D(scales)");
+      p.stats.bytes_link_in += ec + sb;
+    }
+    POOL_TRY(s.h2d_done.record(p.s_h2d), "pull: record(h2d_done)");
+    POOL_TRY(s.ready.record(p.s_h2d), "pull: record(ready)");
+  } else if (!p.compressed()) {
     POOL_TRY(s.consumer.make_wait(p.s_h2d), "pull: wait(consumer)");
     for (size_t k = 0; k < nchunks; ++k) {
       const uint64_t off = k * p.chunk_src_bytes;
@@ -746,7 +762,21 @@ static FlameOffloadStatus push_impl(FlameOffloadPool* p, const void* src, const 
   return FLAME_OFFLOAD_OK;
 }
 
+static FlameOffloadStatus pull_impl(FlameOffloadPool* p, FlameOffloadHandle h, void* dst, size_t dst_bytes, void* scales_dst, void* compute_stream, unsigned int flags);
+
 FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* p, FlameOffloadHandle h, void* dst, size_t dst_bytes, void* compute_stream, unsigned int flags) {
+  return pull_impl(p, h, dst, dst_bytes, nullptr, compute_stream, flags);
+}
+
+FlameOffloadStatus flame_offload_pool_pull_packed(FlameOffloadPool* p, FlameOffloadHandle h, void* codes_dst, void* scales_dst, void* compute_stream, unsigned int flags) {
+  if (!p) return fail(FLAME_OFFLOAD_ERR_INVALID, "pull_packed: null pool");
+  if (p->compression != FLAME_OFFLOAD_COMPRESSION_INT8_B128 && p->compression != FLAME_OFFLOAD_COMPRESSION_FP8_B128)
+    return fail(FLAME_OFFLOAD_ERR_UNSUPPORTED, "pull_packed: the pool is not in a per-128-block mode");
+  if (!scales_dst) return fail(FLAME_OFFLOAD_ERR_INVALID, "pull_packed: null scales destination");
+  return pull_impl(p, h, codes_dst, (size_t)-1, scales_dst, compute_stream, flags);
+}
+
+static FlameOffloadStatus pull_impl(FlameOffloadPool* p, FlameOffloadHandle h, void* dst, size_t dst_bytes, void* scales_dst, void* compute_stream, unsigned int flags) {
   if (!p) return fail(FLAME_OFFLOAD_ERR_INVALID, "pull: null pool");
   std::unique_lock<std::mutex> lk(p->mu);
   FlameOffloadStatus st = p->check_handle(h, "ActivationOffloadPool::pull");
@@ -768,7 +798,7 @@ FlameOffloadStatus flame_offload_pool_pull_into(FlameOffloadPool* p, FlameOffloa
     return fail(FLAME_OFFLOAD_ERR_CUDA, text);
   }
   DeviceGuard guard(p->device);
-  cudaError_t e = enqueue_pull(*p, s, static_cast<uint8_t*>(dst), (cudaStream_t)compute_stream, flags);
+  cudaError_t e = enqueue_pull(*p, s, static_cast<uint8_t*>(dst), static_cast<uint8_t*>(scales_dst), (cudaStream_t)compute_stream, flags);
   if (e != cudaSuccess) return FLAME_OFFLOAD_ERR_CUDA;  // slot stays Pushed (src/activation_offload.rs:704-711)
   if (trace_on())
     fprintf(stderr, "[flame_offload] pull slot=%llu bytes=%llu chunks=%zu deferred_wait=%u keep=%u\n", (unsigned long long)h.slot,

@@ -276,6 +276,12 @@ FlameOffloadStatus flame_offload_pool_wait_ready(FlameOffloadPool* pool, size_t 
  * must stay alive until flame_offload_pool_source_released() reports 1.  pull_into restores BF16 as usual. */
 FlameOffloadStatus flame_offload_pool_push_packed(FlameOffloadPool* pool, const void* codes_device, const void* scales_device, size_t numel, void* compute_stream, FlameOffloadHandle* out_handle);
 
+/* The counterpart of push_packed: restores the compressed form itself, `numel` codes into `codes_device` and
+ * ceil(numel/128) scales into `scales_device` (no staging tile, no dequantise launch), so that the caller can
+ * expand several tensors with one flame_act_dequant_b128_multi launch when it needs them.  Flags and ordering as
+ * for pull_into; the pool must be in a per-128-block mode. */
+FlameOffloadStatus flame_offload_pool_pull_packed(FlameOffloadPool* pool, FlameOffloadHandle handle, void* codes_device, void* scales_device, void* compute_stream, unsigned int flags);
+
 /* Deferred offload only (deferred_inflight_bytes > 0).  1: the tensor was still waiting for its turn; its slot
  * and chunks are free again, nothing was or will be read from the source, which the caller goes on using.
  * 0: its copies are already enqueued (or the pool is not deferred): restore it with pull_into as usual.

@@ -89,13 +89,15 @@ def test_uncompressed_offload_reproduces_resident_gradients(cuda_device, dit, fl
         pool.close()
 
 
-@pytest.mark.parametrize("budget", [1 << 40, 64 << 20])
+@pytest.mark.parametrize("batched", [False, True])
+@pytest.mark.parametrize("budget", [0, 1 << 40, 64 << 20])
 @pytest.mark.parametrize("fused", [False, True])
-def test_int8_offload_keeps_the_large_gradients_close(cuda_device, dit, fused, budget):
+def test_int8_offload_keeps_the_large_gradients_close(cuda_device, dit, fused, budget, batched):
     """budget 64 MB: most tensors are still queued when backward arrives; those that a producer compressed are
     dequantised on the device from their codes, the others are used as they are."""
     grads, want, saved = dit
     W.FUSED_PRODUCERS = fused
+    ckpt.set_batched_codec(batched)     # one compress and one dequantise launch per block, compressed bytes through the pool
     try:
         base = grads(None) if fused else want
         pool = ActivationOffloadPool(cuda_device, 64, saved, OffloadCompression.INT8_B128, deferred_inflight_bytes=budget,
@@ -108,10 +110,14 @@ def test_int8_offload_keeps_the_large_gradients_close(cuda_device, dit, fused, b
             assert _rel(base[i], got[i]) < 0.06, (i, _rel(base[i], got[i]))
         st = pool.stats()
         assert st["pushes"] == 35 and pool.in_flight() == 0 and st["pulls"] + st["pushes_cancelled"] == 35
-        if budget < (1 << 30):
+        if 0 < budget < (1 << 30):
             assert st["pushes_cancelled"] > 0
+        if batched and budget >= (1 << 40):
+            # nothing went through the pool's own codec kernels: 5 compress + 5 dequantise launches were the hooks'
+            assert st["codec_launches"] == 0
     finally:
         W.FUSED_PRODUCERS = False
+        ckpt.set_batched_codec(False)
         ckpt.clear_activation_offload_pool()
 
 
