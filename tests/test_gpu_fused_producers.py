@@ -120,6 +120,14 @@ def test_push_packed_round_trip(cuda_device, mode, codec):
         out = pool.pull(h)
         torch.cuda.synchronize()
         assert np.array_equal(G.bits_of(out), want) and pool.stats()["codec_launches"] > 0      # only the restore launched
+        # and the compressed form itself back, from a tensor the pool compressed on its own
+        launches = pool.stats()["codec_launches"]
+        h = pool.push(x)
+        c2, s2 = torch.zeros_like(codes), torch.zeros_like(scales)
+        pool.pull_packed(h, c2, s2)
+        torch.cuda.synchronize()
+        assert np.array_equal(c2.cpu().numpy(), wc.view(np.uint8)) and np.array_equal(s2.cpu().numpy().view(np.uint32), ws.view(np.uint32))
+        assert pool.stats()["codec_launches"] == launches + (n + (1 << 15) * 8 - 1) // ((1 << 15) * 8) and pool.in_flight() == 0
         if deferred:                                    # cancelled before it went out: dequantised on the device
             pool.hold_offloads(True)
             h = pool.push_packed(codes, scales, (n,))
@@ -130,6 +138,8 @@ def test_push_packed_round_trip(cuda_device, mode, codec):
     plain = ActivationOffloadPool(cuda_device, 2, 2 * n, OffloadCompression.NONE)
     with pytest.raises(Unsupported):
         plain.push_packed(codes, scales, (n,))
+    with pytest.raises(Unsupported):
+        plain.pull_packed(plain.push(x), codes, scales)
     plain.close()
 
 
