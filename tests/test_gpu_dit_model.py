@@ -89,9 +89,9 @@ def test_uncompressed_offload_reproduces_resident_gradients(cuda_device, dit, fl
         pool.close()
 
 
-@pytest.mark.parametrize("batched", [False, True])
-@pytest.mark.parametrize("budget", [0, 1 << 40, 64 << 20])
-@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("fused,budget,batched", [
+    (False, 0, False), (True, 0, False), (False, 1 << 40, False), (True, 1 << 40, False), (False, 64 << 20, False),
+    (True, 64 << 20, False), (False, 1 << 40, True), (True, 64 << 20, True), (True, 0, True)])
 def test_int8_offload_keeps_the_large_gradients_close(cuda_device, dit, fused, budget, batched):
     """budget 64 MB: most tensors are still queued when backward arrives; those that a producer compressed are
     dequantised on the device from their codes, the others are used as they are."""
