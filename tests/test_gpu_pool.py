@@ -427,6 +427,33 @@ def test_injected_kernel_and_alloc_failures(cuda_device):
     torch.cuda.synchronize()
 
 
+def test_deferred_offload_failure_is_reported_by_the_next_call(cuda_device):
+    """A deferred offload fails on the pool's thread after push() has returned OK (host-side injection): the slot is
+    marked, source_released and pull report it, the slot is given up and the pool goes on working."""
+    lib = _lib.lib()
+    pool = ActivationOffloadPool(cuda_device, 2, 1 << 16, INT8B, deferred_inflight_bytes=1 << 20)
+    bits = synthetic.normal_with_outliers(1000, seed=1)
+    x = G.to_dev(bits, cuda_device)
+    for kind in (2, 1):                             # the compress launch, then a copy
+        pool.hold_offloads(True)
+        h = pool.push(x)                            # queued: nothing has run yet
+        lib.flame_offload_inject_fault(kind, 1)
+        pool.hold_offloads(False)                   # the pool's thread picks it up and hits the injected error
+        pool.synchronize(10.0)
+        with pytest.raises(CudaError, match="deferred offload"):
+            pool.source_released(h)
+        with pytest.raises(CudaError, match="deferred offload"):
+            pool.pull(h)
+        assert pool.in_flight() == 0
+        st = pool.stats()
+        assert st["host_chunks_free"] == st["host_chunks_total"]
+        out = pool.pull(pool.push(x))
+        torch.cuda.synchronize()
+        assert np.array_equal(G.bits_of(out), capi.dequant_int8_b128(*capi.quant_int8_b128(bits)))
+    lib.flame_offload_inject_fault(0, 1)
+    pool.close()
+
+
 def test_synchronize_times_out_instead_of_hanging(cuda_device):
     """A bounded host wait: with a long copy queued, a zero timeout reports TIMEOUT and the pool stays usable."""
     from flame_b200.errors import Timeout
