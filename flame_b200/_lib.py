@@ -47,6 +47,10 @@ class ActTensor(C.Structure):
     _fields_ = [("bf16", C.c_void_p), ("codes", C.c_void_p), ("scales", C.c_void_p), ("n", C.c_size_t)]
 
 
+class ActLaunchInfo(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("grid", "resident_per_sm", "tiles_per_block", "form")]
+
+
 class LinkProbe(C.Structure):
     _fields_ = [(n, C.c_double) for n in ("d2h_gbs", "h2d_gbs", "hbm_copy_gbs", "quant_gbs", "dequant_gbs")]
 
@@ -58,7 +62,7 @@ class PolicyTensor(C.Structure):
 class PolicyInput(C.Structure):
     _fields_ = [("d2h_gbs", C.c_double), ("h2d_gbs", C.c_double), ("fwd_ms", C.c_double), ("bwd_ms", C.c_double),
                 ("device_budget_bytes", C.c_uint64), ("lossy_codec", C.c_int32), ("link_utilisation", C.c_double),
-                ("interference", C.c_double)]
+                ("interference", C.c_double), ("overhead_cap_ms", C.c_double)]
 
 
 class PolicyBlock(C.Structure):
@@ -99,6 +103,9 @@ SIGNATURES = {
     "flame_act_packed_scales_offset": (_sz, [_sz]),
     "flame_act_packed_bytes": (_sz, [_sz]),
     "flame_act_set_max_ctas": (_i, [_i]),
+    "flame_act_set_compress_form": (_i, [_i]),
+    "flame_act_last_launch": (None, [C.POINTER(ActLaunchInfo)]),
+    "flame_act_query_resident_blocks": (_i, [_i, _u, _i, _i]),
     "flame_act_offload_packed_noalloc": (_i, [_vp, _vp, _sz, _i, _u, _vp]),
     "flame_offload_pool_create": (_vp, [_sz, _sz, _i, C.POINTER(PoolConfig)]),
     "flame_offload_pool_destroy": (None, [_vp]),

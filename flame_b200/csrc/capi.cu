@@ -177,4 +177,17 @@ size_t flame_act_packed_bytes(size_t n) { return flame_act_packed_scales_offset(
 
 int flame_act_set_max_ctas(int max_ctas) { return set_max_ctas(max_ctas); }
 
+int flame_act_set_compress_form(int form) { return set_compress_form(form); }
+
+void flame_act_last_launch(FlameActLaunchInfo* out) {
+  if (!out) return;
+  const LaunchRecord r = last_launch();
+  out->grid = r.ctas; out->resident_per_sm = r.resident_per_sm; out->tiles_per_block = r.tiles_per_cta; out->form = r.form;
+}
+
+int flame_act_query_resident_blocks(int codec, unsigned int flags, int form, int compress) {
+  if (codec != kCodecInt8 && codec != kCodecFp8) return -1;
+  return query_resident_ctas(codec, flags, form, compress != 0);
+}
+
 }  // extern "C"

@@ -11,13 +11,18 @@
 // an instruction count per element that stays under the issue budget
 // (~18 lane-instructions per element at full HBM rate; in practice ~10).
 //
-// Compress tile: 256 threads x 2 x 32-byte loads = 8192 elements = 64 blocks of
-// 128.  Eight consecutive lanes hold one block (16 elements each), so the
-// block's absmax is three shuffles and the per-block divisions are paid once
-// per 16 elements of a lane.  Codes and scales are written into a shared-memory
-// tile (double buffered) and leave the SM as two bulk asynchronous copies
-// (cp.async.bulk.global.shared::cta), so the store path costs one instruction
-// per tile instead of one per thread.  Cluster size is 1; every copy is CTA-local.
+// Compress tile: 256 threads x 64 bytes = 8192 elements = 64 blocks of 128.  A
+// lane holds 32 consecutive elements (two 32-byte loads), four consecutive
+// lanes hold one block: the block's absmax is a tree of packed BF16 maxima in
+// the lane and two shuffles across the four lanes, and the per-block work (one
+// exactly rounded scale, one exactly rounded reciprocal) is paid once per 32
+// elements of a lane.  By default every lane writes its 32 codes with two
+// 16-byte stores and one lane in four writes the scale: no shared memory, no
+// barrier.  FLAME_ACT_STAGED_STORES selects the variant that stages each warp's
+// 1024 codes and 8 scales in a shared-memory slice of its own and lets one lane
+// send them out as two bulk asynchronous copies
+// (cp.async.bulk.global.shared::cta; warp-level synchronisation only, cluster
+// size 1, every copy CTA-local).  Both write the same bytes.
 //
 // Output addressing is "packed chunks": chunk c of `chunk_elems` elements lives
 // at out + c*chunk_stride, codes first, its scales at a byte offset inside the
@@ -35,7 +40,10 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+#include <atomic>
+#include <mutex>
 #include <type_traits>
+#include <vector>
 
 #include "codec_kernels.cuh"
 
@@ -43,12 +51,16 @@ namespace flame_b200 {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kLaneElems = 16;                               // BF16 per 32-byte load
-constexpr int kUnroll = 2;                                   // loads in flight per thread
-constexpr int kTileElems = kThreads * kLaneElems * kUnroll;  // 8192
-constexpr int kTileBlocks = kTileElems / 128;                // 64 scales per tile
-constexpr int kLanesPerBlock = 128 / kLaneElems;             // 8
-constexpr int kStagedBufBytes = kTileElems + kTileBlocks * 4;  // one staged tile: codes then scales
+constexpr int kLaneElems = 16;                               // BF16 per 32-byte access
+constexpr int kLaneLoads = 2;                                // 32-byte loads per lane per tile: 32 consecutive elements
+constexpr int kCompLaneElems = kLaneElems * kLaneLoads;      // 32
+constexpr int kTileElems = kThreads * kCompLaneElems;        // 8192
+constexpr int kLanesPerBlock = 128 / kLaneElems;             // 8: lanes per block where a lane holds 16 elements (dequantise, producers)
+constexpr int kCompLanesPerBlock = 128 / kCompLaneElems;     // 4: lanes per block in the compress kernels
+constexpr int kWarpCodes = 32 * kCompLaneElems;              // 1024 codes per warp per tile
+constexpr int kWarpScales = kWarpCodes / 128;                // 8 scales per warp per tile
+constexpr int kWarpSliceBytes = kWarpCodes + kWarpScales * 4;  // staged variant: one warp's codes then scales (1056, a multiple of 16)
+constexpr int kStagedSmemBytes = (kThreads / 32) * 2 * kWarpSliceBytes;  // two slices per warp
 constexpr int kDequantUnroll = 4;                            // 16-byte code loads in flight per thread
 constexpr int kDequantTileElems = kThreads * kLaneElems * kDequantUnroll;  // 16384
 
@@ -93,18 +105,40 @@ __device__ __forceinline__ void unpack16(const U32x8& r, float (&x)[16]) {
   for (int i = 0; i < 8; ++i) { x[2 * i] = bf16lo(r.v[i]); x[2 * i + 1] = bf16hi(r.v[i]); }
 }
 
-// fmaxf ignores a NaN operand, so a NaN element never becomes the absmax.
-template <int N>
-__device__ __forceinline__ float absmax_n(const float (&x)[N]) {
-  float m0 = fabsf(x[0]), m1 = fabsf(x[1]);
-#pragma unroll
-  for (int i = 2; i < N; i += 2) { m0 = fmaxf(m0, fabsf(x[i])); m1 = fmaxf(m1, fabsf(x[i + 1])); }
-  return fmaxf(m0, m1);
+// max(|a|, |b|) of two packed BF16 pairs in one instruction.  The sign of each result half is the xor of the
+// operands' signs and is masked away by the caller.  A NaN operand is ignored (the other one is returned), so a
+// NaN element never becomes the absmax; only an all-NaN set gives NaN.
+__device__ __forceinline__ uint32_t max_abs_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
 }
 
-// Max over the 8 lanes that hold one 128-element block.
+// absmax of NW words of two BF16 each, as a float (exact: a maximum only selects).
+template <int NW>
+__device__ __forceinline__ float absmax_words(const uint32_t* w) {
+  static_assert(NW >= 2 && (NW & (NW - 1)) == 0, "a power of two of words");
+  uint32_t t[NW / 2];
+#pragma unroll
+  for (int i = 0; i < NW / 2; ++i) t[i] = max_abs_bf16x2(w[2 * i], w[2 * i + 1]);
+#pragma unroll
+  for (int n = NW / 4; n >= 1; n >>= 1) {
+#pragma unroll
+    for (int i = 0; i < n; ++i) t[i] = max_abs_bf16x2(t[2 * i], t[2 * i + 1]);
+  }
+  const float lo = __uint_as_float((t[0] << 16) & 0x7FFF0000u), hi = __uint_as_float(t[0] & 0x7FFF0000u);
+  return fmaxf(lo, hi);  // fmaxf ignores a NaN operand
+}
+
+// Max over the 8 lanes that hold one 128-element block (16 elements per lane).
 __device__ __forceinline__ float absmax_8lanes(float m) {
   m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 4));
+  m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+  m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+  return m;
+}
+// Max over the 4 lanes that hold one block (32 elements per lane).
+__device__ __forceinline__ float absmax_4lanes(float m) {
   m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
   m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
   return m;
@@ -151,29 +185,46 @@ __device__ __forceinline__ uint32_t pack_s8x4(int e0, int e1, int e2, int e3) {
   return d;
 }
 
-template <int N, bool kMulInv>
-__device__ __forceinline__ void encode_int8(const float (&x)[N], float amax, float& scale, uint32_t (&out)[N / 4]) {
+// The rare scales that Markstein's sequence does not cover (all-ones significand, extreme exponents) take the IEEE
+// division; out of line, so that the common path carries neither its code nor its registers.
+__device__ __noinline__ int int8_code_by_division(float x, float scale) { return f32_to_s32_rne(__fdiv_rn(x, scale)); }
+
+// NW words (two BF16 each) of one lane -> NW/2 words of four codes.
+template <int NW, bool kMulInv>
+__device__ __forceinline__ void encode_int8(const uint32_t* raw, float amax, float& scale, uint32_t* out) {
   scale = div_const<127>(amax);
-  int r[N];
   if (kMulInv) {
     const float inv = __fdiv_rn(1.0f, scale);
 #pragma unroll
-    for (int i = 0; i < N; ++i) r[i] = max(f32_to_s32_rne(__fmul_rn(x[i], inv)), -127);  // -inf would pack as -128
+    for (int i = 0; i < NW / 2; ++i) {
+      const uint32_t w0 = raw[2 * i], w1 = raw[2 * i + 1];
+      out[i] = pack_s8x4(max(f32_to_s32_rne(__fmul_rn(bf16lo(w0), inv)), -127), max(f32_to_s32_rne(__fmul_rn(bf16hi(w0), inv)), -127),
+                         max(f32_to_s32_rne(__fmul_rn(bf16lo(w1), inv)), -127), max(f32_to_s32_rne(__fmul_rn(bf16hi(w1), inv)), -127));  // -inf would pack as -128
+    }
   } else if (markstein_ok(scale)) {
     const float inv = __frcp_rn(scale);
+    auto q = [&](float x) {
+      const float q0 = __fmul_rn(x, inv);
+      const float e = __fmaf_rn(-q0, scale, x);
+      return f32_to_s32_rne(__fmaf_rn(e, inv, q0));
+    };
 #pragma unroll
-    for (int i = 0; i < N; ++i) {
-      const float q0 = __fmul_rn(x[i], inv);
-      const float e = __fmaf_rn(-q0, scale, x[i]);
-      r[i] = f32_to_s32_rne(__fmaf_rn(e, inv, q0));
+    for (int i = 0; i < NW / 2; ++i) {
+      const uint32_t w0 = raw[2 * i], w1 = raw[2 * i + 1];
+      out[i] = pack_s8x4(q(bf16lo(w0)), q(bf16hi(w0)), q(bf16lo(w1)), q(bf16hi(w1)));
     }
+  } else if (amax == 0.0f) {
+    // every element is zero or NaN: x / 0 is NaN either way, which converts to 0
+#pragma unroll
+    for (int i = 0; i < NW / 2; ++i) out[i] = 0u;
   } else {
-    // scale == 0 lands here: 0/0 is NaN, which converts to 0.
 #pragma unroll
-    for (int i = 0; i < N; ++i) r[i] = f32_to_s32_rne(__fdiv_rn(x[i], scale));
+    for (int i = 0; i < NW / 2; ++i) {
+      const uint32_t w0 = raw[2 * i], w1 = raw[2 * i + 1];
+      out[i] = pack_s8x4(int8_code_by_division(bf16lo(w0), scale), int8_code_by_division(bf16hi(w0), scale),
+                         int8_code_by_division(bf16lo(w1), scale), int8_code_by_division(bf16hi(w1), scale));
+    }
   }
-#pragma unroll
-  for (int i = 0; i < N / 4; ++i) out[i] = pack_s8x4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
 }
 
 // ---- FP8 E4M3, the reference's encoder (src/cuda/fp8_quant.cu:19-57) --------
@@ -210,9 +261,17 @@ __device__ __forceinline__ uint32_t fp8_encode_legacy(float x, float inv) {
   const float y = __fmul_rn(x, inv);
   return (y != y) ? 0x30u : fp8_encode_ref(y, x);
 }
+// Out of line: called for the few elements the fast path cannot decide, so that the common path carries neither
+// the exact encoder's code nor its registers.
 template <bool kLegacy>
-__device__ __forceinline__ uint32_t fp8_encode_exact(float x, float inv) {
+__device__ __noinline__ uint32_t fp8_encode_exact(float x, float inv) {
   return kLegacy ? fp8_encode_legacy(x, inv) : fp8_encode_ref_scaled(x, inv);
+}
+__device__ __noinline__ uint32_t fp8_encode_ocp_scaled(float x, float inv) {
+  uint16_t r;
+  const float y = scaled(x, inv);
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.0f), "f"(y));
+  return r & 0xFFu;
 }
 
 // Fast form of the same encoder for a lane's worth of magnitudes, two at a time,
@@ -224,7 +283,7 @@ __device__ __forceinline__ uint32_t fp8_encode_exact(float x, float inv) {
 // equals round-half-up of |y|.  |y| >= 248 must give 0x7F: those lanes are made
 // NaN, which the converter encodes as 0x7F.  Zero gives 0.  `min_all` collects the
 // smallest magnitude seen, so that the caller can tell whether any lane needs
-// more care (see fp8_encode_lane_ref).
+// more care (see fp8_encode_words_ref).
 template <bool kNanPropagates = false>
 __device__ __forceinline__ uint32_t fp8_encode_pair_fast(float ylo_abs, float yhi_abs, __half2& min_all) {
   uint32_t h;
@@ -238,51 +297,45 @@ __device__ __forceinline__ uint32_t fp8_encode_pair_fast(float ylo_abs, float yh
   return c;  // low byte = code(ylo), high byte = code(yhi); bit 7 may be set on saturated lanes
 }
 
-// N elements of one lane with the reference encoder: codes of x[i] * inv, inv finite and positive.
-// raw: the N/2 input words (two BF16 each), which carry the sign bits.
+// NW words (two BF16 each) of one lane with the reference encoder: codes of x * inv, inv finite and positive.
+// The words carry the sign bits.
 //   common case  : every magnitude is 0 or >= 2^-6 and no source element is zero: hardware path,
 //                  sign = sign bit of x.
 //   zeros present: same codes, but a zero magnitude keeps sign 0 (`val < 0` is false for -0.0).
 //   a magnitude in (0, 2^-6): the reference's float formula decides; the lane is re-encoded exactly.
 // kLegacy (the element-wise entry point): a NaN element also sends the lane to the exact arm, which
 // gives it the reference's 0x30; the block codecs keep NaN on the fast path (saturation code, sign of x).
-template <int N, bool kLegacy = false>
-__device__ __forceinline__ void fp8_encode_lane_ref(const float (&x)[N], const uint32_t* raw, float inv, uint32_t (&out)[N / 4]) {
+template <int NW, bool kLegacy = false>
+__device__ __forceinline__ void fp8_encode_words_ref(const uint32_t* raw, float inv, uint32_t* out) {
   __half2 min_all = __half2half2(__ushort_as_half((unsigned short)0x7BFF));  // 65504
 #pragma unroll
-  for (int i = 0; i < N / 4; ++i) {
-    const uint32_t c01 = fp8_encode_pair_fast<kLegacy>(__fmul_rn(fabsf(x[4 * i]), inv), __fmul_rn(fabsf(x[4 * i + 1]), inv), min_all);
-    const uint32_t c23 = fp8_encode_pair_fast<kLegacy>(__fmul_rn(fabsf(x[4 * i + 2]), inv), __fmul_rn(fabsf(x[4 * i + 3]), inv), min_all);
+  for (int i = 0; i < NW / 2; ++i) {
+    const uint32_t w0 = raw[2 * i], w1 = raw[2 * i + 1];
+    const uint32_t c01 = fp8_encode_pair_fast<kLegacy>(__fmul_rn(fabsf(bf16lo(w0)), inv), __fmul_rn(fabsf(bf16hi(w0)), inv), min_all);
+    const uint32_t c23 = fp8_encode_pair_fast<kLegacy>(__fmul_rn(fabsf(bf16lo(w1)), inv), __fmul_rn(fabsf(bf16hi(w1)), inv), min_all);
     const uint32_t mag = __byte_perm(c01, c23, 0x5410);
-    const uint32_t sgn = __byte_perm(raw[2 * i], raw[2 * i + 1], 0x7531);  // high bytes of the four BF16
+    const uint32_t sgn = __byte_perm(w0, w1, 0x7531);  // high bytes of the four BF16
     out[i] = (mag & 0x7F7F7F7Fu) | (sgn & 0x80808080u);
   }
-  // anything below 2^-6 (0x2400 in FP16)?  Zero counts: rare enough to be handled off the fast path.
-  // The careful arms unpack the elements again from `raw` so that x[] need not stay in registers
-  // across the fast loop.
+  // anything below 2^-6 (0x2400 in FP16)?  Zero counts: rare enough to be handled off the fast path.  The few
+  // elements concerned (zero, a magnitude in (0, 2^-6), and for the element-wise entry point NaN) are encoded
+  // again one by one with the exact restatement; every other byte of the fast path stands.
   const __half thr = __ushort_as_half((unsigned short)0x2400);
   const bool careful = kLegacy ? !__hge(__hmin_nan(__low2half(min_all), __high2half(min_all)), thr)
                                : __hlt(__hmin(__low2half(min_all), __high2half(min_all)), thr);
   if (careful) {
-    bool tiny = false;
 #pragma unroll
-    for (int i = 0; i < N / 2; ++i) {
-      const float lo = bf16lo(raw[i]), hi = bf16hi(raw[i]);
-      tiny |= (lo != 0.0f) && (__fmul_rn(fabsf(lo), inv) < 0.015625f);
-      tiny |= (hi != 0.0f) && (__fmul_rn(fabsf(hi), inv) < 0.015625f);
-      if (kLegacy) tiny |= (lo != lo) || (hi != hi);
-    }
-    if (!tiny) {
+    for (int i = 0; i < NW / 2; ++i) {
+      uint32_t o = out[i];
 #pragma unroll
-      for (int i = 0; i < N / 4; ++i) {
-        const uint32_t mag = out[i] & 0x7F7F7F7Fu;
-        out[i] = mag | (out[i] & ((mag + 0x7F7F7F7Fu) & 0x80808080u));
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t rw = raw[2 * i + (k >> 1)];
+        const float x = (k & 1) ? bf16hi(rw) : bf16lo(rw);
+        const float y = __fmul_rn(fabsf(x), inv);
+        const bool redo = kLegacy ? !(y >= 0.015625f) : (y < 0.015625f);
+        if (redo) o = (o & ~(0xFFu << (8 * k))) | (fp8_encode_exact<kLegacy>(x, inv) << (8 * k));
       }
-    } else {
-#pragma unroll
-      for (int i = 0; i < N / 4; ++i)
-        out[i] = fp8_encode_exact<kLegacy>(bf16lo(raw[2 * i]), inv) | (fp8_encode_exact<kLegacy>(bf16hi(raw[2 * i]), inv) << 8) |
-                 (fp8_encode_exact<kLegacy>(bf16lo(raw[2 * i + 1]), inv) << 16) | (fp8_encode_exact<kLegacy>(bf16hi(raw[2 * i + 1]), inv) << 24);
+      out[i] = o;
     }
   }
 }
@@ -295,25 +348,24 @@ __device__ __forceinline__ uint32_t fp8_encode_ocp_pair(float lo, float hi) {
   return r;
 }
 
-// raw: the N/2 input words (two BF16 each), needed for the sign bits.
-template <int N, bool kOcp>
-__device__ __forceinline__ void encode_fp8(const float (&x)[N], const uint32_t* raw, float amax, float& scale,
-                                           uint32_t (&out)[N / 4]) {
+template <int NW, bool kOcp>
+__device__ __forceinline__ void encode_fp8(const uint32_t* raw, float amax, float& scale, uint32_t* out) {
   scale = div_const<448>(amax);
   if (amax == 0.0f) {  // all-zero block: codes 0, scale 0
 #pragma unroll
-    for (int i = 0; i < N / 4; ++i) out[i] = 0u;
+    for (int i = 0; i < NW / 2; ++i) out[i] = 0u;
     return;
   }
   const float inv = __frcp_rn(scale);  // == RN(1/scale)
   if (!(inv < 3.0e38f)) {  // sub-normal scale: 1/scale overflowed; exact element-wise path
 #pragma unroll
-    for (int i = 0; i < N / 4; ++i) {
+    for (int i = 0; i < NW / 2; ++i) {
       uint32_t w = 0;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const float xv = x[4 * i + k], y = scaled(xv, inv);
-        w |= (kOcp ? (fp8_encode_ocp_pair(y, 0.0f) & 0xFFu) : fp8_encode_ref(y, xv)) << (8 * k);
+        const uint32_t rw = raw[2 * i + (k >> 1)];
+        const float xv = (k & 1) ? bf16hi(rw) : bf16lo(rw);
+        w |= (kOcp ? fp8_encode_ocp_scaled(xv, inv) : fp8_encode_exact<false>(xv, inv)) << (8 * k);
       }
       out[i] = w;
     }
@@ -321,19 +373,21 @@ __device__ __forceinline__ void encode_fp8(const float (&x)[N], const uint32_t* 
   }
   if (kOcp) {
 #pragma unroll
-    for (int i = 0; i < N / 4; ++i)
-      out[i] = fp8_encode_ocp_pair(__fmul_rn(x[4 * i], inv), __fmul_rn(x[4 * i + 1], inv)) |
-               (fp8_encode_ocp_pair(__fmul_rn(x[4 * i + 2], inv), __fmul_rn(x[4 * i + 3], inv)) << 16);
+    for (int i = 0; i < NW / 2; ++i) {
+      const uint32_t w0 = raw[2 * i], w1 = raw[2 * i + 1];
+      out[i] = fp8_encode_ocp_pair(__fmul_rn(bf16lo(w0), inv), __fmul_rn(bf16hi(w0), inv)) |
+               (fp8_encode_ocp_pair(__fmul_rn(bf16lo(w1), inv), __fmul_rn(bf16hi(w1), inv)) << 16);
+    }
     return;
   }
-  fp8_encode_lane_ref<N>(x, raw, inv, out);
+  fp8_encode_words_ref<NW>(raw, inv, out);
 }
 
-template <int kCodec, bool kFlag, int N>
-__device__ __forceinline__ void encode_block_part(const float (&x)[N], const uint32_t* raw, float amax, float& scale,
-                                                  uint32_t (&out)[N / 4]) {
-  if (kCodec == kCodecInt8) encode_int8<N, kFlag>(x, amax, scale, out);
-  else encode_fp8<N, kFlag>(x, raw, amax, scale, out);
+// NW words of one lane, whose block has absolute maximum `amax`: the block's scale and the lane's codes.
+template <int kCodec, bool kFlag, int NW>
+__device__ __forceinline__ void encode_block_part(const uint32_t* raw, float amax, float& scale, uint32_t* out) {
+  if (kCodec == kCodecInt8) encode_int8<NW, kFlag>(raw, amax, scale, out);
+  else encode_fp8<NW, kFlag>(raw, amax, scale, out);
 }
 
 // Where a block's output goes (see the header comment on packed chunks).
@@ -377,141 +431,126 @@ static_assert(sizeof(JobTable) <= 4000, "kernel parameters must stay under 4 KB"
 // aligned; chunk_elems a multiple of 16384 (or >= n).  A job's last tile may be
 // ragged: it uses predicated loads and direct stores.
 
-// One tile's worth of work for one lane-vector: 16 elements in, 16 codes out.
+// 16 elements of a lane where eight lanes hold a block (the producers below): 16 codes out.
 template <int kCodec, bool kFlag>
 __device__ __forceinline__ uint4 compress_lane(const U32x8& raw, float& scale) {
-  float x[kLaneElems];
-  unpack16(raw, x);
-  const float amax = absmax_8lanes(absmax_n<kLaneElems>(x));
+  const float amax = absmax_8lanes(absmax_words<8>(raw.v));
   uint32_t c[kLaneElems / 4];
-  encode_block_part<kCodec, kFlag, kLaneElems>(x, raw.v, amax, scale, c);
+  encode_block_part<kCodec, kFlag, 8>(raw.v, amax, scale, c);
   return make_uint4(c[0], c[1], c[2], c[3]);
+}
+
+// 32 consecutive elements of a lane where four lanes hold a block: 32 codes out.
+struct Lane32 { uint32_t w[16]; };
+template <int kCodec, bool kFlag>
+__device__ __forceinline__ void compress_lane32(const Lane32& raw, float& scale, uint4& c_lo, uint4& c_hi) {
+  const float amax = absmax_4lanes(absmax_words<16>(raw.w));
+  uint32_t c[kCompLaneElems / 4];
+  encode_block_part<kCodec, kFlag, 16>(raw.w, amax, scale, c);
+  c_lo = make_uint4(c[0], c[1], c[2], c[3]);
+  c_hi = make_uint4(c[4], c[5], c[6], c[7]);
+}
+
+__device__ __forceinline__ Lane32 load_lane32(const uint16_t* p) {
+  const U32x8 a = ld_stream32(p), b = ld_stream32(p + kLaneElems);
+  Lane32 r;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { r.w[i] = a.v[i]; r.w[8 + i] = b.v[i]; }
+  return r;
 }
 
 // Ragged last tile of a job: `rem` (< 8192) elements starting at tin / o.
 template <int kCodec, bool kFlag>
 __device__ __forceinline__ void compress_ragged_tile(const uint16_t* __restrict__ tin, const OutAddr o, size_t rem, int tid) {
-#pragma unroll 1
-  for (int u = 0; u < kUnroll; ++u) {
-    const size_t e0 = (size_t)(u * kThreads + tid) * kLaneElems;
-    // whole warps enter together so the shuffles stay converged
-    if (((size_t)(u * kThreads + (tid & ~31)) * kLaneElems) >= rem) break;
-    U32x8 r;
+  const size_t e0 = (size_t)tid * kCompLaneElems;
+  // whole warps enter together so the shuffles stay converged
+  if ((size_t)(tid & ~31) * kCompLaneElems >= rem) return;
+  Lane32 r;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) r.v[i] = 0u;
-    if (e0 + kLaneElems <= rem) {
-      r = ld_stream32(tin + e0);
-    } else if (e0 < rem) {
-      for (size_t i = 0; e0 + i < rem; ++i) {
-        const uint32_t h = tin[e0 + i];
-        r.v[i >> 1] |= (i & 1) ? (h << 16) : h;
-      }
+  for (int i = 0; i < 16; ++i) r.w[i] = 0u;
+  if (e0 + kCompLaneElems <= rem) {
+    r = load_lane32(tin + e0);
+  } else if (e0 < rem) {
+    for (size_t i = 0; e0 + i < rem; ++i) {
+      const uint32_t h = tin[e0 + i];
+      r.w[i >> 1] |= (i & 1) ? (h << 16) : h;
     }
-    float scale;
-    const uint4 c4 = compress_lane<kCodec, kFlag>(r, scale);
-    if (e0 + kLaneElems <= rem) {
-      *reinterpret_cast<uint4*>(o.codes + e0) = c4;
-    } else if (e0 < rem) {
-      const uint32_t c[4] = {c4.x, c4.y, c4.z, c4.w};
-      for (size_t i = 0; e0 + i < rem; ++i) o.codes[e0 + i] = (uint8_t)(c[i >> 2] >> (8 * (i & 3)));
+  }
+  float scale;
+  uint4 c_lo, c_hi;
+  compress_lane32<kCodec, kFlag>(r, scale, c_lo, c_hi);
+  if (e0 + kCompLaneElems <= rem) {
+    *reinterpret_cast<uint4*>(o.codes + e0) = c_lo;
+    *reinterpret_cast<uint4*>(o.codes + e0 + 16) = c_hi;
+  } else if (e0 < rem) {
+    const uint32_t c[8] = {c_lo.x, c_lo.y, c_lo.z, c_lo.w, c_hi.x, c_hi.y, c_hi.z, c_hi.w};
+    for (size_t i = 0; e0 + i < rem; ++i) o.codes[e0 + i] = (uint8_t)(c[i >> 2] >> (8 * (i & 3)));
+  }
+  if ((tid & (kCompLanesPerBlock - 1)) == 0 && e0 < rem) o.scales[e0 / 128] = scale;
+}
+
+// One full tile: encode the lane's 32 elements and write codes and scale.
+// kStaged = false: two 16-byte stores per lane, one lane in four stores the scale.
+// kStaged = true : the warp's 1024 codes and 8 scales go to the warp's own shared-memory slice (two slices, taking
+//                  turns) and lane 0 sends them out as two bulk asynchronous copies.  Only the warp synchronises:
+//                  before a slice is written again, lane 0 waits until the bulk group issued from it two tiles ago
+//                  has been read.
+template <int kCodec, bool kFlag, bool kStaged>
+__device__ __forceinline__ void compress_full_tile(const Lane32& raw, const OutAddr o, int tid, uint8_t* smem, int& buf) {
+  float scale;
+  uint4 c_lo, c_hi;
+  compress_lane32<kCodec, kFlag>(raw, scale, c_lo, c_hi);
+  if (!kStaged) {
+    uint8_t* dst = o.codes + tid * kCompLaneElems;
+    __stcs(reinterpret_cast<uint4*>(dst), c_lo);
+    __stcs(reinterpret_cast<uint4*>(dst + 16), c_hi);
+    if ((tid & (kCompLanesPerBlock - 1)) == 0) o.scales[tid / kCompLanesPerBlock] = scale;
+  } else {
+    const int lane = tid & 31, warp = tid >> 5;
+    uint8_t* slice = smem + (warp * 2 + buf) * kWarpSliceBytes;
+    if (lane == 0) bulk_wait_read<1>();
+    __syncwarp();
+    *reinterpret_cast<uint4*>(slice + lane * kCompLaneElems) = c_lo;
+    *reinterpret_cast<uint4*>(slice + lane * kCompLaneElems + 16) = c_hi;
+    if ((lane & (kCompLanesPerBlock - 1)) == 0) reinterpret_cast<float*>(slice + kWarpCodes)[lane / kCompLanesPerBlock] = scale;
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      bulk_store(o.codes + warp * kWarpCodes, slice, kWarpCodes);
+      bulk_store(o.scales + warp * kWarpScales, slice + kWarpCodes, kWarpScales * sizeof(float));
+      bulk_commit();
     }
-    if ((tid & (kLanesPerBlock - 1)) == 0 && e0 < rem) o.scales[e0 / 128] = scale;
+    buf ^= 1;
   }
 }
 
-// kStaged = true : codes and scales of a tile are collected in shared memory and
-//                  leave as two bulk asynchronous copies issued by one thread.
-// kStaged = false: every lane stores its 16 codes with one 16-byte store and one
-//                  lane in eight stores the scale; no shared memory, no barrier.
 // Round k of every thread block works on tile k*grid + block of the launch's
 // tile space; the host sizes the grid so that all blocks run the same number of
 // rounds (see grid_balanced).
-// Five resident blocks per SM (48 registers).  The FP8 body would like 64 registers; measured, five
-// blocks with a few spilled words (off the hot loop) beat four blocks without (5.5 vs 5.3 TB/s).
-template <int kCodec>
-struct CompressOccupancy { static constexpr int kMinBlocks = 5; };
+// kForm 0: load a tile, encode it, store it; five resident blocks per SM (48 registers).
+// kForm 1: software-pipelined: the loads of a block's next tile are issued before the current tile is encoded, so
+//          a thread always has a tile's worth of loads in flight.  Twice the input registers: four resident blocks.
+// kForm 2: as form 0 with four resident blocks (64 registers).
+// Same tile order, same results.
+constexpr int kCompressForms = 3;
+template <int kForm>
+struct CompressForm {
+  static constexpr bool kPipelined = kForm == 1;
+  static constexpr int kMinBlocks = kForm == 0 ? 5 : 4;
+};
 
-template <int kCodec, bool kFlag, bool kStaged>
-__global__ void __launch_bounds__(kThreads, CompressOccupancy<kCodec>::kMinBlocks)
+template <int kCodec, bool kFlag, bool kStaged, int kForm>
+__global__ void __launch_bounds__(kThreads, CompressForm<kForm>::kMinBlocks)
 compress_b128_kernel(const __grid_constant__ JobTable T, unsigned rounds, unsigned multi_ctas, unsigned multi_tiles) {
-  // staged variant only: two buffers of (codes tile | scales tile) in dynamic shared memory
+  // staged variant only: two slices of (codes | scales) per warp in dynamic shared memory
   extern __shared__ __align__(128) uint8_t smem_tiles[];
+  constexpr bool kPipelined = CompressForm<kForm>::kPipelined;
   const int tid = threadIdx.x;
   int buf = 0;
-  uint32_t j = 0;
-
   // Blocks below multi_ctas take `rounds` tiles each out of the first multi_tiles (tile k*multi_ctas + b in
   // round k, so blocks that run side by side read neighbouring tiles); the blocks after them take one tile
   // each of the rest.  Blocks start in index order, so the launch ends on short blocks and the SMs run dry
   // within one tile's time of each other instead of one long block's.
-  const bool multi = blockIdx.x < multi_ctas;
-  for (unsigned k = 0; k < rounds; ++k) {
-    uint32_t g;
-    if (multi) {
-      g = k * multi_ctas + blockIdx.x;
-      if (g >= multi_tiles) break;
-    } else {
-      if (k) break;
-      g = multi_tiles + (blockIdx.x - multi_ctas);
-    }
-    if (g >= T.total_tiles) break;
-    while (j + 1 < T.count && g >= T.jobs[j + 1].tile0) ++j;
-    const CodecJob& J = T.jobs[j];
-    const size_t e_tile = (size_t)(g - J.tile0) * kTileElems;
-    const uint16_t* tin = static_cast<const uint16_t*>(J.in) + e_tile;
-    if (e_tile + kTileElems > J.n) {  // the job's ragged last tile
-      compress_ragged_tile<kCodec, kFlag>(tin, locate(static_cast<uint8_t*>(J.out), J.L, e_tile), J.n - e_tile, tid);
-      continue;
-    }
-    U32x8 raw[kUnroll];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) raw[u] = ld_stream32(tin + (size_t)(u * kThreads + tid) * kLaneElems);
-
-    if (!kStaged) {
-      const OutAddr o = locate(static_cast<uint8_t*>(J.out), J.L, e_tile);
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        float scale;
-        const uint4 c = compress_lane<kCodec, kFlag>(raw[u], scale);
-        const int v = u * kThreads + tid;
-        __stcs(reinterpret_cast<uint4*>(o.codes + v * kLaneElems), c);
-        if ((tid & (kLanesPerBlock - 1)) == 0) o.scales[v / kLanesPerBlock] = scale;
-      }
-    } else {
-      // The bulk store issued two tiles ago read this buffer; it must be done.
-      if (tid == 0) bulk_wait_read<1>();
-      __syncthreads();
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        float scale;
-        const uint4 c = compress_lane<kCodec, kFlag>(raw[u], scale);
-        const int v = u * kThreads + tid;
-        uint8_t* s_codes = smem_tiles + buf * kStagedBufBytes;
-        *reinterpret_cast<uint4*>(s_codes + v * kLaneElems) = c;
-        if ((tid & (kLanesPerBlock - 1)) == 0) reinterpret_cast<float*>(s_codes + kTileElems)[v / kLanesPerBlock] = scale;
-      }
-      fence_async_smem();
-      __syncthreads();
-      if (tid == 0) {
-        const OutAddr o = locate(static_cast<uint8_t*>(J.out), J.L, e_tile);
-        const uint8_t* s_codes = smem_tiles + buf * kStagedBufBytes;
-        bulk_store(o.codes, s_codes, kTileElems);
-        bulk_store(o.scales, s_codes + kTileElems, kTileBlocks * sizeof(float));
-        bulk_commit();
-      }
-      buf ^= 1;
-    }
-  }
-  if (kStaged && tid == 0) bulk_wait_all<0>();
-}
-
-// Software-pipelined form of the direct-store kernel: the loads of a block's next tile are issued before the
-// current tile is encoded, so a thread always has a tile's worth of loads in flight.  Twice the input registers
-// (four resident blocks per SM instead of five).  Same tile order, same results.
-template <int kCodec, bool kFlag>
-__global__ void __launch_bounds__(kThreads, 4)
-compress_b128_pipelined_kernel(const __grid_constant__ JobTable T, unsigned rounds, unsigned multi_ctas, unsigned multi_tiles) {
-  const int tid = threadIdx.x;
   const bool multi = blockIdx.x < multi_ctas;
   uint32_t j = 0;
   // tile of round k for this block, or false
@@ -541,39 +580,26 @@ compress_b128_pipelined_kernel(const __grid_constant__ JobTable T, unsigned roun
   };
   auto in_of = [&](const Where& w) { return static_cast<const uint16_t*>(T.jobs[w.job].in) + (size_t)w.tile * kTileElems; };
   Where cur = resolve(0);
-  U32x8 nxt[kUnroll];
-  if (cur.ok && cur.full) {
-    const uint16_t* tin = in_of(cur);
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) nxt[u] = ld_stream32(tin + (size_t)(u * kThreads + tid) * kLaneElems);
-  }
+  Lane32 nxt;
+  if (kPipelined && cur.ok && cur.full) nxt = load_lane32(in_of(cur) + (size_t)tid * kCompLaneElems);
   for (unsigned k = 0; cur.ok; ++k) {
-    U32x8 raw[kUnroll];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) raw[u] = nxt[u];
-    const Where next = resolve(k + 1);
-    if (next.ok && next.full) {
-      const uint16_t* tin = in_of(next);
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) nxt[u] = ld_stream32(tin + (size_t)(u * kThreads + tid) * kLaneElems);
+    Lane32 raw;
+    Where next{0u, 0u, false, false};
+    if (kPipelined) {
+      raw = nxt;
+      next = resolve(k + 1);
+      if (next.ok && next.full) nxt = load_lane32(in_of(next) + (size_t)tid * kCompLaneElems);
+    } else if (cur.full) {
+      raw = load_lane32(in_of(cur) + (size_t)tid * kCompLaneElems);
     }
     const CodecJob& J = T.jobs[cur.job];
     const size_t e_tile = (size_t)cur.tile * kTileElems;
     const OutAddr o = locate(static_cast<uint8_t*>(J.out), J.L, e_tile);
-    if (cur.full) {
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        float scale;
-        const uint4 c = compress_lane<kCodec, kFlag>(raw[u], scale);
-        const int v = u * kThreads + tid;
-        __stcs(reinterpret_cast<uint4*>(o.codes + v * kLaneElems), c);
-        if ((tid & (kLanesPerBlock - 1)) == 0) o.scales[v / kLanesPerBlock] = scale;
-      }
-    } else {
-      compress_ragged_tile<kCodec, kFlag>(in_of(cur), o, J.n - e_tile, tid);
-    }
-    cur = next;
+    if (cur.full) compress_full_tile<kCodec, kFlag, kStaged>(raw, o, tid, smem_tiles, buf);
+    else compress_ragged_tile<kCodec, kFlag>(in_of(cur), o, J.n - e_tile, tid);
+    cur = kPipelined ? next : resolve(k + 1);
   }
+  if (kStaged && (tid & 31) == 0) bulk_wait_all<0>();
 }
 
 // Any alignment, any n: one warp per 128-element block, scalar accesses.
@@ -589,14 +615,13 @@ compress_b128_generic_kernel(const uint16_t* __restrict__ in, uint8_t* __restric
     uint32_t raw[2] = {0u, 0u};
     for (int i = 0; i < 4; ++i)
       if (e0 + i < n) raw[i >> 1] |= (uint32_t)in[e0 + i] << (16 * (i & 1));
-    float x[4] = {bf16lo(raw[0]), bf16hi(raw[0]), bf16lo(raw[1]), bf16hi(raw[1])};
-    float m = absmax_n<4>(x);
+    float m = absmax_words<2>(raw);
     m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 16));
     m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 8));
     const float amax = absmax_8lanes(m);
     float scale;
     uint32_t c[1];
-    encode_block_part<kCodec, kFlag, 4>(x, raw, amax, scale, c);
+    encode_block_part<kCodec, kFlag, 2>(raw, amax, scale, c);
     const OutAddr o = locate(out, L, blk * 128);
     for (int i = 0; i < 4; ++i)
       if (e0 + i < n) o.codes[(size_t)lane * 4 + i] = (uint8_t)(c[0] >> (8 * i));
@@ -723,16 +748,14 @@ bf16_to_fp8_vec_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ ou
   const size_t stride = (size_t)gridDim.x * kThreads;
   for (size_t v = (size_t)blockIdx.x * kThreads + threadIdx.x; v < nvec; v += stride) {
     const U32x8 r = ld_stream32(in + v * kLaneElems);
-    float x[kLaneElems];
-    unpack16(r, x);
     uint32_t c[4];
     if ((inv_scale > 0.0f) && (inv_scale < 3.0e38f)) {  // the sign of x*inv_scale is the sign of x
-      fp8_encode_lane_ref<kLaneElems, true>(x, r.v, inv_scale, c);
+      fp8_encode_words_ref<8, true>(r.v, inv_scale, c);
     } else {
 #pragma unroll
       for (int i = 0; i < 4; ++i)
-        c[i] = fp8_encode_legacy(x[4 * i], inv_scale) | (fp8_encode_legacy(x[4 * i + 1], inv_scale) << 8) |
-               (fp8_encode_legacy(x[4 * i + 2], inv_scale) << 16) | (fp8_encode_legacy(x[4 * i + 3], inv_scale) << 24);
+        c[i] = fp8_encode_legacy(bf16lo(r.v[2 * i]), inv_scale) | (fp8_encode_legacy(bf16hi(r.v[2 * i]), inv_scale) << 8) |
+               (fp8_encode_legacy(bf16lo(r.v[2 * i + 1]), inv_scale) << 16) | (fp8_encode_legacy(bf16hi(r.v[2 * i + 1]), inv_scale) << 24);
     }
     __stcs(reinterpret_cast<uint4*>(out + v * kLaneElems), make_uint4(c[0], c[1], c[2], c[3]));
   }
@@ -802,23 +825,35 @@ int grid_for(size_t work_items, int ctas_per_sm, int max_ctas) {
   return (int)g;
 }
 
-// Resident thread blocks per SM of a kernel (queried once per kernel).
-template <typename K>
-int resident_ctas_per_sm(K kernel, size_t dyn_smem = 0) {
-  static int cached = 0;
-  if (cached == 0) {
-    int v = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, kernel, kThreads, dyn_smem) != cudaSuccess || v <= 0) v = 4;
-    cached = v;
-  }
-  return cached;
+// Resident thread blocks per SM of a kernel, from the occupancy query; remembered per (kernel, dynamic shared
+// memory, device).  The key is the kernel's address: different instantiations of one template have the same
+// function type, so a cache keyed by type would hand one kernel's answer to another.
+int resident_ctas_per_sm(const void* kernel, size_t dyn_smem = 0) {
+  struct Entry { const void* k; size_t smem; int dev; int v; };
+  static std::mutex mu;
+  static std::vector<Entry> cache;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+  std::lock_guard<std::mutex> lk(mu);
+  for (const Entry& e : cache)
+    if (e.k == kernel && e.smem == dyn_smem && e.dev == dev) return e.v;
+  int v = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, kernel, kThreads, dyn_smem) != cudaSuccess || v <= 0) v = 4;
+  cache.push_back({kernel, dyn_smem, dev, v});
+  return v;
 }
+
+// What the last compress / dequantise launch of this thread chose (inspection hook for the tests).
+thread_local LaunchRecord g_last_launch = {0, 0, 0, 0};
 
 // A grid in which every thread block takes the same number of consecutive tiles
 // and all blocks are resident at once: no second wave, no ragged last round.
 struct Grid { int ctas; unsigned tiles_per_cta; };
 constexpr int kTaperWaves = 2;
-constexpr int kPipelinedBalanceLimit = 8, kPipelinedRounds = 6;  // grid policy of the software-pipelined compress kernel  // waves of single-tile blocks at the end of an oversubscribed compress launch
+// waves of single-tile blocks at the end of an oversubscribed compress launch
+// Measured on a B200, one DiT block per launch, 20 launches back to back (fraction of the 6552 GB/s copy rate):
+// int8 form 0 / 1 / 2 = 0.95 / 0.91 / 0.98, FP8 = 0.86 / 0.71 / 0.85; with staged stores 0.91 / 0.95 / 0.89 and 0.78 / 0.66 / 0.78.
+constexpr int kDefaultFormInt8 = 2, kDefaultFormFp8 = 0;  // see CompressForm
 int env_int(const char* name) {
   const char* e = getenv(name);
   return e ? (atoi(e) < 1 ? 1 : atoi(e)) : 0;
@@ -858,6 +893,8 @@ bool layout_fast(const void* base, const PackedLayout& L, size_t n) {
 
 int set_max_ctas(int v) { const int old = g_max_ctas; g_max_ctas = v < 0 ? 0 : v; return old; }
 
+LaunchRecord last_launch() { return g_last_launch; }
+
 PackedLayout single_chunk_layout(const void* codes, const void* scales, size_t n) {
   PackedLayout L;
   L.chunk_elems = n ? n : 1;
@@ -889,20 +926,12 @@ void add_job(JobTable& T, const void* in, void* out, const TensorJob& j) {
   T.total_tiles += (uint32_t)((j.n + kTile - 1) / kTile);
 }
 
-template <int kCodec, bool kFlag, bool kStaged>
-cudaError_t launch_compress_table(const JobTable& T, cudaStream_t stream, int max_ctas) {
-  // int8: the software-pipelined kernel (0.91 -> 0.93-0.95 of the HBM rate on a DiT block, 0.96 -> 1.0 at 1 Gi
-  // elements); FP8 is bound by its encoder's ALU work and loses more to four resident blocks than it gains
-  // (0.75 -> 0.68).  FLAME_ACT_PIPELINED=0/1 overrides.
-  static int pipelined = -1;
-  if (pipelined < 0) { const char* e = getenv("FLAME_ACT_PIPELINED"); pipelined = e ? (atoi(e) != 0) : 2; }
-  const bool use_pipelined = !kStaged && (pipelined == 2 ? (kCodec == kCodecInt8) : pipelined != 0);
-  auto kern = compress_b128_kernel<kCodec, kFlag, kStaged>;
-  auto kern_p = compress_b128_pipelined_kernel<kCodec, kFlag>;
-  const size_t smem = kStaged ? 2 * kStagedBufBytes : 0;
-  const int per_sm = use_pipelined ? resident_ctas_per_sm(kern_p, 0) : resident_ctas_per_sm(kern, smem);
-  const Grid g = use_pipelined ? grid_balanced(T.total_tiles, per_sm, max_ctas, kPipelinedBalanceLimit, kPipelinedRounds)
-                               : grid_balanced(T.total_tiles, per_sm, max_ctas, 8, 6);
+template <int kCodec, bool kFlag, bool kStaged, int kForm>
+cudaError_t launch_compress_kernel(const JobTable& T, cudaStream_t stream, int max_ctas) {
+  auto kern = compress_b128_kernel<kCodec, kFlag, kStaged, kForm>;
+  const size_t smem = kStaged ? kStagedSmemBytes : 0;
+  const int per_sm = resident_ctas_per_sm(reinterpret_cast<const void*>(kern), smem);
+  const Grid g = grid_balanced(T.total_tiles, per_sm, max_ctas, 8, 6);
   // Oversubscribed launches (several waves of blocks) end on single-tile blocks: `taper` waves of them.
   static int taper = -1;
   if (taper < 0) { const char* e = getenv("FLAME_ACT_TAPER_WAVES"); taper = e ? atoi(e) : kTaperWaves; if (taper < 0) taper = 0; }
@@ -914,9 +943,32 @@ cudaError_t launch_compress_table(const JobTable& T, cudaStream_t stream, int ma
     multi_ctas = (multi_tiles + g.tiles_per_cta - 1) / g.tiles_per_cta;
     ctas = multi_ctas + (unsigned)singles;
   }
-  if (use_pipelined) kern_p<<<ctas, kThreads, 0, stream>>>(T, g.tiles_per_cta, multi_ctas, multi_tiles);
-  else kern<<<ctas, kThreads, smem, stream>>>(T, g.tiles_per_cta, multi_ctas, multi_tiles);
+  g_last_launch = {(int)ctas, per_sm, (int)g.tiles_per_cta, kForm | (kStaged ? 4 : 0)};
+  kern<<<ctas, kThreads, smem, stream>>>(T, g.tiles_per_cta, multi_ctas, multi_tiles);
   return cudaGetLastError();
+}
+
+// Which form of the kernel a codec takes (defaults measured on a B200; FLAME_ACT_COMPRESS_FORM=0/1/2 or
+// set_compress_form() override both codecs, for tuning and tests).
+std::atomic<int> g_form_override{-2};  // -2: not read from the environment yet; -1: defaults
+int compress_form(int codec) {
+  int f = g_form_override.load(std::memory_order_relaxed);
+  if (f == -2) {
+    const char* e = getenv("FLAME_ACT_COMPRESS_FORM");
+    f = (e && *e >= '0' && *e < '0' + kCompressForms && e[1] == 0) ? *e - '0' : -1;
+    g_form_override.store(f, std::memory_order_relaxed);
+  }
+  if (f >= 0) return f;
+  return codec == kCodecInt8 ? kDefaultFormInt8 : kDefaultFormFp8;
+}
+
+template <int kCodec, bool kFlag, bool kStaged>
+cudaError_t launch_compress_table(const JobTable& T, cudaStream_t stream, int max_ctas) {
+  switch (compress_form(kCodec)) {
+    case 1: return launch_compress_kernel<kCodec, kFlag, kStaged, 1>(T, stream, max_ctas);
+    case 2: return launch_compress_kernel<kCodec, kFlag, kStaged, 2>(T, stream, max_ctas);
+    default: return launch_compress_kernel<kCodec, kFlag, kStaged, 0>(T, stream, max_ctas);
+  }
 }
 
 cudaError_t launch_compress_table(int codec, unsigned flags, const JobTable& T, cudaStream_t stream, int max_ctas) {
@@ -976,11 +1028,15 @@ cudaError_t launch_dequant_multi(int codec, const TensorJob* jobs, size_t count,
     if (T.count == 0) return cudaSuccess;
     if (codec == kCodecInt8) {
       auto kern = dequant_b128_kernel<kCodecInt8>;
-      const Grid g = grid_balanced(T.total_tiles, resident_ctas_per_sm(kern), max_ctas, 2, 2);
+      const int per_sm = resident_ctas_per_sm(reinterpret_cast<const void*>(kern));
+      const Grid g = grid_balanced(T.total_tiles, per_sm, max_ctas, 2, 2);
+      g_last_launch = {g.ctas, per_sm, (int)g.tiles_per_cta, 0};
       kern<<<g.ctas, kThreads, 0, stream>>>(T, g.tiles_per_cta);
     } else {
       auto kern = dequant_b128_kernel<kCodecFp8>;
-      const Grid g = grid_balanced(T.total_tiles, resident_ctas_per_sm(kern), max_ctas, 2, 2);
+      const int per_sm = resident_ctas_per_sm(reinterpret_cast<const void*>(kern));
+      const Grid g = grid_balanced(T.total_tiles, per_sm, max_ctas, 2, 2);
+      g_last_launch = {g.ctas, per_sm, (int)g.tiles_per_cta, 0};
       kern<<<g.ctas, kThreads, 0, stream>>>(T, g.tiles_per_cta);
     }
     T.count = 0; T.total_tiles = 0;
@@ -1207,6 +1263,44 @@ cudaError_t launch_fp8_to_bf16(const void* in, void* out, float scale, size_t n,
     fp8_to_bf16_scalar_kernel<<<grid, kThreads, 0, stream>>>(i, o, scale, n);
   }
   return cudaGetLastError();
+}
+
+int default_compress_form(int codec) { return compress_form(codec); }
+int set_compress_form(int form) {
+  const int old = g_form_override.load(std::memory_order_relaxed);
+  g_form_override.store((form >= 0 && form < kCompressForms) ? form : -1, std::memory_order_relaxed);
+  return old < 0 ? -1 : old;
+}
+
+namespace {
+template <int kCodec, bool kFlag, bool kStaged>
+const void* compress_kernel_address(int form) {
+  switch (form) {
+    case 1: return reinterpret_cast<const void*>(compress_b128_kernel<kCodec, kFlag, kStaged, 1>);
+    case 2: return reinterpret_cast<const void*>(compress_b128_kernel<kCodec, kFlag, kStaged, 2>);
+    default: return reinterpret_cast<const void*>(compress_b128_kernel<kCodec, kFlag, kStaged, 0>);
+  }
+}
+template <int kCodec>
+const void* compress_kernel_address(bool f, bool st, int form) {
+  if (f) return st ? compress_kernel_address<kCodec, true, true>(form) : compress_kernel_address<kCodec, true, false>(form);
+  return st ? compress_kernel_address<kCodec, false, true>(form) : compress_kernel_address<kCodec, false, false>(form);
+}
+}  // namespace
+
+int query_resident_ctas(int codec, unsigned flags, int form, bool compress) {
+  const bool f = (flags & 1u) != 0, st = (flags & kFlagStagedStores) != 0;
+  const void* k = nullptr;
+  if (!compress) {
+    k = codec == kCodecInt8 ? reinterpret_cast<const void*>(dequant_b128_kernel<kCodecInt8>) : reinterpret_cast<const void*>(dequant_b128_kernel<kCodecFp8>);
+  } else {
+    if (form < 0) form = compress_form(codec);
+    k = codec == kCodecInt8 ? compress_kernel_address<kCodecInt8>(f, st, form) : compress_kernel_address<kCodecFp8>(f, st, form);
+  }
+  int v = 0;
+  const size_t smem = (compress && st) ? kStagedSmemBytes : 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, k, kThreads, smem) != cudaSuccess) return -1;
+  return v;
 }
 
 }  // namespace flame_b200

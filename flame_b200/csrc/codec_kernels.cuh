@@ -60,4 +60,13 @@ cudaError_t launch_swiglu_quant(int codec, unsigned flags, const void* gate_up, 
                                 size_t rows, size_t hidden, cudaStream_t stream, int max_ctas);
 int set_max_ctas(int v);
 
+// Inspection hooks (tests): what the calling thread's last compress / dequantise launch chose, and a fresh
+// occupancy query for the kernel a (codec, flags, form) combination selects.
+struct LaunchRecord { int ctas, resident_per_sm, tiles_per_cta, form; };  // form: kernel form 0..2, +4 with staged stores
+LaunchRecord last_launch();
+int default_compress_form(int codec);
+int set_compress_form(int form);  // 0..2, anything else = per-codec default; returns the old override (-1 = none)
+// form < 0: the form the codec takes by default
+int query_resident_ctas(int codec, unsigned flags, int form, bool compress);
+
 }  // namespace flame_b200

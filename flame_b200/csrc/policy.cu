@@ -210,18 +210,28 @@ FlameOffloadStatus flame_offload_policy_plan_blocks(const FlamePolicyInput* in, 
   SimResult best_r{};
   double best_cost = 0.0;
   std::vector<int32_t> dec(n);
+  const bool capped = in->overhead_cap_ms > 0.0;
   for (size_t resident = 0; resident <= n; ++resident) {
     uint64_t res_bytes = 0;
     for (size_t g = n - resident; g < n; ++g) res_bytes += blocks[g].saved_bytes;
-    if (res_bytes > in->device_budget_bytes) break;  // more trailing blocks only cost more memory
+    if (!capped && res_bytes > in->device_budget_bytes) break;  // more trailing blocks only cost more memory
+    bool feasible = false;
     for (size_t recompute = 0; recompute + resident <= n; ++recompute) {
       for (size_t g = 0; g < n; ++g)
         dec[g] = g >= n - resident ? FLAME_POLICY_RESIDENT : (g < recompute ? FLAME_POLICY_RECOMPUTE : offload_decision);
       const SimResult r = simulate(*in, blocks, n, dec, ratio);
       const double cost = r.stall_ms + r.recompute_ms + std::max(0.0, in->interference) * r.busy_ms;
+      if (capped) {
+        // the first resident count (fewest resident bytes) with a plan under the cap wins; among its plans, the cheapest
+        if (cost > in->overhead_cap_ms) continue;
+        if (!feasible || cost < best_cost - 0.01) { best = dec; best_r = r; best_cost = cost; }
+        feasible = true;
+        continue;
+      }
       // strictly better time wins; within 0.01 ms prefer fewer resident bytes (earlier in the search)
       if (best.empty() || cost < best_cost - 0.01) { best = dec; best_r = r; best_cost = cost; }
     }
+    if (capped && feasible) break;
   }
   for (size_t g = 0; g < n; ++g) decisions[g] = best.empty() ? offload_decision : best[g];
   if (out) { out->est_stall_ms = best_r.stall_ms; out->est_recompute_ms = best_r.recompute_ms; out->resident_bytes = best_r.resident; out->link_bytes = best_r.link;

@@ -54,7 +54,7 @@ def plan(tensors: list[SavedTensor], *, d2h_gbs: float, h2d_gbs: float, fwd_ms: 
     arr = (_lib.PolicyTensor * max(n, 1))()
     for i, t in enumerate(tensors):
         arr[i] = _lib.PolicyTensor(t.nbytes, t.recompute_ms, t.group, int(t.allow_lossy))
-    inp = _lib.PolicyInput(d2h_gbs, h2d_gbs, fwd_ms, bwd_ms, device_budget_bytes, int(lossy_codec), link_utilisation, 0.0)
+    inp = _lib.PolicyInput(d2h_gbs, h2d_gbs, fwd_ms, bwd_ms, device_budget_bytes, int(lossy_codec), link_utilisation, 0.0, 0.0)
     dec = (C.c_int32 * max(n, 1))()
     est = C.c_double()
     st = _lib.lib().flame_offload_policy_plan(C.byref(inp), arr, n, dec, C.byref(est))
@@ -83,14 +83,18 @@ class BlockPlan:
 DEFAULT_INTERFERENCE = 0.1
 
 
-def plan_blocks(blocks: list[Block], *, d2h_gbs: float, h2d_gbs: float, device_budget_bytes: int,
-                offload: Decision = Decision.OFFLOAD_INT8, interference: float = DEFAULT_INTERFERENCE) -> BlockPlan:
-    """Per-block decision for a stack of checkpointed blocks (flame_offload_policy_plan_blocks)."""
+def plan_blocks(blocks: list[Block], *, d2h_gbs: float, h2d_gbs: float, device_budget_bytes: int = 0,
+                offload: Decision = Decision.OFFLOAD_INT8, interference: float = DEFAULT_INTERFERENCE,
+                overhead_cap_ms: float = 0.0) -> BlockPlan:
+    """Per-block decision for a stack of checkpointed blocks (flame_offload_policy_plan_blocks).
+
+    ``overhead_cap_ms`` = 0: the least estimated step time with at most ``device_budget_bytes`` resident.
+    ``overhead_cap_ms`` > 0: the fewest resident bytes whose estimated extra step time stays under the cap."""
     n = len(blocks)
     arr = (_lib.PolicyBlock * max(n, 1))()
     for i, b in enumerate(blocks):
         arr[i] = _lib.PolicyBlock(b.saved_bytes, b.fwd_ms, b.bwd_ms)
-    inp = _lib.PolicyInput(d2h_gbs, h2d_gbs, 0.0, 0.0, device_budget_bytes, int(offload), 0.0, interference)
+    inp = _lib.PolicyInput(d2h_gbs, h2d_gbs, 0.0, 0.0, device_budget_bytes, int(offload), 0.0, interference, overhead_cap_ms)
     dec = (C.c_int32 * max(n, 1))()
     out = _lib.PolicyBlockPlan()
     st = _lib.lib().flame_offload_policy_plan_blocks(C.byref(inp), arr, n, int(offload), dec, C.byref(out))

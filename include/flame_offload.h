@@ -89,8 +89,9 @@ int flame_fp8_to_bf16(const void* input_u8, void* output_bf16, float scale, size
 #define FLAME_ACT_BLOCK 128
 #define FLAME_ACT_INT8_MUL_INV 1u /* int8: code = rne(x * (1/scale)) instead of the division */
 #define FLAME_ACT_FP8_OCP 1u      /* fp8: OCP round-to-nearest-even, saturating encoder (not the reference's) */
-#define FLAME_ACT_STAGED_STORES 2u /* compress: collect each tile's codes and scales in shared memory and write them
-                                      with bulk asynchronous copies instead of per-lane stores; same results */
+#define FLAME_ACT_STAGED_STORES 2u /* compress: each warp collects its 1024 codes and 8 scales of a tile in shared memory and
+                                      one lane writes them with two bulk asynchronous copies instead of per-lane stores
+                                      (warp-level synchronisation only); same results */
 
 int flame_act_quant_int8_b128(const void* in_bf16, void* codes_i8, void* scales_f32, size_t n, unsigned int flags, void* stream);
 int flame_act_dequant_int8_b128(const void* codes_i8, const void* scales_f32, void* out_bf16, size_t n, void* stream);
@@ -163,6 +164,26 @@ int flame_act_offload_packed_noalloc(const void* in_bf16, void* packed_out, size
 /* Limits the number of thread blocks the codec kernels launch on the current
  * device (0 = default: a multiple of the SM count).  Returns the old value. */
 int flame_act_set_max_ctas(int max_ctas);
+
+/* Tuning hook: the compress kernel exists in three forms that write the same bytes (0: load, encode, store with
+ * five resident thread blocks per SM; 1: software-pipelined loads, four resident blocks; 2: as 0 with four
+ * resident blocks).  form 0..2 forces one for both codecs, anything else restores the per-codec defaults (also
+ * settable once per process by the environment variable FLAME_ACT_COMPRESS_FORM).  Returns the previous
+ * override, -1 if none.  No counterpart in the reference. */
+int flame_act_set_compress_form(int form);
+
+/* Inspection of launch decisions (no counterpart in the reference, whose kernels use a fixed
+ * (n + 255) / 256 grid, src/cuda/fp8_quant.cu:84-88).  flame_act_last_launch: grid, resident thread
+ * blocks per SM the grid was sized for, tiles per block and kernel form (0..2, +4 with staged stores)
+ * of the calling thread's most recent fast-path compress or dequantise launch.
+ * flame_act_query_resident_blocks: a fresh occupancy query on the current device for the kernel a
+ * (codec, flags, form) selects; form < 0 = the codec's default form; compress 0 = the dequantise
+ * kernel.  Returns -1 on error. */
+typedef struct {
+  int32_t grid, resident_per_sm, tiles_per_block, form;
+} FlameActLaunchInfo;
+void flame_act_last_launch(FlameActLaunchInfo* out);
+int flame_act_query_resident_blocks(int codec, unsigned int flags, int form, int compress);
 
 /* ------------------------------------------------------------------------
  * 4. Activation offload pool.
@@ -385,6 +406,13 @@ typedef struct {
   double interference;          /* plan_blocks: extra compute time per unit of time a copy engine is busy beside it
                                    (copies slow HBM-bound kernels, see FlameOffloadPoolConfig.d2h_piece_bytes);
                                    ~0.1 measured on a B200 DiT step with 2 MiB pieces; 0 = ignore */
+  double overhead_cap_ms;       /* plan_blocks: 0 = least estimated step time within device_budget_bytes (above).
+                                   > 0 = the other way round: keep as few bytes resident as possible while the
+                                   estimated extra step time (stalls + recompute + interference) stays at or under
+                                   this many milliseconds; device_budget_bytes is then not consulted and the plan
+                                   reports the resident bytes it ends with.  This is the mode for a link whose rate
+                                   depends on how many replicas share it: the same cap gives a smaller offload on a
+                                   slower link instead of a stalled backward pass. */
 } FlamePolicyInput;
 
 /* Deterministic for given inputs.  decisions[i] receives a FLAME_POLICY_* value. */
@@ -397,7 +425,9 @@ FlameOffloadStatus flame_offload_policy_plan(const FlamePolicyInput* in, const F
  * start before its own offload has finished.  Searches over how many trailing
  * blocks stay resident (within device_budget_bytes) and how many leading
  * blocks are recomputed instead, and returns the plan with the least estimated
- * step time (ties: fewest resident bytes).  Deterministic. */
+ * step time (ties: fewest resident bytes); with overhead_cap_ms > 0 it returns
+ * instead the plan with the fewest resident bytes whose estimate is under the
+ * cap (all blocks resident always is).  Deterministic. */
 typedef struct {
   uint64_t saved_bytes; /* BF16 bytes the block saves for backward */
   double fwd_ms;        /* forward time of the block (= its recompute cost) */

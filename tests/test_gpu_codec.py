@@ -48,12 +48,78 @@ def test_fp8_sizes(cuda_device, n):
 
 @pytest.mark.parametrize("n", [8192, 8193, 5 * 8192 + 4000, (1 << 22) + 8192 * 3 + 9])
 def test_staged_store_path_gives_the_same_bytes(cuda_device, n):
-    """FLAME_ACT_STAGED_STORES: shared-memory tiles drained by bulk asynchronous copies."""
+    """FLAME_ACT_STAGED_STORES: each warp's shared-memory slice drained by bulk asynchronous copies."""
     bits = synthetic.normal_with_outliers(n, seed=n + 2)
     _check_int8(bits, cuda_device, flags=2)
     _check_int8(bits, cuda_device, flags=3)
     _check_fp8(bits, cuda_device, flags=2)
     _check_fp8(bits, cuda_device, flags=3)
+
+
+@pytest.mark.parametrize("form", [0, 1, 2])
+def test_every_kernel_form_gives_the_same_bytes(cuda_device, form):
+    """The three forms of the compress kernel (plain, software-pipelined, plain with four resident blocks), with
+    direct and with staged stores, against the oracle: full tiles, a ragged last tile, many rounds per block."""
+    lib = _lib.lib()
+    lib.flame_act_set_compress_form(form)
+    try:
+        info = _lib.ActLaunchInfo()
+        for n in (8192, 3 * 8192 + 77, (1 << 20) + 13, (1 << 24) + 8192 * 5 + 1):
+            bits = synthetic.normal_with_outliers(n, seed=n + form)
+            for flags in (0, 2):
+                _check_int8(bits, cuda_device, flags=flags)
+                lib.flame_act_last_launch(info)            # the dequantise launch of the check ran last
+                _check_fp8(bits, cuda_device, flags=flags)
+        x = G.to_dev(synthetic.normal(1 << 20, seed=3), cuda_device)
+        G.quant("fp8", x, 2)
+        lib.flame_act_last_launch(info)
+        assert info.form == form + 4
+    finally:
+        lib.flame_act_set_compress_form(-1)
+
+
+_OCCUPANCY_SCRIPT = r"""
+import sys, json
+import numpy as np, torch
+sys.path.insert(0, {root!r})
+from flame_b200 import _lib
+lib = _lib.lib()
+torch.cuda.set_device(0)
+n = 1 << 24
+x = torch.randn(n, device="cuda").to(torch.bfloat16)
+codes = torch.empty(n, dtype=torch.uint8, device="cuda")
+scales = torch.empty(n // 128, dtype=torch.float32, device="cuda")
+info = _lib.ActLaunchInfo()
+out = {{}}
+for codec in {order!r}:
+    fn = getattr(lib, "flame_act_quant_%s_b128" % codec)
+    assert fn(x.data_ptr(), codes.data_ptr(), scales.data_ptr(), n, 0, None) == 0
+    lib.flame_act_last_launch(info)
+    cid = 2 if codec == "int8" else 3
+    out[codec] = dict(used=info.resident_per_sm, fresh=lib.flame_act_query_resident_blocks(cid, 0, -1, 1), grid=info.grid, form=info.form)
+torch.cuda.synchronize()
+print(json.dumps(out))
+"""
+
+
+@pytest.mark.parametrize("order", [("fp8", "int8"), ("int8", "fp8")])
+def test_each_kernel_is_sized_by_its_own_occupancy(cuda_device, order):
+    """The grid of a launch comes from the occupancy of the kernel that is launched, whichever kernel ran first in
+    the process (the kernels are instantiations of one template and differ in registers per thread)."""
+    import json
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", _OCCUPANCY_SCRIPT.format(root=root, order=order)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = json.loads(r.stdout.strip().splitlines()[-1])
+    for codec in order:
+        assert got[codec]["used"] == got[codec]["fresh"] > 0, got
+    # the two default kernels differ in registers per thread, so a shared answer would show here
+    lib = _lib.lib()
+    assert got["int8"]["fresh"] == lib.flame_act_query_resident_blocks(2, 0, -1, 1)
+    assert got["fp8"]["fresh"] == lib.flame_act_query_resident_blocks(3, 0, -1, 1)
 
 
 def test_empty_input_is_a_no_op(cuda_device):

@@ -59,3 +59,26 @@ def test_block_plan_keeps_trailing_blocks_resident_and_counts_interference():
     assert set(all_res.decisions) == {Decision.RESIDENT} and all_res.link_bytes == 0
     none = plan_blocks(blocks, d2h_gbs=57, h2d_gbs=55.5, device_budget_bytes=0, offload=Decision.OFFLOAD_BF16)
     assert Decision.RESIDENT not in none.decisions and (Decision.RECOMPUTE in none.decisions)
+
+
+def test_capped_plan_offloads_less_over_a_slower_link():
+    """overhead_cap_ms: the fewest resident bytes whose estimated extra time stays under the cap."""
+    from flame_b200.policy import Block, plan_blocks
+
+    blocks = [Block(340 * MB, 1.64, 3.74) for _ in range(20)]
+    step_ms = 20 * (1.64 + 3.74)
+    cap = 0.04 * step_ms
+    fast = plan_blocks(blocks, d2h_gbs=57, h2d_gbs=55.5, overhead_cap_ms=cap)
+    slow = plan_blocks(blocks, d2h_gbs=10, h2d_gbs=21, overhead_cap_ms=cap)
+    slower = plan_blocks(blocks, d2h_gbs=3, h2d_gbs=6, overhead_cap_ms=cap)
+    for p in (fast, slow, slower):
+        assert p.est_stall_ms + p.est_recompute_ms + p.est_interference_ms <= cap + 1e-9
+        # residents are the trailing blocks, recomputed ones the leading blocks
+        s = "".join({Decision.RESIDENT: "R", Decision.RECOMPUTE: "C"}.get(d, "O") for d in p.decisions)
+        assert s == "C" * s.count("C") + "O" * s.count("O") + "R" * s.count("R")
+    assert fast.resident_bytes < slow.resident_bytes <= slower.resident_bytes
+    assert fast.link_bytes > slow.link_bytes >= slower.link_bytes
+    # a cap nothing but the all-resident plan meets still gives a plan
+    none = plan_blocks(blocks, d2h_gbs=57, h2d_gbs=55.5, overhead_cap_ms=1e-6, interference=0.1)
+    assert set(none.decisions) == {Decision.RESIDENT}
+    assert plan_blocks(blocks, d2h_gbs=10, h2d_gbs=21, overhead_cap_ms=cap).decisions == slow.decisions  # deterministic
