@@ -7,21 +7,32 @@ training step (20 blocks x {2 norm outputs, QKV, attention output, SwiGLU
 gate+up} at 4608 tokens, hidden 3072; 6.79 GB of BF16): every tensor is
 offloaded in forward order, then every tensor is restored in reverse order.
 
-Reported, for the whole job (all N replicas):
+Reported, for the whole job (all N replicas; the slowest replica sets the time):
 
 * ``value``  BF16-equivalent GB/s (bytes offloaded + bytes restored, per second)
-  of the device-resident part: compress into packed device buffers and
-  dequantise back, inputs and outputs in HBM, no host link.
-* ``e2e``    the same metric through ``ActivationOffloadPool.push`` /
-  ``pull_into``: compress, D2H into the pinned slab, H2D, dequantise into the
-  destination tensor.  The host<->device copies are inside the timed region.
+  of the path itself: ``push`` of every tensor (compress, D2H into the pinned
+  slab), then ``pull_into`` of every tensor (H2D, dequantise into the
+  destination).  Inputs are resident in HBM when the timed region starts, as
+  activations are; CUDA events; ``value_per_gpu`` = value / N.
+* ``e2e``    the same step through the reference's own signatures, ``push`` and
+  the allocating ``pull``, plus a device-to-host read of a number computed from
+  what came back, timed on the host clock around a device synchronise.
 * ``roofline``  achieved algorithmic GB/s of the compress kernel (3.03125 B per
-  element) against the measured HBM copy rate; ``roofline_dequant`` likewise.
-* ``link``   achieved D2H / H2D GB/s against the PCIe Gen5 x16 bound (63.0 GB/s).
+  element) with inputs and outputs in HBM, against the measured HBM copy rate;
+  ``roofline_dequant`` likewise.  No host link in that leg: it is what bounds
+  the kernels, not the metric.
+* ``link``   D2H / H2D GB/s of the pool per replica, measured one direction at a
+  time (a barrier between) and both at once, beside plain pinned copies issued
+  by all replicas at the same moment and the PCIe Gen5 x16 bound (63.0 GB/s);
+  ``link.pcie`` is what sysfs says about each GPU's link and its bridges.
+* ``fp8_mixed``  (N=1) the FP8 per-128 codec over the mixed activation set
+  (GELU outputs, heavy-tailed attention outputs, SwiGLU hidden states).
 * ``cpu_baseline``  the CPU oracle's quantise+pack / unpack+dequantise on this
   box's host cores over a bounded sample (rank 0, N=1 only).
-* ``overhead``  (N=1, unless --no-dit) step time of a 20-block DiT training step
-  with activations offloaded / recomputed, relative to keeping them resident.
+* ``overhead``  step time of a 20-block DiT training step with activations
+  offloaded, relative to keeping them resident.  N=1: every arm.  N>1: on every
+  replica at once, the link probed with all replicas copying, and the plan that
+  keeps the estimated overhead under a cap at that link rate.
 
 ``--impl reference`` times the reference's CPU arm instead: the reference crate
 is GPU-only Rust and has no CPU quantise/pack path of its own, so the timed code
@@ -41,14 +52,14 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-METRIC = "activation offload+restore GB/s per GPU (BF16-equiv), whole job"
+METRIC = "activation offload+restore GB/s (BF16-equiv), sum over the N replicas (value_per_gpu = value / N)"
 UNIT = "GB/s"
 ALG_BYTES_PER_ELEM = 3.03125  # 2 B read + 1 B code + 4/128 B scale (and the mirror image for dequantise)
 # dram__bytes_read.sum + dram__bytes_write.sum per element from the ncu captures summarised under profiles/
-# (one launch = one DiT block, 169,869,312 elements: 486.1 MB compress, 458.1 MB dequantise); traffic grows in
+# (one launch = one DiT block, 169,869,312 elements: 483.1 MB int8 / 490.0 MB FP8 compress, 458.1 MB dequantise); traffic grows in
 # proportion to the elements of a launch.  Below the algorithmic figure because the L2 still holds part of the
 # output when the kernel ends.
-NCU_TRAFFIC_PER_ELEM = {"compress": 479.7e6 / 169869312, "dequant": 458.1e6 / 169869312}
+NCU_TRAFFIC_PER_ELEM = {"compress": {"int8": 483.1e6 / 169869312, "fp8": 490.0e6 / 169869312}, "dequant": 458.1e6 / 169869312}
 PCIE_GEN5_X16_GBS = 63.0      # 32 GT/s x 16 lanes x 128/130 / 8
 TOKENS, HIDDEN, BLOCKS = 4608, 3072, 20
 # saved set of one block, as last dims: norm1 out, QKV, attention out, norm2 out, SwiGLU gate+up
@@ -183,11 +194,15 @@ def verify_against_oracle(torch, lib, x, codec: str) -> bool:
 
 
 def plain_copy_rates(torch, lib, dev, barrier):
-    """(D2H GB/s, H2D GB/s) of a plain 1 GiB pinned cudaMemcpyAsync on this replica, started together with the others."""
+    """(D2H, H2D, duplex D2H, duplex H2D) GB/s of plain 1 GiB pinned cudaMemcpyAsync on this replica, every phase started
+    together with the other replicas; the duplex pair runs both directions at once on two streams."""
     nb = 1 << 30
     d = torch.empty(nb, dtype=torch.uint8, device=dev)
+    d2 = torch.empty(nb, dtype=torch.uint8, device=dev)
     h = torch.empty(nb, dtype=torch.uint8).pin_memory()
+    h2 = torch.empty(nb, dtype=torch.uint8).pin_memory()
     st = torch.cuda.current_stream()
+    side = torch.cuda.Stream(dev)
     rates = []
     for kind, dst, src in ((2, h, d), (1, d, h)):
         lib.flame_cuda_memcpy_async(dst.data_ptr(), src.data_ptr(), nb, kind, st.cuda_stream)
@@ -199,6 +214,17 @@ def plain_copy_rates(torch, lib, dev, barrier):
         e1.record(st)
         torch.cuda.synchronize()
         rates.append(2 * nb / (e0.elapsed_time(e1) * 1e-3) * 1e-9)
+    lib.flame_cuda_memcpy_async(d2.data_ptr(), h2.data_ptr(), nb, 1, side.cuda_stream)
+    barrier()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    ev[0].record(st); ev[2].record(side)
+    for _ in range(2):
+        lib.flame_cuda_memcpy_async(h.data_ptr(), d.data_ptr(), nb, 2, st.cuda_stream)
+        lib.flame_cuda_memcpy_async(d2.data_ptr(), h2.data_ptr(), nb, 1, side.cuda_stream)
+    ev[1].record(st); ev[3].record(side)
+    torch.cuda.synchronize()
+    rates.append(2 * nb / (ev[0].elapsed_time(ev[1]) * 1e-3) * 1e-9)
+    rates.append(2 * nb / (ev[2].elapsed_time(ev[3]) * 1e-3) * 1e-9)
     return rates
 
 
@@ -641,6 +667,203 @@ def run_producers(args, torch, lib, dev):
     print(json.dumps(out), flush=True)
 
 
+def pcie_info(torch, index: int) -> dict:
+    """What sysfs says about the host link of CUDA device `index`: negotiated and maximum speed and width of the GPU's
+    own PCIe function and of every bridge above it, up to the root.  Plain file reads; absent files are left out."""
+    try:
+        pr = torch.cuda.get_device_properties(index)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+    except Exception as exc:
+        return {"error": f"{type(exc).__name__}: {exc}"}
+
+    def read(path):
+        try:
+            with open(path) as f:
+                return f.read().strip()
+        except OSError:
+            return None
+
+    def link(dev_path):
+        d = {k: read(os.path.join(dev_path, k)) for k in ("current_link_speed", "current_link_width", "max_link_speed", "max_link_width")}
+        return {k: v for k, v in d.items() if v is not None}
+
+    out = {"bdf": bdf}
+    node = os.path.realpath(os.path.join("/sys/bus/pci/devices", bdf))
+    if not os.path.isdir(node):
+        out["sysfs"] = "no such device directory"
+        return out
+    out.update(link(node))
+    numa = read(os.path.join(node, "numa_node"))
+    if numa is not None:
+        out["numa_node"] = numa
+    chain = []
+    parent = os.path.dirname(node)
+    while os.path.basename(parent).count(":") == 2:          # 0000:17:00.0 style names: bridges above the GPU
+        chain.append({"bdf": os.path.basename(parent), **link(parent)})
+        parent = os.path.dirname(parent)
+    out["bridges_to_root"] = chain
+    out["root"] = os.path.basename(parent)
+    return out
+
+
+def verify_restored(torch, tensors, dst, codec: str, picks=(0, 2, 3)) -> bool:
+    """A few restored tensors of the pool round trip against the CPU oracle's dequantise-of-quantise of their sources
+    (bit for bit; for the uncompressed mode, against the sources themselves).  The checker, not the product."""
+    import numpy as np
+    from oracle import capi
+
+    ok = True
+    for i in picks:
+        if i >= len(tensors):
+            continue
+        got = dst[i].reshape(-1).view(torch.int16).cpu().numpy().view(np.uint16)
+        bits = tensors[i].reshape(-1).view(torch.int16).cpu().numpy().view(np.uint16)
+        if codec == "none":
+            ok &= bool(np.array_equal(got, bits))
+            continue
+        wc, ws = (capi.quant_int8_b128 if codec == "int8" else capi.quant_fp8_b128)(bits)
+        ok &= bool(np.array_equal(got, (capi.dequant_int8_b128 if codec == "int8" else capi.dequant_fp8_b128)(wc, ws)))
+    return ok
+
+
+def codec_leg(torch, lib, dev, tensors, dst, codec: str, steps: int, warmup: int, groups, sampler_index: int):
+    """Compress into packed device buffers and dequantise back, HBM in and HBM out, one launch per group of tensors.
+    Returns (ms per step compress, ms per step dequantise, launches per step, clock summary)."""
+    from flame_b200 import _lib
+
+    stream = torch.cuda.current_stream()
+    sp = stream.cuda_stream
+    codec_id = 2 if codec == "int8" else 3
+    packed = [torch.empty(lib.flame_act_packed_bytes(t.numel()), dtype=torch.uint8, device=dev) for t in tensors]
+    so = [lib.flame_act_packed_scales_offset(t.numel()) for t in tensors]
+
+    def table(bf16):
+        return [((_lib.ActTensor * len(g))(*[_lib.ActTensor(bf16[i].data_ptr(), packed[i].data_ptr(), packed[i].data_ptr() + so[i],
+                                                              bf16[i].numel()) for i in g]), len(g)) for g in groups]
+    q_tables, d_tables = table(tensors), table(dst)
+
+    def offload_all():
+        for arr, n in q_tables:
+            rc = lib.flame_act_quant_b128_multi(codec_id, arr, n, 0, sp)
+            assert rc == 0, rc
+
+    def restore_all():
+        for arr, n in reversed(d_tables):
+            rc = lib.flame_act_dequant_b128_multi(codec_id, arr, n, sp)
+            assert rc == 0, rc
+
+    for _ in range(max(warmup, 1)):
+        offload_all(); restore_all()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * steps + 1)]
+    with ClockSampler(sampler_index) as clk:
+        ev[0].record(stream)
+        for k in range(steps):
+            offload_all(); ev[2 * k + 1].record(stream)
+            restore_all(); ev[2 * k + 2].record(stream)
+        torch.cuda.synchronize()
+    q_ms = sum(ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(steps)) / steps
+    d_ms = sum(ev[2 * k + 1].elapsed_time(ev[2 * k + 2]) for k in range(steps)) / steps
+    return q_ms, d_ms, len(groups), clk.summary()
+
+
+def roofline_entries(codec: str, q_ms: float, d_ms: float, elems: int, launches: int):
+    hbm_peak, peak_kind = measured_peaks()
+    alg = ALG_BYTES_PER_ELEM * elems
+    qa, da = alg / (q_ms * 1e-3) * 1e-9, alg / (d_ms * 1e-3) * 1e-9
+    comp = {"bound": "hbm", "kernel": "compress_b128_kernel", "achieved": round(qa, 1), "peak": hbm_peak, "unit": "GB/s",
+            "frac": round(qa / hbm_peak, 4), "peak_kind": f"of {peak_kind}",
+            "traffic": int(NCU_TRAFFIC_PER_ELEM["compress"][codec] * elems / launches),
+            "alg_bytes_per_launch": int(alg / launches), "avg_launch_us": round(q_ms * 1e3 / launches, 2), "launches_per_step": launches,
+            "leg": "device-resident: packed codes written to HBM, no host link"}
+    deq = {"bound": "hbm", "kernel": "dequant_b128_kernel", "achieved": round(da, 1), "peak": hbm_peak, "unit": "GB/s",
+           "frac": round(da / hbm_peak, 4), "peak_kind": f"of {peak_kind}",
+           "traffic": int(NCU_TRAFFIC_PER_ELEM["dequant"] * elems / launches),
+           "alg_bytes_per_launch": int(alg / launches), "avg_launch_us": round(d_ms * 1e3 / launches, 2)}
+    return comp, deq
+
+
+def run_fp8_mixed(torch, lib, dev, steps: int, warmup: int) -> dict:
+    """FP8 e4m3 per-128 (scale = absmax/448) over the mixed activation set: GELU outputs of an N(0,1) input
+    [1,4608,9216], heavy-tailed attention outputs 2*t(nu=3) [1,4608,3072], SwiGLU hidden states [1,4608,9216].
+    Codes and scales of a sample are checked against the oracle; the kernels are timed device-resident, the pool end
+    to end.  The three tensors are replicated to six so that one pass is larger than the L2."""
+    import numpy as np
+    from flame_b200 import ActivationOffloadPool, OffloadCompression, synthetic
+    from oracle import capi
+
+    base = [synthetic.gelu_of_normal(TOKENS * 3 * HIDDEN, seed=0), synthetic.student_t3_times2(TOKENS * HIDDEN, seed=0),
+            synthetic.swiglu_hidden(TOKENS * 3 * HIDDEN, seed=0)]
+    names = ["gelu(N(0,1)) [1,4608,9216]", "2*t(nu=3) [1,4608,3072]", "silu(g)*u [1,4608,9216]"]
+    tensors = [torch.from_numpy(b.view(np.int16)).to(dev).view(torch.bfloat16) for b in base]
+    tensors = tensors + [t.clone() for t in tensors]
+    dst = [torch.empty_like(t) for t in tensors]
+    step_bytes = sum(t.numel() * 2 for t in tensors)
+    step_elems = sum(t.numel() for t in tensors)
+    ok = True
+    for b in base:                                           # the first 4 Mi elements of each distribution against the oracle
+        ok &= verify_against_oracle(torch, lib, torch.from_numpy(b[:1 << 22].view(np.int16)).to(dev).view(torch.bfloat16), "fp8")
+    groups = [[0, 1, 2], [3, 4, 5]]
+    q_ms, d_ms, launches, clk = codec_leg(torch, lib, dev, tensors, dst, "fp8", steps, warmup, groups, dev.index or 0)
+    comp, deq = roofline_entries("fp8", q_ms, d_ms, step_elems, launches)
+    pool = ActivationOffloadPool(dev, len(tensors), max(t.numel() * 2 for t in tensors), OffloadCompression.FP8_B128,
+                                 host_budget_bytes=ActivationOffloadPool.host_bytes_needed([t.numel() * 2 for t in tensors], OffloadCompression.FP8_B128))
+    stream = torch.cuda.current_stream()
+
+    def step():
+        hs = [pool.push(t) for t in tensors]
+        for h, d in zip(reversed(hs), reversed(dst)):
+            pool.pull_into(h, d)
+    for _ in range(max(1, warmup)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    ok &= verify_restored(torch, tensors, dst, "fp8", picks=(1,))
+    # quantisation error of the round trip per distribution, relative to the block maximum (one e4m3 step is 1/16 at most)
+    err = {}
+    for n, t, d in zip(names, tensors, dst):
+        x, y = t.float().view(-1, 128), d.float().view(-1, 128)
+        err[n] = round(float(((x - y).abs().amax(1) / x.abs().amax(1).clamp_min(1e-30)).max()), 4)
+    pool.close()
+    return {"workload": "FP8 e4m3 per 128 over " + ", ".join(names) + " (each twice: 339.7 MB per pass)", "verified_against_oracle": bool(ok),
+            "value": round(2 * step_bytes / (ms * 1e-3) * 1e-9, 2), "unit": UNIT, "ms_per_step": round(ms, 3), "steps": steps,
+            "roofline": comp, "roofline_dequant": deq, "max_abs_err_over_block_absmax": err, "clocks": clk}
+
+
+def run_overhead_replicas(torch, dev, rank: int, world: int, barrier, gather, steps: int) -> dict:
+    """N > 1: the DiT step on every replica at the same moment.  The link is probed with all replicas copying at
+    once, the block planner gets those rates and a cap on the estimated overhead, and the planned arm runs beside
+    the resident one."""
+    from flame_b200.dit_workload import measure_overhead
+
+    o = measure_overhead(dev, steps=steps, warmup=2, arms=("capped",), sync=barrier)
+    keys = ("ms_per_step", "overhead_pct", "overhead_pct_vs_mean_baseline", "held_after_forward_gb", "peak_mem_gb")
+    mine = o.get("offload_int8_capped", {})
+    out = {"replicas": world, "model": o["model"], "cap_pct": o.get("cap_pct"), "interference": o.get("interference"),
+           "note": "every replica probes its link, plans and runs the step at the same moment; lists are in rank order"}
+    out["probe_d2h_gbs"] = [round(v, 2) for v in gather(o["probe"]["d2h_gbs"])]
+    out["probe_h2d_gbs"] = [round(v, 2) for v in gather(o["probe"]["h2d_gbs"])]
+    out["resident_ms_per_step"] = [round(v, 3) for v in gather(o["resident"]["ms_per_step"])]
+    out["resident_held_after_forward_gb"] = o["resident"]["held_after_forward_gb"]
+    for k in keys:
+        out["planned_" + k] = [round(v, 3) for v in gather(float(mine.get(k, float("nan"))))]
+    offl = gather(float(mine.get("blocks", "").count("O")))
+    reco = gather(float(mine.get("blocks", "").count("C")))
+    out["planned_blocks_offloaded"] = [int(v) for v in offl]
+    out["planned_blocks_recomputed"] = [int(v) for v in reco]
+    out["planned_freed_after_forward_gb"] = [round(out["resident_held_after_forward_gb"] - v, 3) for v in out["planned_held_after_forward_gb"]]
+    out["rank0"] = {"plan": mine.get("blocks"), "plan_est_ms": mine.get("plan_est_ms"), "offloaded_gb_per_step": mine.get("offloaded_gb_per_step"),
+                    "link_gb_per_step": mine.get("link_gb_per_step")}
+    out["overhead_pct_worst_replica"] = max(out["planned_overhead_pct_vs_mean_baseline"])
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -650,11 +873,15 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--chunk-mb", type=int, default=16)
     ap.add_argument("--tile-chunks", type=int, default=8)
+    ap.add_argument("--d2h-piece-mb", type=float, default=0.0, help="issue device-to-host copies in pieces of this size (0 = whole chunks)")
+    ap.add_argument("--host-alloc-flags", type=int, default=0, help="cudaHostAlloc flags of the pinned slab (4 = write-combined)")
     ap.add_argument("--blocks", type=int, default=BLOCKS, help="fewer blocks = smaller case (profiling only)")
     ap.add_argument("--no-dit", action="store_true", help="skip the DiT training-step overhead measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-fp8-mixed", action="store_true", help="skip the FP8 mixed-activation-set block")
     ap.add_argument("--no-ref-gpu", action="store_true", help="--impl reference: skip timing the reference's own compiled CUDA files")
-    ap.add_argument("--only", choices=["all", "value", "e2e"], default="all", help="profiling: run only one timed region")
+    ap.add_argument("--only", choices=["all", "value", "codec", "e2e"], default="all",
+                    help="profiling: run only one timed region (codec = the device-resident compress/dequantise leg)")
     ap.add_argument("--mode", choices=["bench", "sweep", "interference", "weights", "producers"], default="bench",
                     help="sweep: 1 MB..4 GB single tensor x codec x chunk size; interference: copies against HBM-bound kernels; "
                          "weights: block weights streamed host->device through the same pool")
@@ -691,26 +918,15 @@ def main():
     def max_over_ranks(ms: float) -> float:
         return replicas.max_over_ranks(ms, world, dev)
 
-    if args.mode == "sweep":
-        run_sweep(args, torch, lib, dev, rank)
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    if args.mode == "producers":
-        if rank == 0:
-            run_producers(args, torch, lib, dev)
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    if args.mode == "weights":
-        if rank == 0:
-            run_weights(args, torch, dev)
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    if args.mode == "interference":
-        if rank == 0:
-            run_interference(args, torch, lib, dev)
+    def gather(v: float) -> list:
+        return replicas.gather_over_ranks(v, world, dev)
+
+    if args.mode != "bench":
+        if args.mode == "sweep":
+            run_sweep(args, torch, lib, dev, rank)
+        elif rank == 0:
+            {"producers": lambda: run_producers(args, torch, lib, dev), "weights": lambda: run_weights(args, torch, dev),
+             "interference": lambda: run_interference(args, torch, lib, dev)}[args.mode]()
         if world > 1:
             dist.destroy_process_group()
         return
@@ -721,181 +937,198 @@ def main():
     max_bytes = max(t.numel() * 2 for t in tensors)
     mode = {"int8": OffloadCompression.INT8_B128, "fp8": OffloadCompression.FP8_B128, "none": OffloadCompression.NONE}[args.codec]
     stream = torch.cuda.current_stream()
-    sp = stream.cuda_stream
     verified = verify_against_oracle(torch, lib, tensors[1], args.codec) if args.codec != "none" else True
-
-    # ---- device-resident leg: compress + dequantise, HBM in, HBM out ---------------------------------
-    value_ms = quant_ms = dequant_ms = None
-    launches = 0
     dst = [torch.empty_like(t) for t in tensors]
-    if args.only in ("all", "value"):
-        if args.codec == "none":
-            def offload_all():
-                for t, d in zip(tensors, packed):
-                    lib.flame_d2d_async(d.data_ptr(), t.data_ptr(), t.numel() * 2, sp)
+    hbm_peak, peak_kind = measured_peaks()
+    line = {
+        "metric": METRIC, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": {"int8": "int8 codes + f32 scales", "fp8": "fp8-e4m3 codes + f32 scales", "none": "bf16"}[args.codec],
+        "data": "synthetic", "config": workload_config(args, world),
+    }
+    launches = 0
 
-            def restore_all():
-                for d, p in zip(reversed(dst), reversed(packed)):
-                    lib.flame_d2d_async(d.data_ptr(), p.data_ptr(), d.numel() * 2, sp)
-            packed = [torch.empty(t.numel() * 2, dtype=torch.uint8, device=dev) for t in tensors]
-            per_step_launches = 0
-        else:
-            # one launch per checkpointed block: its five saved tensors are pushed together
-            # (flame_act_quant_b128_multi), as checkpoint_offload pushes a block's sub-tape in one loop
-            codec_id = 2 if args.codec == "int8" else 3
-            packed = [torch.empty(lib.flame_act_packed_bytes(t.numel()), dtype=torch.uint8, device=dev) for t in tensors]
-            so = [lib.flame_act_packed_scales_offset(t.numel()) for t in tensors]
-            per_block = len(BLOCK_SAVED)
-            groups = [list(range(b, min(b + per_block, len(tensors)))) for b in range(0, len(tensors), per_block)]
-
-            def table(bf16):
-                return [((_lib.ActTensor * len(g))(*[_lib.ActTensor(bf16[i].data_ptr(), packed[i].data_ptr(), packed[i].data_ptr() + so[i],
-                                                                      bf16[i].numel()) for i in g]), len(g)) for g in groups]
-            q_tables, d_tables = table(tensors), table(dst)
-
-            def offload_all():
-                for arr, n in q_tables:
-                    rc = lib.flame_act_quant_b128_multi(codec_id, arr, n, 0, sp)
-                    assert rc == 0, rc
-
-            def restore_all():
-                for arr, n in reversed(d_tables):
-                    rc = lib.flame_act_dequant_b128_multi(codec_id, arr, n, sp)
-                    assert rc == 0, rc
-            per_step_launches = 2 * len(groups)
-
-        for _ in range(max(args.warmup, 1)):
-            offload_all(); restore_all()
-        barrier()
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3 * args.steps + 1)]
-        with ClockSampler(local) as clk_value:
-            ev[0].record(stream)
-            for k in range(args.steps):
-                offload_all(); ev[3 * k + 1].record(stream)
-                restore_all(); ev[3 * k + 2].record(stream)
-                ev[3 * k + 3].record(stream)
-            barrier()
-        quant_ms = sum(ev[3 * k].elapsed_time(ev[3 * k + 1]) for k in range(args.steps)) / args.steps
-        dequant_ms = sum(ev[3 * k + 1].elapsed_time(ev[3 * k + 2]) for k in range(args.steps)) / args.steps
-        value_ms = max_over_ranks(ev[0].elapsed_time(ev[-1]) / args.steps)
-        launches += per_step_launches * args.steps
-        del packed
-
-    # ---- end-to-end leg: the pool, through pinned host memory --------------------------------------------
-    e2e = link = None
-    e2e_ms = None
-    if args.only in ("all", "e2e"):
-        pool = ActivationOffloadPool(dev, len(tensors), max_bytes, mode, chunk_bytes=args.chunk_mb << 20,
-                                     tile_chunks=args.tile_chunks,
+    # ---- the path: the pool, through pinned host memory; inputs resident in HBM, CUDA events -----------------------
+    if args.only in ("all", "value", "e2e"):
+        pool = ActivationOffloadPool(dev, len(tensors), max_bytes, mode, chunk_bytes=args.chunk_mb << 20, tile_chunks=args.tile_chunks,
+                                     d2h_piece_bytes=int(args.d2h_piece_mb * (1 << 20)), host_alloc_flags=args.host_alloc_flags,
                                      host_budget_bytes=ActivationOffloadPool.host_bytes_needed(
                                          [t.numel() * 2 for t in tensors], mode, args.chunk_mb << 20))
 
-        def e2e_step():
+        def path_step():
             handles = [pool.push(t) for t in tensors]
             for h, d in zip(reversed(handles), reversed(dst)):
                 pool.pull_into(h, d)
 
+    if args.only in ("all", "value"):
         for _ in range(max(args.warmup, 1)):
-            e2e_step()
+            path_step()
         barrier()
         st0 = pool.stats()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local) as clk_e2e:
+        with ClockSampler(local) as clk_value:
             wall0 = time.perf_counter()
             e0.record(stream)
             for _ in range(args.steps):
-                e2e_step()
+                path_step()
             e1.record(stream)
             barrier()
             wall = (time.perf_counter() - wall0) / args.steps
-        e2e_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+        my_ms = e0.elapsed_time(e1) / args.steps
+        value_ms = max_over_ranks(my_ms)
         st1 = pool.stats()
         d2h_b = (st1["bytes_link_out"] - st0["bytes_link_out"]) // args.steps
         h2d_b = (st1["bytes_link_in"] - st0["bytes_link_in"]) // args.steps
         launches += st1["codec_launches"] - st0["codec_launches"]
-        # restored values must equal the device-resident result (same kernels) and, for none, the source
-        if args.codec == "none":
-            assert all(torch.equal(a.view(torch.int16), b.view(torch.int16)) for a, b in zip(tensors[:3], dst[:3])), "BF16 round trip not bit exact"
+        # what came back, against the oracle's dequantise-of-quantise of what went out
+        restored_ok = verify_restored(torch, tensors, dst, args.codec) if args.workload == "dit" else verify_restored(torch, tensors, dst, args.codec, picks=(0,))
+        verified = bool(verified and restored_ok)
+        value = world * 2 * step_bytes / (value_ms * 1e-3) * 1e-9
+        line.update({"value": round(value, 2), "value_per_gpu": round(value / world, 2), "ms_per_step": round(value_ms, 3),
+                     "ms_per_step_per_replica": [round(v, 2) for v in gather(my_ms)], "wall_ms_per_step": round(wall * 1e3, 3),
+                     "pinned_bytes": pool.host_bytes(), "d2h_bytes_per_step": int(d2h_b), "h2d_bytes_per_step": int(h2d_b),
+                     "api": "flame_offload_pool_push / flame_offload_pool_pull_into", "clocks": clk_value.summary()})
 
-        # per-direction link rate, measured apart from the headline: all offloads, wait, then all restores
+    # ---- end to end through the reference's signatures: push, allocating pull, a result read back on the host ------
+    if args.only in ("all", "e2e"):
+        def e2e_step():
+            handles = [pool.push(t) for t in tensors]
+            acc = torch.zeros((), dtype=torch.float32, device=dev)
+            for h in reversed(handles):
+                y = pool.pull(h)                        # a fresh tensor per pull, as src/activation_offload.rs:655
+                acc += y.view(-1)[:: max(1, y.numel() // 64)].float().sum()
+                del y
+            return float(acc.item())                    # device-to-host read of the step's result
+
+        k_e2e = max(1, min(args.steps, 10))
+        for _ in range(max(1, min(args.warmup, 2))):
+            e2e_step()
+        barrier()
+        sa = pool.stats()
+        with ClockSampler(local) as clk_e2e:
+            t0 = time.perf_counter()
+            for _ in range(k_e2e):
+                result = e2e_step()
+            torch.cuda.synchronize()
+            my_s = (time.perf_counter() - t0) / k_e2e
+            barrier()
+        sb = pool.stats()
+        launches_e2e = sb["codec_launches"] - sa["codec_launches"]
+        e2e_ms = max_over_ranks(my_s * 1e3)
+        line["e2e"] = {"value": round(world * 2 * step_bytes / (e2e_ms * 1e-3) * 1e-9, 2), "unit": UNIT,
+                       "h2d_bytes_per_step": int((sb["bytes_link_in"] - sa["bytes_link_in"]) // k_e2e),
+                       "d2h_bytes_per_step": int((sb["bytes_link_out"] - sa["bytes_link_out"]) // k_e2e) + 4,   # + the result read back
+                       "ms_per_step": round(e2e_ms, 3), "steps": k_e2e, "timed": "host clock around the steps and a device synchronise",
+                       "result_read_back": result, "gpu_launches": int(launches_e2e),
+                       "api": "ActivationOffloadPool.push / pull (fresh destination per pull) + .item() of a checksum"}
+        line["clocks_e2e"] = clk_e2e.summary()
+        if "value" not in line:
+            line.update({"value": line["e2e"]["value"], "ms_per_step": line["e2e"]["ms_per_step"], "clocks": line["clocks_e2e"]})
+
+    # ---- per-direction link rates, apart from the headline ------------------------------------------------------------
+    if args.only == "all":
         barrier()
         w0 = time.perf_counter()
         handles = [pool.push(t) for t in tensors]
-        pool.synchronize(120.0)          # bounded wait for the pool's own streams
+        pool.synchronize(300.0)          # bounded wait for the pool's own streams
         d2h_s = time.perf_counter() - w0
+        barrier()                        # every replica has finished offloading before any starts restoring
         a1, a2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a1.record(stream)
         for h, d in zip(reversed(handles), reversed(dst)):
             pool.pull_into(h, d)          # the compute stream waits for each restore
         a2.record(stream)
         torch.cuda.synchronize()
-        d2h_all = replicas.gather_over_ranks(d2h_b / d2h_s * 1e-9, world, dev)
-        h2d_all = replicas.gather_over_ranks(h2d_b / (a1.elapsed_time(a2) * 1e-3) * 1e-9, world, dev)
+        d2h_all = gather(d2h_b / d2h_s * 1e-9)
+        h2d_all = gather(h2d_b / (a1.elapsed_time(a2) * 1e-3) * 1e-9)
+        # both directions at once: the second half of the tensors goes out while the first half comes back
+        half = len(tensors) // 2
+        first = [pool.push(t) for t in tensors[:half]]
+        pool.synchronize(300.0)
+        barrier()
+        sa = pool.stats()
+        w0 = time.perf_counter()
+        second = []
+        for i in range(half):
+            second.append(pool.push(tensors[half + i]))
+            pool.pull_into(first[half - 1 - i], dst[half - 1 - i])
+        pool.synchronize(300.0)
+        torch.cuda.synchronize()
+        dup_s = time.perf_counter() - w0
+        sb = pool.stats()
+        dup_out = gather((sb["bytes_link_out"] - sa["bytes_link_out"]) / dup_s * 1e-9)
+        dup_in = gather((sb["bytes_link_in"] - sa["bytes_link_in"]) / dup_s * 1e-9)
+        for h in second:
+            pool.discard(h)
         # the practical ceiling at this replica count: plain 1 GiB pinned copies, all replicas at the same moment
         plain = plain_copy_rates(torch, lib, dev, barrier)
-        plain_d2h = replicas.gather_over_ranks(plain[0], world, dev)
-        plain_h2d = replicas.gather_over_ranks(plain[1], world, dev)
+        plain_d2h, plain_h2d = gather(plain[0]), gather(plain[1])
+        plain_dup_out, plain_dup_in = gather(plain[2]), gather(plain[3])
+        r1 = lambda xs: [round(v, 1) for v in xs]
         link = {"bound_gbs": PCIE_GEN5_X16_GBS, "d2h_gbs": round(min(d2h_all), 2), "h2d_gbs": round(min(h2d_all), 2),
-                "d2h_gbs_per_replica": [round(v, 1) for v in d2h_all], "h2d_gbs_per_replica": [round(v, 1) for v in h2d_all],
-                "plain_copy_d2h_gbs_per_replica": [round(v, 1) for v in plain_d2h],
-                "plain_copy_h2d_gbs_per_replica": [round(v, 1) for v in plain_h2d],
-                "note": "d2h_gbs / h2d_gbs are the slowest replica's; plain_copy_* is cudaMemcpyAsync of 1 GiB from all replicas at once"}
+                "d2h_gbs_per_replica": r1(d2h_all), "h2d_gbs_per_replica": r1(h2d_all),
+                "plain_copy_d2h_gbs_per_replica": r1(plain_d2h), "plain_copy_h2d_gbs_per_replica": r1(plain_h2d),
+                "duplex_d2h_gbs_per_replica": r1(dup_out), "duplex_h2d_gbs_per_replica": r1(dup_in),
+                "plain_copy_duplex_d2h_gbs_per_replica": r1(plain_dup_out), "plain_copy_duplex_h2d_gbs_per_replica": r1(plain_dup_in),
+                "sum_d2h_gbs": round(sum(d2h_all), 1), "sum_h2d_gbs": round(sum(h2d_all), 1),
+                "sum_plain_copy_d2h_gbs": round(sum(plain_d2h), 1), "sum_plain_copy_h2d_gbs": round(sum(plain_h2d), 1),
+                "note": "d2h_gbs / h2d_gbs are the slowest replica's, one direction at a time with a barrier between the phases; duplex_* is "
+                        "offload of one half of the tensors beside restore of the other half; plain_copy_* is cudaMemcpyAsync of 1 GiB "
+                        "from all replicas at once (duplex: both directions at once on two streams)"}
         link["d2h_frac_of_bound"] = round(link["d2h_gbs"] / PCIE_GEN5_X16_GBS, 3)
         link["h2d_frac_of_bound"] = round(link["h2d_gbs"] / PCIE_GEN5_X16_GBS, 3)
         link["d2h_frac_of_plain_copy"] = round(min(a / b for a, b in zip(d2h_all, plain_d2h)), 3)
         link["h2d_frac_of_plain_copy"] = round(min(a / b for a, b in zip(h2d_all, plain_h2d)), 3)
-        pool.clear()
-        e2e_value = world * 2 * step_bytes / (e2e_ms * 1e-3) * 1e-9
-        e2e = {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": int(h2d_b), "d2h_bytes_per_step": int(d2h_b),
-               "ms_per_step": round(e2e_ms, 3), "wall_ms_per_step": round(wall * 1e3, 3), "pinned_bytes": pool.host_bytes(),
-               "api": "ActivationOffloadPool.push / pull_into over flame_offload_pool_push / _pull_into"}
-        pool.close()
-
-    hbm_peak, peak_kind = measured_peaks()
-    line = {
-        "metric": METRIC, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": {"int8": "int8 codes + f32 scales", "fp8": "fp8-e4m3 codes + f32 scales", "none": "bf16"}[args.codec],
-        "data": "synthetic", "config": workload_config(args, world), "verified_against_oracle": bool(verified),
-        "gpu_launches": int(launches),
-    }
-    if value_ms is not None:
-        line["value"] = round(world * 2 * step_bytes / (value_ms * 1e-3) * 1e-9, 1)
-        line["ms_per_step"] = round(value_ms, 4)
-        if args.codec != "none":
-            alg = ALG_BYTES_PER_ELEM * step_elems
-            qa, da = alg / (quant_ms * 1e-3) * 1e-9, alg / (dequant_ms * 1e-3) * 1e-9
-            n_l = per_step_launches // 2
-            line["roofline"] = {"bound": "hbm", "kernel": "compress_b128_kernel", "achieved": round(qa, 1), "peak": hbm_peak, "unit": "GB/s",
-                                "frac": round(qa / hbm_peak, 4), "peak_kind": f"of {peak_kind}",
-                                "traffic": int(NCU_TRAFFIC_PER_ELEM["compress"] * step_elems / (per_step_launches // 2)) if args.codec == "int8" else None,
-                                "alg_bytes_per_launch": int(alg / n_l), "avg_launch_us": round(quant_ms * 1e3 / n_l, 2), "launches_per_step": n_l}
-            line["roofline_dequant"] = {"bound": "hbm", "kernel": "dequant_b128_kernel", "achieved": round(da, 1), "peak": hbm_peak, "unit": "GB/s",
-                                        "frac": round(da / hbm_peak, 4), "peak_kind": f"of {peak_kind}",
-                                        "traffic": int(NCU_TRAFFIC_PER_ELEM["dequant"] * step_elems / (per_step_launches // 2)) if args.codec == "int8" else None,
-                                        "alg_bytes_per_launch": int(alg / n_l), "avg_launch_us": round(dequant_ms * 1e3 / n_l, 2)}
-        line["clocks"] = clk_value.summary()
-    else:
-        line["value"] = e2e["value"]
-        line["ms_per_step"] = e2e["ms_per_step"]
-    if e2e is not None:
-        line["e2e"] = e2e
+        link["duplex_frac_of_plain_copy"] = round(min((a + b) / (c + d) for a, b, c, d in zip(dup_out, dup_in, plain_dup_out, plain_dup_in)), 3)
+        # what sysfs knows about each replica's link: replica r uses CUDA device r, and every device is visible to rank 0
+        link["pcie"] = [pcie_info(torch, i) for i in range(world)] if rank == 0 else None
         line["link"] = link
-        line["clocks_e2e"] = clk_e2e.summary()
-        if "clocks" not in line:
-            line["clocks"] = line["clocks_e2e"]
+    if args.only in ("all", "value", "e2e"):
+        pool.clear()
+        pool.close()
+        del pool
 
+    # ---- the codec kernels alone: HBM in, HBM out, one launch per checkpointed block -----------------------------------
+    if args.only in ("all", "codec") and args.codec != "none":
+        per_block = len(BLOCK_SAVED) if args.workload == "dit" else 4
+        groups = [list(range(b, min(b + per_block, len(tensors)))) for b in range(0, len(tensors), per_block)]
+        k_codec = max(1, min(args.steps, 10))
+        q_ms, d_ms, n_l, clk_codec = codec_leg(torch, lib, dev, tensors, dst, args.codec, k_codec, min(args.warmup, 3), groups, local)
+        comp, deq = roofline_entries(args.codec, q_ms, d_ms, step_elems, n_l)
+        comp["clocks"] = clk_codec
+        line["roofline"], line["roofline_dequant"] = comp, deq
+        line["device_resident"] = {"value": round(2 * step_bytes / ((q_ms + d_ms) * 1e-3) * 1e-9, 1), "unit": UNIT, "ms_per_step": round(q_ms + d_ms, 4),
+                                   "steps": k_codec, "gpu_launches": 2 * n_l * k_codec,
+                                   "note": "compress into packed device buffers and dequantise back; no host link, so not the metric"}
+        if "value" not in line:
+            line.update({"value": line["device_resident"]["value"], "ms_per_step": line["device_resident"]["ms_per_step"], "clocks": clk_codec})
+            launches += 2 * n_l * k_codec
+    line["verified_against_oracle"] = bool(verified)
+    line["gpu_launches"] = int(launches)
+
+    del tensors, dst
+    torch.cuda.empty_cache()
+    full = args.only == "all" and args.workload == "dit"
+    if rank == 0 and world == 1 and full and not args.no_fp8_mixed:
+        try:
+            line["fp8_mixed"] = run_fp8_mixed(torch, lib, dev, steps=max(3, min(args.steps, 10)), warmup=3)
+        except Exception as exc:
+            line["fp8_mixed"] = {"error": f"{type(exc).__name__}: {exc}"}
+        torch.cuda.empty_cache()
     if rank == 0 and world == 1 and not args.no_cpu:
         gbs, cores, sample, _ = cpu_leg(12.0, args.codec)
         line["cpu_baseline"] = {"value": round(gbs, 3), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
-    if rank == 0 and world == 1 and not args.no_dit and args.only == "all":
+    if full and not args.no_dit:
         try:
-            from flame_b200.dit_workload import measure_overhead
-            del tensors, dst
-            torch.cuda.empty_cache()
-            line["overhead"] = measure_overhead(dev, steps=max(3, min(args.steps, 5)), warmup=3)
+            if world == 1:
+                from flame_b200.dit_workload import measure_overhead
+                line["overhead"] = measure_overhead(dev, steps=max(3, min(args.steps, 5)), warmup=3)
+            else:
+                line["overhead"] = run_overhead_replicas(torch, dev, rank, world, barrier, gather, steps=3)
         except Exception as exc:  # the headline numbers above stand on their own
             line["overhead"] = {"error": f"{type(exc).__name__}: {exc}"}
+            if world > 1:
+                raise
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

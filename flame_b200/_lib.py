@@ -94,6 +94,7 @@ SIGNATURES = {
     "flame_d2d_async": (_i, [_vp, _vp, C.c_uint64, _vp]),
     "flame_bf16_to_fp8": (_i, [_vp, _vp, _f, _sz, _vp]),
     "flame_fp8_to_bf16": (_i, [_vp, _vp, _f, _sz, _vp]),
+    "flame_fused_dequant_transpose_bf16": (_i, [_vp, _vp, _f, _i, _i, _vp]),
     "flame_act_quant_int8_b128": (_i, [_vp, _vp, _vp, _sz, _u, _vp]),
     "flame_act_dequant_int8_b128": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "flame_act_quant_fp8_b128": (_i, [_vp, _vp, _vp, _sz, _u, _vp]),

@@ -99,7 +99,13 @@ class ActivationOffloadPool:
             raise CudaError(msg)
         self.compression = OffloadCompression(compression)
         self._meta: dict[int, tuple] = {}        # slot -> (shape, dtype)
-        self._keep_alive: dict[int, tuple] = {}  # slot -> (handle, tensor)
+        # Source tensors held until their device-to-host copy cannot be disturbed any more.  Keyed by a per-push
+        # sequence number, not by slot: a slot is free again as soon as a restore with a deferred wait has been
+        # issued from it, and a push that reuses it must not release (or be released with) the earlier tensor.
+        self._keep_alive: dict[int, tuple] = {}  # push sequence number -> (handle, tensor)
+        self._seq = 0
+        self._seq_of_slot: dict[int, int] = {}   # slot -> sequence number of the push that holds it now
+        self._awaiting: dict[int, int] = {}      # slot -> sequence number of the push whose deferred restore awaits wait_ready
 
     @staticmethod
     def host_bytes_needed(tensor_bytes, compression: OffloadCompression, chunk_bytes: int = 0) -> int:
@@ -145,10 +151,27 @@ class ActivationOffloadPool:
         """
         ka = self._keep_alive
         while ka:
-            slot = next(iter(ka))
-            if self._lib.flame_offload_pool_source_released(self._h, ka[slot][0]) == 0:
+            seq = next(iter(ka))
+            if self._lib.flame_offload_pool_source_released(self._h, ka[seq][0]) == 0:
                 break
-            del ka[slot]
+            del ka[seq]
+
+    def _hold_source(self, h, obj) -> None:
+        self._seq += 1
+        self._keep_alive[self._seq] = (h, obj)
+        self._seq_of_slot[h.slot] = self._seq
+
+    def _release_source(self, slot: int, deferred: bool) -> None:
+        """After a restore from `slot` was issued.  Not deferred: the current stream already waits for the restore,
+        which waited for the offload, so later work on that stream cannot disturb the source.  Deferred: the same
+        holds only from wait_ready on, which looks the push up under `_awaiting`."""
+        seq = self._seq_of_slot.pop(slot, None)
+        if seq is None:
+            return
+        if deferred:
+            self._awaiting[slot] = seq
+        else:
+            self._keep_alive.pop(seq, None)
 
     def push(self, tensor) -> OffloadHandle:
         """Asynchronously offload `tensor`; never blocks the host (activation_offload.rs:465-611)."""
@@ -165,8 +188,7 @@ class ActivationOffloadPool:
             raise_for_status(st, _lib.last_error())
         handle = OffloadHandle(h.slot, h.epoch)
         self._meta[h.slot] = (tuple(tensor.shape), tensor.dtype)
-        self._keep_alive.pop(h.slot, None)          # re-inserted at the young end
-        self._keep_alive[h.slot] = (h, tensor.detach())
+        self._hold_source(h, tensor.detach())
         return handle
 
     def push_packed(self, codes, scales, shape, dtype=None) -> OffloadHandle:
@@ -187,8 +209,7 @@ class ActivationOffloadPool:
         if st != 0:
             raise_for_status(st, _lib.last_error())
         self._meta[h.slot] = (tuple(shape), dtype or torch.bfloat16)
-        self._keep_alive.pop(h.slot, None)
-        self._keep_alive[h.slot] = (h, _Prepacked(codes, scales, numel, tuple(shape)))
+        self._hold_source(h, _Prepacked(codes, scales, numel, tuple(shape)))
         return OffloadHandle(h.slot, h.epoch)
 
     def pull_into(self, handle: OffloadHandle, dst, defer_wait: bool = False, keep: bool = False) -> None:
@@ -204,8 +225,7 @@ class ActivationOffloadPool:
             raise_for_status(st, _lib.last_error())
         if keep:
             return
-        if not defer_wait:
-            self._keep_alive.pop(handle.slot, None)
+        self._release_source(handle.slot, defer_wait)
         self._meta.pop(handle.slot, None)
 
     def pull_packed(self, handle: OffloadHandle, codes, scales, defer_wait: bool = False) -> None:
@@ -221,8 +241,7 @@ class ActivationOffloadPool:
                                                      1 if defer_wait else 0)
         if st != 0:
             raise_for_status(st, _lib.last_error())
-        if not defer_wait:
-            self._keep_alive.pop(handle.slot, None)
+        self._release_source(handle.slot, defer_wait)
         self._meta.pop(handle.slot, None)
 
     def prefetch(self, handle: OffloadHandle, dst) -> None:
@@ -250,7 +269,7 @@ class ActivationOffloadPool:
         if r == 0:
             return None
         self._meta.pop(handle.slot, None)
-        src = self._keep_alive.pop(handle.slot)[1]
+        src = self._keep_alive.pop(self._seq_of_slot.pop(handle.slot))[1]
         if isinstance(src, _Prepacked):
             # only the compressed form was kept on the device: dequantise it here, without a trip over the link
             out = self._torch.empty(src.numel, dtype=self._torch.bfloat16, device=self.device)
@@ -278,6 +297,7 @@ class ActivationOffloadPool:
         """Frees the slot of `handle` without restoring it (an abandoned block, src/autograd.rs:1742-1769)."""
         raise_for_status(self._lib.flame_offload_pool_discard(self._h, handle._c()), _lib.last_error())
         self._meta.pop(handle.slot, None)
+        self._seq_of_slot.pop(handle.slot, None)
         # the source stays referenced until its device-to-host copy, already queued, has finished
         self._sweep_keep_alive()
 
@@ -286,13 +306,17 @@ class ActivationOffloadPool:
         st = self._lib.flame_offload_pool_wait_ready(self._h, slot, self._stream())
         if st != 0:
             raise_for_status(st, _lib.last_error())
-        self._keep_alive.pop(slot, None)
+        seq = self._awaiting.pop(slot, None)
+        if seq is not None:
+            self._keep_alive.pop(seq, None)
 
     def clear(self) -> None:
         """Invalidate every handle, free every slot; does not synchronise (activation_offload.rs:742-760)."""
         raise_for_status(self._lib.flame_offload_pool_clear(self._h), _lib.last_error())
         self._meta.clear()
         self._keep_alive.clear()
+        self._seq_of_slot.clear()
+        self._awaiting.clear()
 
     # -- extras ------------------------------------------------------------------------------
     def synchronize(self, timeout_s: float = 60.0) -> None:

@@ -69,23 +69,56 @@ class SdpaCtx:
     dropout_seed: Optional[int] = None
     _handles: dict = field(default_factory=dict, repr=False)
 
-    _OFFLOADABLE = ("q", "k", "v", "probs")
+    _OFFLOADABLE = ("q", "k", "v", "probs", "lse")
 
-    def offload(self, pool) -> int:
-        """Pushes the BF16 saved tensors to `pool` and drops the device references; returns bytes offloaded."""
+    @classmethod
+    def from_forward(cls, q, k, v, *, scale: float, save: SdpaSave, causal: bool = False, attn_mask=None,
+                     probs=None, lse=None, chunk_cfg=None, dropout_p: float = 0.0, dropout_seed=None) -> "SdpaCtx":
+        """The record ``sdpa_forward`` leaves for backward (sdpa.rs:260-274): q, k, v always; the probabilities
+        [B,H,Q,K] in BF16 only under ``SaveProbs``; the log-sum-exp [B,H,Q,1] in FP32 only under ``SaveLSE``;
+        neither under ``Recompute``.  What does not belong to the mode is refused, so that a context never holds
+        more than its mode says it saves."""
         import torch
 
+        b, h, ql, _ = q.shape
+        kl = k.shape[2]
+        if save == SdpaSave.SAVE_PROBS:
+            if probs is None or lse is not None or tuple(probs.shape) != (b, h, ql, kl) or probs.dtype != torch.bfloat16:
+                raise ValueError("SaveProbs keeps the probabilities [B,H,Q,K] in BF16 and no log-sum-exp")
+        elif save == SdpaSave.SAVE_LSE:
+            if lse is None or probs is not None or tuple(lse.shape) != (b, h, ql, 1) or lse.dtype != torch.float32:
+                raise ValueError("SaveLSE keeps the log-sum-exp [B,H,Q,1] in FP32 and no probabilities")
+        elif probs is not None or lse is not None:
+            raise ValueError("Recompute keeps neither probabilities nor log-sum-exp")
+        return cls(q=q, k=k, v=v, attn_mask=attn_mask, scale=float(scale), save=save, causal=causal, lse=lse, probs=probs,
+                   shapes=(b, h, ql, kl), chunk_cfg=chunk_cfg, dropout_p=dropout_p, dropout_seed=dropout_seed)
+
+    def saved_bytes(self) -> int:
+        """Bytes the context keeps on the device right now (what SdpaStats.bytes_saved counts)."""
+        return sum(t.numel() * t.element_size() for t in (getattr(self, n) for n in self._OFFLOADABLE) if t is not None)
+
+    def offload(self, pool) -> int:
+        """Pushes the saved tensors to `pool` and drops the device references; returns the bytes offloaded.
+
+        BF16 tensors go through whatever compression the pool has; the FP32 log-sum-exp only through an
+        uncompressed pool (compression is defined for BF16 only, src/activation_offload.rs:537-542) and stays
+        resident otherwise.  A tensor that is not contiguous stays resident too."""
+        import torch
+
+        compressed = int(getattr(pool, "compression", 0)) != 0
         total = 0
         for name in self._OFFLOADABLE:
             t = getattr(self, name)
-            if t is not None and t.dtype == torch.bfloat16 and t.is_contiguous():
+            if t is None or not t.is_contiguous():
+                continue
+            if t.dtype == torch.bfloat16 or (t.dtype == torch.float32 and not compressed):
                 self._handles[name] = pool.push(t)
                 setattr(self, name, None)
-                total += t.numel() * 2
+                total += t.numel() * t.element_size()
         return total
 
     def restore(self, pool) -> None:
-        """Pulls back, in reverse push order, what `offload` pushed."""
+        """Pulls back, in reverse push order (the pool's slot stack is last in, first out), what `offload` pushed."""
         for name in reversed(list(self._handles)):
             setattr(self, name, pool.pull(self._handles.pop(name)))
 

@@ -8,21 +8,31 @@ alternate, ``prefetch_block(i + 1)`` runs while block ``i`` computes, ``await_bl
 Here the host copy is a set of slots in an :class:`ActivationOffloadPool` (one per block and dtype) that are
 restored with ``keep=True``, so the pinned copy stays and the same handle is restored again next step.  With a
 compressed pool the host copy is int8 / FP8 codes with one scale per 128 elements and the restore dequantises
-into the slot (the FP8 weight path of src/ops/fused_inference.rs:86-140 without its transpose).
+into the slot.
+
+Weights that already are FP8 E4M3 bytes with one scale per tensor (the checkpoints the reference's inference path
+loads, src/ops/fused_inference.rs:86-175) stream as they are through an uncompressed pool, one byte per element over
+the link, and are expanded on the device when the block is awaited: ``flame_fp8_to_bf16`` for a weight used in its
+stored [M, N] orientation, ``flame_fused_dequant_transpose_bf16`` for one the GEMM wants as [N, M]
+(src/cuda/fused_dequant_transpose.cu), into BF16 buffers that belong to the device slot.
 """
 from __future__ import annotations
 
 from typing import Dict, List, Mapping, Optional, Sequence
 
+from . import _lib
 from .activation_offload import ActivationOffloadPool, OffloadCompression
-from .errors import InvalidInput, InvalidOperation, Unsupported
+from .errors import CudaError, InvalidInput, InvalidOperation, Unsupported
 
 _ALIGN = 256
 
 
 class BlockOffloader:
     def __init__(self, device, blocks: Sequence[Mapping[str, "object"]], compression: OffloadCompression = OffloadCompression.NONE,
-                 chunk_bytes: int = 16 << 20, gpu_slots: int = 2, h2d_piece_bytes: int = 0):
+                 chunk_bytes: int = 16 << 20, gpu_slots: int = 2, h2d_piece_bytes: int = 0,
+                 fp8_weights: Optional[Mapping[str, tuple]] = None):
+        """``fp8_weights``: name -> (scale, transpose) for the uint8 tensors of the blocks that hold FP8 E4M3 codes
+        of a 2-D weight [M, N]; ``await_block`` hands them out as BF16, [N, M] when ``transpose`` is true."""
         import torch
 
         if not blocks:
@@ -36,16 +46,24 @@ class BlockOffloader:
         # being zero, changes no scale).  Each dtype group crosses the link as one pool slot.
         self._layout: List[List[tuple]] = []          # per block: (name, shape, dtype, offset, nbytes)
         self._groups: List[List[tuple]] = []          # per block: (dtype, offset, nbytes) of each dtype group
+        self._fp8 = dict(fp8_weights or {})
+        self._expand_bytes = 0                        # BF16 bytes the FP8 weights of the largest block expand to
         for blk in blocks:
             rows, groups, off = [], [], 0
             for name, t in blk.items():
+                if t.dtype == torch.uint8:
+                    if name not in self._fp8 or t.dim() != 2:
+                        raise Unsupported(f"BlockOffloader: {name} is uint8; FP8 weights must be 2-D and named in fp8_weights")
+                    if compression != OffloadCompression.NONE:
+                        raise Unsupported("BlockOffloader: FP8 weight bytes stream through an uncompressed pool")
+                    continue
                 if t.dtype not in (torch.bfloat16, torch.float32):
-                    raise Unsupported(f"BlockOffloader: {name} has dtype {t.dtype} (BF16/F32 only)")
+                    raise Unsupported(f"BlockOffloader: {name} has dtype {t.dtype} (BF16/F32, or uint8 FP8 codes)")
                 if compression != OffloadCompression.NONE and t.dtype != torch.bfloat16:
                     raise Unsupported(f"BlockOffloader: compressed streaming only supports BF16 weights ({name} is {t.dtype})")
                 if t.numel() == 0:
                     raise InvalidInput(f"BlockOffloader: {name} is empty")
-            for dtype in (torch.bfloat16, torch.float32):
+            for dtype in (torch.bfloat16, torch.float32, torch.uint8):
                 g0 = off
                 for name, t in blk.items():
                     if t.dtype != dtype:
@@ -54,7 +72,9 @@ class BlockOffloader:
                     rows.append((name, tuple(t.shape), dtype, off, nbytes))
                     off = (off + nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
                 if off > g0:
-                    groups.append((dtype, g0, off - g0))
+                    # FP8 bytes cross the link as they are: the uncompressed pool copies bytes, whatever the tag
+                    groups.append((torch.bfloat16 if dtype == torch.uint8 else dtype, g0, off - g0))
+            self._expand_bytes = max(self._expand_bytes, sum((2 * r[4] + _ALIGN - 1) // _ALIGN * _ALIGN for r in rows if r[2] == torch.uint8))
             self._layout.append(rows)
             self._groups.append(groups)
         self._slot_bytes = max(g[-1][1] + g[-1][2] for g in self._groups)
@@ -75,6 +95,7 @@ class BlockOffloader:
         self._pool.synchronize(600.0)
         self._pool.release_finished_sources()
         self._n_slots = gpu_slots
+        self._expanded: List[Optional[object]] = [None] * gpu_slots   # per device slot: BF16 forms of the block's FP8 weights
         self._bufs: List[Optional[object]] = [None] * gpu_slots
         self._resident: List[Optional[int]] = [None] * gpu_slots    # block index held (or being loaded) per device slot
         self._pending: List[bool] = [False] * gpu_slots              # its host-to-device copies have not been awaited yet
@@ -88,7 +109,7 @@ class BlockOffloader:
         return self._pool.host_bytes()
 
     def device_bytes(self) -> int:
-        return self._slot_bytes * self._n_slots
+        return (self._slot_bytes + self._expand_bytes) * self._n_slots
 
     def stats(self) -> dict:
         return self._pool.stats()
@@ -144,7 +165,27 @@ class BlockOffloader:
             self._pending[slot] = False
         self._active = slot
         buf = self._bufs[slot]
-        return {name: buf[off:off + nbytes].view(dtype).view(shape) for name, shape, dtype, off, nbytes in self._layout[idx]}
+        torch = self._torch
+        out, eoff = {}, 0
+        for name, shape, dtype, off, nbytes in self._layout[idx]:
+            if dtype != torch.uint8:
+                out[name] = buf[off:off + nbytes].view(dtype).view(shape)
+                continue
+            # FP8 codes [M, N] -> BF16 on the current stream, which already waits for the block's copies
+            if self._expanded[slot] is None:
+                self._expanded[slot] = torch.empty(self._expand_bytes, dtype=torch.uint8, device=self.device)
+            scale, transpose = self._fp8[name]
+            m, n = shape
+            dst = self._expanded[slot][eoff:eoff + 2 * nbytes].view(torch.bfloat16)
+            eoff += (2 * nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            lib = _lib.lib()
+            rc = (lib.flame_fused_dequant_transpose_bf16(buf.data_ptr() + off, dst.data_ptr(), float(scale), m, n, stream) if transpose
+                  else lib.flame_fp8_to_bf16(buf.data_ptr() + off, dst.data_ptr(), float(scale), m * n, stream))
+            if rc != 0:
+                raise CudaError(f"BlockOffloader: FP8 weight expansion of {name} failed ({rc}): {_lib.last_error()}")
+            out[name] = dst.view(n, m) if transpose else dst.view(m, n)
+        return out
 
     def ensure_block(self, idx: int) -> Dict[str, "object"]:
         """prefetch_block + await_block."""
@@ -160,6 +201,7 @@ class BlockOffloader:
                 for h in self._handles[idx]:
                     self._pool.wait_ready(h.slot)
         self._bufs = [None] * self._n_slots
+        self._expanded = [None] * self._n_slots
         self._resident = [None] * self._n_slots
         self._pending = [False] * self._n_slots
         self._active = None

@@ -158,6 +158,26 @@ class _Entry:
                 pass
 
 
+def _manager():
+    """The legacy side channel (gradient_checkpointing.CHECKPOINT_MANAGER), or None while it holds no entry.
+
+    The reference consults its manager for every saved tensor behind one relaxed atomic load
+    (src/autograd.rs:894-907 when an op is recorded, 1867-1880 when backward fetches a saved tensor); the flag is
+    False until an entry exists, so a step that never uses the manager pays one attribute read per saved tensor."""
+    from . import gradient_checkpointing as gc_mod   # imported late: that module imports this one
+
+    return gc_mod if gc_mod.CHECKPOINT_HAS_ENTRIES else None
+
+
+class _Managed:
+    """A saved tensor that was also handed to the legacy manager when it was recorded."""
+
+    __slots__ = ("tid", "inner")
+
+    def __init__(self, tid, inner):
+        self.tid, self.inner = tid, inner
+
+
 class _View:
     """A saved tensor that is a reshaped and/or permuted view of an offloaded entry's flat memory."""
 
@@ -189,6 +209,18 @@ class _Block:
 
     # -- forward -----------------------------------------------------------------------------
     def pack(self, t: torch.Tensor):
+        inner = self._pack(t)
+        mgr = _manager()
+        if mgr is None:
+            return inner
+        # src/autograd.rs:894-907: with entries present, every saved tensor of a recorded op is offered to the
+        # manager (which keeps it under its CPUOffload policy and ignores it otherwise); the tape keeps its own
+        tid = mgr.tensor_id(t)
+        with mgr.CHECKPOINT_MANAGER_LOCK:
+            mgr.CHECKPOINT_MANAGER.checkpoint_saved_tensor(tid, t)
+        return _Managed(tid, inner)
+
+    def _pack(self, t: torch.Tensor):
         # Only BF16 activations that take part in the gradient are offloaded; weights, non-BF16
         # tensors and small tensors stay resident (autograd.rs:1721-1739).
         if self.failed or not offloadable(t, self.min_bytes):
@@ -266,6 +298,12 @@ class _Block:
                 self.pool.discard(h)
             except OffloadError:
                 pass
+        # the entries must not discard these handles a second time when they die: a (slot, epoch) pair is not
+        # unique per push, and by then the slot may hold another tensor
+        for ref in self.entries:
+            e = ref()
+            if e is not None:
+                e.handle = None
         self.entries.clear()
 
     # -- backward ------------------------------------------------------------------------------
@@ -314,6 +352,16 @@ class _Block:
             e.restored, e.waited, e.packed = d, True, None
 
     def unpack(self, obj):
+        if isinstance(obj, _Managed):
+            # src/autograd.rs:1867-1892: the manager's copy wins when it has one, and whatever comes back is made
+            # contiguous; otherwise the tape's own saved tensor is used
+            mgr = _manager()
+            if mgr is not None:
+                with mgr.CHECKPOINT_MANAGER_LOCK:
+                    r = mgr.CHECKPOINT_MANAGER.fetch_saved(obj.tid)
+                if r is not None:
+                    return r if r.is_contiguous() else r.contiguous()
+            return self.unpack(obj.inner)
         if isinstance(obj, _View):
             return self.unpack(obj.entry).view(obj.shape).permute(obj.inverse)
         if not isinstance(obj, _Entry):

@@ -111,6 +111,15 @@ int flame_fp8_to_bf16(const void* input, void* output, float scale, size_t n, vo
   return (int)launch_fp8_to_bf16(input, output, scale, n, (cudaStream_t)stream, 0);
 }
 
+// ---- FP8 weights with the transpose built in (src/cuda/fused_dequant_transpose.cu:104-126) ----
+
+int flame_fused_dequant_transpose_bf16(const void* input, void* output, float scale, int M, int N, void* stream) {
+  if (M == 0 || N == 0) return 0;
+  if (M < 0 || N < 0) return (int)cudaErrorInvalidValue;
+  if (fault_fires(FLAME_OFFLOAD_FAULT_KERNEL)) return (int)cudaErrorLaunchFailure;
+  return (int)launch_fp8_dequant_transpose(input, output, scale, M, N, (cudaStream_t)stream, 0);
+}
+
 // ---- per-128-block codecs --------------------------------------------------------
 
 static int quant_entry(int codec, const void* in, void* codes, void* scales, size_t n, unsigned flags, void* stream) {

@@ -58,6 +58,8 @@ cudaError_t launch_rmsnorm_quant(int codec, unsigned flags, const void* x, const
                                  void* rstd_out, size_t rows, size_t cols, float eps, cudaStream_t stream);
 cudaError_t launch_swiglu_quant(int codec, unsigned flags, const void* gate_up, void* h, void* codes, void* scales,
                                 size_t rows, size_t hidden, cudaStream_t stream, int max_ctas);
+// FP8 weights [M, N] -> BF16 [N, M] with the decoder of the reference's fused_dequant_transpose.cu (weight_kernels.cu).
+cudaError_t launch_fp8_dequant_transpose(const void* in_fp8, void* out_bf16, float scale, int M, int N, cudaStream_t stream, int max_ctas);
 int set_max_ctas(int v);
 
 // Inspection hooks (tests): what the calling thread's last compress / dequantise launch chose, and a fresh

@@ -218,10 +218,21 @@ DEFERRED_D2H_PIECE_BYTES = 1 << 20
 ISSUE_OFF_THREAD = 1 << 40   # a deferred pool with this in-flight budget never queues: it only moves the issuing off the training thread
 
 
+# The capped plan's estimate of what a busy copy engine costs the compute beside it, per unit of busy time: a step
+# with 12 of 20 blocks offloaded in int8 measured +4.2 to +5.3 ms for 75 ms of copy-engine time on a B200.
+CAPPED_PLAN_INTERFERENCE = 0.065
+
+
 def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
-                     arms=("offload_int8", "deferred", "offload_bf16", "recompute", "fused"), custom=(),
-                     resident_budget_blocks: int = 8) -> dict:
-    """Step time of each arm relative to resident activations.  Returns a JSON-ready dict."""
+                     arms=("offload_int8", "capped", "deferred", "offload_bf16", "recompute", "fused"), custom=(),
+                     resident_budget_blocks: int = 8, sync=None, cap_pct: float = 4.0) -> dict:
+    """Step time of each arm relative to resident activations.  Returns a JSON-ready dict.
+
+    ``sync``: called before the link probe and before every timed arm.  With several replicas it is a barrier, so
+    that all of them probe, and later copy, at the same moment and see the link as it is when it is shared.
+    Arm "capped": the plan that keeps as little resident as the probed link allows within ``cap_pct`` per cent of
+    estimated extra step time (flame_offload_policy_plan_blocks with overhead_cap_ms)."""
+    sync = sync or (lambda: None)
     torch.manual_seed(0)
     dev = torch.device(device)
     model = DiT(blocks).to(dev, torch.bfloat16)
@@ -229,12 +240,14 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
     x = torch.randn(1, TOKENS, HIDDEN, device=dev, dtype=torch.bfloat16)
     cos, sin = rope_tables(dev)
     fwd_ms, bwd_ms, saved_bytes = _block_times(model, x, cos, sin)
+    sync()
     link = probe(256 << 20, 3)
     out = {"model": f"DiT {blocks} blocks, hidden {HIDDEN}, {HEADS}x{HEAD_DIM} heads, SwiGLU {MLP_HIDDEN}, {TOKENS} tokens, batch 1, bf16, fused AdamW",
            "block_fwd_ms": round(fwd_ms, 3), "block_bwd_ms": round(bwd_ms, 3), "saved_bytes_per_block": int(saved_bytes),
            "probe": {"d2h_gbs": round(link.d2h_gbs, 2), "h2d_gbs": round(link.h2d_gbs, 2), "hbm_copy_gbs": round(link.hbm_copy_gbs, 1)}}
 
     model.decisions = None
+    sync()
     base_ms, base_mem, base_held = _time_steps(model, opt, x, cos, sin, steps, warmup)
     out["resident"] = {"ms_per_step": round(base_ms, 3), "peak_mem_gb": round(base_mem / 1e9, 2),
                        "held_after_forward_gb": round(base_held / 1e9, 2)}
@@ -251,6 +264,7 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
             ckpt.set_activation_offload_pool(pool)
         model.decisions = decisions
         try:
+            sync()
             ms, mem, held = _time_steps(model, opt, x, cos, sin, steps, warmup)
             res = {"ms_per_step": round(ms, 3), "overhead_pct": round(100.0 * (ms - base) / base, 2), "peak_mem_gb": round(mem / 1e9, 2),
                    "held_after_forward_gb": round(held / 1e9, 2),
@@ -291,6 +305,17 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
             curve.append({"offloaded_blocks": k, "overhead_pct": r["overhead_pct"], "ms_per_step": r["ms_per_step"],
                           "held_after_forward_gb": r["held_after_forward_gb"], "offloaded_gb_per_step": r.get("offloaded_gb_per_step")})
         out["offload_int8_curve"] = curve
+    if "capped" in arms:
+        cap_ms = cap_pct / 100.0 * base_ms
+        p = plan_blocks(blk, d2h_gbs=link.d2h_gbs, h2d_gbs=link.h2d_gbs, offload=Decision.OFFLOAD_INT8,
+                        interference=CAPPED_PLAN_INTERFERENCE, overhead_cap_ms=cap_ms)
+        r = run_arm("offload_int8_capped", p.decisions, OffloadCompression.INT8_B128 if Decision.OFFLOAD_INT8 in p.decisions else None,
+                    deferred_bytes=ISSUE_OFF_THREAD, d2h_piece=DEFERRED_D2H_PIECE_BYTES)
+        r["plan_est_ms"] = {"stall": round(p.est_stall_ms, 2), "recompute": round(p.est_recompute_ms, 2),
+                            "interference": round(p.est_interference_ms, 2), "cap": round(cap_ms, 2)}
+        r["plan_resident_gb"] = round(p.resident_bytes / 1e9, 3)
+        out["offload_int8_capped"] = r
+        out["cap_pct"], out["interference"] = cap_pct, CAPPED_PLAN_INTERFERENCE
     if "deferred" in arms:
         # Every block handed to the pool; a deferred pool sends out what the link carries beside the forward pass
         # and backward uses the rest where it is.  No plan, no budget: the link decides.
@@ -343,6 +368,7 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
                                    "rest is used where it is (tensors_used_in_place_per_step)"}
     # the baseline again, last: run-to-run drift of the step time shows up as the difference to the first measurement
     model.decisions = None
+    sync()
     again_ms, _, _ = _time_steps(model, opt, x, cos, sin, steps, 1)
     out["resident"]["ms_per_step_rerun"] = round(again_ms, 3)
     mean_base = 0.5 * (base_ms + again_ms)

@@ -1,7 +1,8 @@
 """CheckpointManager and friends: mirror of src/gradient_checkpointing.rs:19-358.
 
 The reference's manager is a side channel consulted per saved tensor
-(src/autograd.rs:894-907, 1867-1880).  Its ``CPUOffload`` policy is a device-side
+(src/autograd.rs:894-907, 1867-1880); ``checkpoint_offload``'s save and restore
+hooks consult this one the same way, behind ``CHECKPOINT_HAS_ENTRIES``.  Its ``CPUOffload`` policy is a device-side
 clone placeholder (gradient_checkpointing.rs:92-97); here it really offloads
 through the installed ``ActivationOffloadPool`` when there is one, and keeps the
 clone behaviour when there is not.  ``Adaptive`` keeps its two fields and its
@@ -17,6 +18,14 @@ from typing import Callable, Optional
 
 from . import checkpoint as _ckpt
 from .errors import InvalidOperation
+
+
+def tensor_id(t):
+    """Identity of a tensor for the manager's registry (the reference's TensorId): the memory it views and how.
+
+    A saved-tensor hook does not always receive the Python object the caller holds (an op's saved output arrives
+    as a detached alias), so the key is what both objects share."""
+    return (t.untyped_storage().data_ptr(), t.storage_offset(), tuple(t.shape), tuple(t.stride()), t.dtype)
 
 
 class CheckpointPolicyKind(enum.Enum):
@@ -174,7 +183,7 @@ class CheckpointManager:
 
 
 CHECKPOINT_MANAGER = CheckpointManager()
-CHECKPOINT_MANAGER_LOCK = threading.Lock()
+CHECKPOINT_MANAGER_LOCK = threading.RLock()   # re-entrant: a CheckpointedBlock holds it while its forward runs the save hooks
 CHECKPOINT_HAS_ENTRIES = False
 
 
@@ -190,8 +199,8 @@ class CheckpointedBlock:
             outputs = self.forward_fn(inputs)
             for i, out in enumerate(outputs):
                 if i < len(outputs) - 1:  # the final output is not checkpointed
-                    CHECKPOINT_MANAGER.register_tensor(id(out), out)
-                    CHECKPOINT_MANAGER.checkpoint_tensor(id(out), None)
+                    CHECKPOINT_MANAGER.register_tensor(tensor_id(out), out)
+                    CHECKPOINT_MANAGER.checkpoint_tensor(tensor_id(out), None)
             return outputs
 
 

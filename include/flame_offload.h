@@ -70,6 +70,14 @@ FlameOffloadStatus flame_d2d_async(void* dst_device, const void* src_device, uin
 int flame_bf16_to_fp8(const void* input_bf16, void* output_u8, float inv_scale, size_t n_elements, void* stream);
 int flame_fp8_to_bf16(const void* input_u8, void* output_bf16, float scale, size_t n_elements, void* stream);
 
+/* FP8 E4M3 weights with the transpose built in: signature kept.
+ * Replaces src/cuda/fused_dequant_transpose.cu:104-126 (declared src/cuda/ffi.rs, called from
+ * src/ops/fused_inference.rs:140-175): input [M, N] row-major FP8 bytes, output [N, M] row-major BF16,
+ * out[n][m] = bf16_rn(dec(in[m][n]) * scale) with that file's decoder (sub-normals, exponent 15 with a zero
+ * mantissa = 256, exponent 15 with any other mantissa = NaN), bit for bit under IEEE float semantics.
+ * M == 0 or N == 0 returns 0 at once.  M % 8 == 0, N % 4 == 0 and 16-byte aligned pointers take the fast kernel. */
+int flame_fused_dequant_transpose_bf16(const void* input_fp8, void* output_bf16, float scale, int M, int N, void* stream);
+
 /* ------------------------------------------------------------------------
  * 3. Per-128-element-block codecs (new; they take the place of the two calls
  *    above inside push/pull, src/activation_offload.rs:543-579 and 678-700).

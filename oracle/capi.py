@@ -55,6 +55,8 @@ def load() -> C.CDLL:
             "oracle_roundtrip_mt": (i, [vp, vp, vp, sz, i, u, i, i]),
             "oracle_fp8_encode_sweep": (C.c_uint64, [vp, C.c_uint64, C.c_uint64, C.c_uint64, vp]),
             "oracle_fp8_encode_many": (None, [vp, vp, sz, i]),
+            "oracle_fp8_weight_decode": (f, [C.c_uint8]),
+            "oracle_fp8_dequant_transpose": (None, [vp, vp, f, i, i]),
         }
         for name, (res, args) in sigs.items():
             fn = getattr(lib, name)
@@ -122,6 +124,8 @@ def load_ref_cuda():
         lib.flame_cuda_alloc_pinned_host.restype, lib.flame_cuda_alloc_pinned_host.argtypes = vp, [sz, u]
         lib.flame_cuda_free_pinned_host.restype, lib.flame_cuda_free_pinned_host.argtypes = i, [vp]
         lib.flame_cuda_memcpy_async.restype, lib.flame_cuda_memcpy_async.argtypes = i, [vp, vp, sz, i, vp]
+        if hasattr(lib, "flame_fused_dequant_transpose_bf16"):   # src/cuda/fused_dequant_transpose.cu, built into the same library
+            lib.flame_fused_dequant_transpose_bf16.restype, lib.flame_fused_dequant_transpose_bf16.argtypes = i, [vp, vp, f, i, i, vp]
         if hasattr(lib, "flame_fused_rms_norm_bf16"):      # src/cuda/fused_rms_norm.cu, built into the same library
             lib.flame_fused_rms_norm_bf16.restype, lib.flame_fused_rms_norm_bf16.argtypes = i, [vp, vp, vp, i, i, f, vp]
         _REF_CUDA = lib
@@ -205,6 +209,15 @@ def fp8_to_bf16(codes, scale: float):
     out = np.empty(codes.size, np.uint16)
     load().oracle_fp8_to_bf16(_p(codes), _p(out), np.float32(scale), codes.size)
     return out
+
+
+def fp8_dequant_transpose(codes, scale: float, m: int, n: int):
+    """[m, n] FP8 weight codes -> [n, m] BF16 bits with the decoder of src/cuda/fused_dequant_transpose.cu."""
+    codes = np.ascontiguousarray(codes, np.uint8).reshape(-1)
+    assert codes.size == m * n
+    out = np.empty(m * n, np.uint16)
+    load().oracle_fp8_dequant_transpose(_p(codes), _p(out), np.float32(scale), m, n)
+    return out.reshape(n, m)
 
 
 def packed_bytes(n: int) -> int:

@@ -28,6 +28,10 @@
  *     per block of 128 consecutive elements with a +-127 clamp.
  *   - the per-128-block FP8 variant: scale = absmax/448, inv = 1/scale,
  *     code = enc(x * inv), value = bf16(dec(code) * scale).
+ *   - the FP8 weight decoder with transpose of
+ *     src/cuda/fused_dequant_transpose.cu:37-72 (a different reading of E4M3
+ *     from the activation decoder: exponent 15 with a non-zero mantissa is
+ *     NaN there), [M,N] codes -> [N,M] BF16.
  *
  * Parity status.  The FP8 encoder/decoder restatement is checked against the
  * reference's own encoder body compiled from its source (oracle/_ref, built by
@@ -260,6 +264,29 @@ void oracle_dequant_fp8_b128(const uint8_t* codes, const float* scales, uint16_t
 
 /* ---- packed host layout ---------------------------------------------------
  * codes[n] | zero padding to a 256-byte boundary | scales[ceil(n/128)] fp32 LE */
+
+/* src/cuda/fused_dequant_transpose.cu:37-72: sign, 4-bit exponent, 3-bit mantissa; zero; sub-normal
+ * (mant/8) * 2^-6; exponent 15 with mantissa != 0 -> quiet NaN; exponent 15 with mantissa 0 -> 2^8;
+ * otherwise (1 + mant/8) * 2^(exp-7); the sign applied after; then val *= scale and
+ * __float2bfloat16 (round to nearest even, NaN -> 0x7FFF). */
+float oracle_fp8_weight_decode(uint8_t bits) {
+  const int sign = (bits >> 7) & 1, ex = (bits >> 3) & 0xF, mant = bits & 0x7;
+  float val;
+  if (ex == 0 && mant == 0) val = 0.0f;
+  else if (ex == 0) val = ldexpf((float)mant / 8.0f, -6);
+  else if (ex == 15 && mant != 0) val = bits_to_f32(0x7FC00000u);
+  else if (ex == 15) val = ldexpf(1.0f, 15 - 7);
+  else val = ldexpf(1.0f + (float)mant / 8.0f, ex - 7);
+  return sign ? -val : val;
+}
+
+void oracle_fp8_dequant_transpose(const uint8_t* in, uint16_t* out, float scale, int M, int N) {
+  for (int m = 0; m < M; ++m)
+    for (int n = 0; n < N; ++n) {
+      const float v = oracle_fp8_weight_decode(in[(size_t)m * N + n]) * scale;
+      out[(size_t)n * M + m] = (v != v) ? (uint16_t)0x7FFF : oracle_f32_to_bf16(v);
+    }
+}
 
 size_t oracle_packed_scales_offset(size_t n) { return (n + 255u) & ~(size_t)255u; }
 size_t oracle_packed_bytes(size_t n) {

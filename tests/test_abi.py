@@ -41,7 +41,7 @@ def test_struct_sizes_match_the_header():
     assert C.sizeof(_lib.Stats) == 14 * 8
     assert C.sizeof(_lib.SlotInfo) == 40
     assert C.sizeof(_lib.PolicyTensor) == 24
-    assert C.sizeof(_lib.PolicyInput) == 64
+    assert C.sizeof(_lib.PolicyInput) == 72
 
 
 def test_packed_size_helpers():

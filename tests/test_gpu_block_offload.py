@@ -116,3 +116,41 @@ def test_block_offloader_argument_errors(cuda_device):
     with pytest.raises(InvalidInput):
         off.await_block(5)
     off.close()
+
+
+def test_fp8_weight_bytes_stream_as_they_are_and_expand_on_the_device(cuda_device):
+    """FP8 E4M3 weights with one scale per tensor (src/ops/fused_inference.rs:86-175): one byte per element over the
+    link, BF16 after await_block, transposed where the caller asks for it."""
+    rng = np.random.default_rng(4)
+    d = 128
+    scale_qkv, scale_out = 0.0123, 0.5
+    blocks = []
+    for b in range(3):
+        codes_qkv = rng.integers(0, 0x78, size=(3 * d, d), dtype=np.uint8) | (rng.integers(0, 2, size=(3 * d, d), dtype=np.uint8) << 7)
+        codes_out = rng.integers(0, 256, size=(d, d + 8 * b), dtype=np.uint8)
+        blocks.append({"attn.qkv.weight": torch.from_numpy(codes_qkv), "attn.out.weight": torch.from_numpy(codes_out),
+                       "norm.weight": torch.ones(d, dtype=torch.bfloat16) * (b + 1)})
+    with pytest.raises(Unsupported):
+        BlockOffloader(cuda_device, blocks, OffloadCompression.NONE)                      # uint8 without a description
+    with pytest.raises(Unsupported):
+        BlockOffloader(cuda_device, blocks, OffloadCompression.INT8_B128, fp8_weights={"attn.qkv.weight": (1.0, True), "attn.out.weight": (1.0, False)})
+    off = BlockOffloader(cuda_device, blocks, OffloadCompression.NONE, chunk_bytes=64 << 10,
+                         fp8_weights={"attn.qkv.weight": (scale_qkv, True), "attn.out.weight": (scale_out, False)})
+    try:
+        st0 = off.stats()
+        for idx in (0, 1, 2, 1, 0):
+            off.prefetch_block(idx)
+            w = off.await_block(idx)
+            torch.cuda.synchronize()
+            cq, co = blocks[idx]["attn.qkv.weight"].numpy(), blocks[idx]["attn.out.weight"].numpy()
+            assert w["attn.qkv.weight"].shape == (d, 3 * d) and w["attn.qkv.weight"].dtype == torch.bfloat16
+            assert np.array_equal(G.bits_of(w["attn.qkv.weight"]).reshape(d, 3 * d), capi.fp8_dequant_transpose(cq, scale_qkv, 3 * d, d))
+            assert w["attn.out.weight"].shape == co.shape
+            assert np.array_equal(G.bits_of(w["attn.out.weight"]).reshape(-1), capi.fp8_to_bf16(co.reshape(-1), scale_out))
+            assert torch.equal(w["norm.weight"].cpu(), blocks[idx]["norm.weight"])
+        # one byte per FP8 element crossed the link (plus the BF16 norm weight and padding to 256 bytes)
+        per_block = [3 * d * d + d * (d + 8 * b) for b in range(3)]
+        moved = off.stats()["bytes_link_in"] - st0["bytes_link_in"]
+        assert sum(per_block[i] for i in (0, 1, 2, 1, 0)) <= moved < sum(per_block[i] for i in (0, 1, 2, 1, 0)) + 5 * 4096
+    finally:
+        off.close()

@@ -245,3 +245,60 @@ def test_checkpoint_manager_cpu_offload_policy_uses_the_pool(cuda_device):
     finally:
         CHECKPOINT_MANAGER.clear()
         ckpt.clear_activation_offload_pool()
+
+
+def test_save_and_restore_hooks_consult_the_manager_once_it_has_entries(cuda_device, model_and_input):
+    """src/autograd.rs:894-907 and 1867-1892: with CHECKPOINT_HAS_ENTRIES set, every tensor a block saves is offered
+    to the manager, and backward takes the manager's copy (made contiguous) where it has one."""
+    from flame_b200 import gradient_checkpointing as gc_mod
+
+    model, x = model_and_input
+    want = _grads(model, x, ["resident"] * 4)
+    pool = ActivationOffloadPool(cuda_device, 256, 2 * 1024 * 2048 * 2 * 2, OffloadCompression.NONE, chunk_bytes=1 << 20)
+    ckpt.set_activation_offload_pool(pool)
+    mgr = gc_mod.CHECKPOINT_MANAGER
+    fetched, offered = [], []
+    real_fetch, real_offer = mgr.fetch_saved, mgr.checkpoint_saved_tensor
+    mgr.fetch_saved = lambda tid, device=None: (fetched.append(tid), real_fetch(tid, device))[1]
+    mgr.checkpoint_saved_tensor = lambda tid, t: (offered.append(tid), real_offer(tid, t))[1]
+    try:
+        mgr.clear()
+        assert gc_mod.CHECKPOINT_HAS_ENTRIES is False
+        _grads(model, x, ["offload"] * 4)
+        assert not offered and not fetched                     # the fast path: no entry, the manager is never asked
+        mgr.set_policy(CheckpointPolicy.cpu_offload())
+        marker = torch.ones(8, device=cuda_device, dtype=torch.bfloat16)
+        mgr.checkpoint_saved_tensor("marker", marker)          # the first entry raises the flag
+        assert gc_mod.CHECKPOINT_HAS_ENTRIES is True
+        offered.clear()
+        got = _grads(model, x, ["offload"] * 4)
+        assert len(offered) >= 4 * 3 and set(fetched) >= set(offered)          # every saved tensor went both ways
+        assert mgr.stats().checkpointed_tensors == len(set(offered)) + 1
+        for a, b in zip(want, got):
+            assert torch.equal(a, b)                           # the manager's copies are the same bytes
+        # a tensor whose manager entry is a recompute closure comes from that closure
+        mgr.clear()
+        mgr.set_policy(CheckpointPolicy.recompute())
+        calls = []
+        h = x.clone().requires_grad_(True)
+        saved_ids = []
+        real_offer2 = mgr.checkpoint_saved_tensor
+
+        def spy(tid, t):
+            saved_ids.append((tid, t))
+            return real_offer2(tid, t)
+        mgr.set_recompute_for("marker", (8,), torch.bfloat16, lambda: marker)
+        mgr.checkpoint_saved_tensor = spy
+        y = ckpt.checkpoint_offload([h], model[0], min_bytes=1 << 12)
+        tid0, t0 = saved_ids[0]
+        keep = t0.detach().clone()
+        mgr.set_recompute_for(tid0, tuple(t0.shape), t0.dtype, lambda: (calls.append(tid0), keep.clone())[1])
+        y.float().pow(2).mean().backward()
+        torch.cuda.synchronize()
+        assert calls and all(c == tid0 for c in calls)
+    finally:
+        mgr.fetch_saved, mgr.checkpoint_saved_tensor = real_fetch, real_offer
+        mgr.clear()
+        mgr.set_policy(CheckpointPolicy.recompute())
+        ckpt.clear_activation_offload_pool()
+        pool.close()

@@ -1,0 +1,83 @@
+"""flame_fused_dequant_transpose_bf16 (FP8 weights -> BF16 with the transpose built in) against the oracle, the
+committed fixture and, where it was built, the reference's own kernel on the same device buffers.  Bit exact."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from flame_b200 import _lib
+from oracle import capi
+
+pytestmark = pytest.mark.gpu
+SCALES = [1.0, 0.0123, 3.0e-5, 1.0e30, 1.0e-30, -2.5, 0.0]
+
+
+def _run(lib, codes: np.ndarray, scale: float, m: int, n: int, dev, in_offset: int = 0, out_offset: int = 0) -> np.ndarray:
+    base = torch.zeros(m * n + in_offset + 32, dtype=torch.uint8, device=dev)
+    base[in_offset:in_offset + m * n] = torch.from_numpy(np.ascontiguousarray(codes).reshape(-1)).to(dev)
+    obase = torch.full((m * n + out_offset + 64,), 0x7F7F, dtype=torch.int16, device=dev)
+    out = obase[out_offset:out_offset + m * n]
+    rc = lib.flame_fused_dequant_transpose_bf16(base.data_ptr() + in_offset, out.data_ptr(), float(scale), m, n,
+                                               torch.cuda.current_stream(dev).cuda_stream)
+    assert rc == 0, rc
+    torch.cuda.synchronize(dev)
+    assert bool((obase[:out_offset] == 0x7F7F).all()) and bool((obase[out_offset + m * n:] == 0x7F7F).all())   # nothing outside
+    return out.cpu().numpy().view(np.uint16).reshape(n, m)
+
+
+@pytest.mark.parametrize("m,n", [(16, 16), (8, 4), (32, 32), (40, 36), (64, 128), (72, 100), (256, 96), (1024, 3072)])
+def test_fast_kernel_equals_the_oracle(cuda_device, m, n):
+    lib = _lib.lib()
+    rng = np.random.default_rng(m * 1000 + n)
+    codes = rng.integers(0, 256, size=(m, n), dtype=np.uint8)
+    codes.reshape(-1)[:256] = np.arange(256, dtype=np.uint8)[: min(256, m * n)]     # every code, NaN codes included
+    for sc in SCALES[:4] + [-2.5]:
+        assert np.array_equal(_run(lib, codes, sc, m, n, cuda_device), capi.fp8_dequant_transpose(codes, sc, m, n)), (m, n, sc)
+
+
+@pytest.mark.parametrize("m,n,io,oo", [(7, 5, 0, 0), (33, 17, 0, 0), (40, 36, 1, 0), (40, 36, 0, 1), (30, 64, 0, 0), (64, 30, 0, 0), (1, 1, 3, 3)])
+def test_odd_shapes_and_pointers_take_the_element_kernel(cuda_device, m, n, io, oo):
+    lib = _lib.lib()
+    codes = np.random.default_rng(m + n + io).integers(0, 256, size=(m, n), dtype=np.uint8)
+    for sc in (1.0, 0.37):
+        assert np.array_equal(_run(lib, codes, sc, m, n, cuda_device, io, oo), capi.fp8_dequant_transpose(codes, sc, m, n))
+
+
+def test_empty_and_bad_arguments(cuda_device):
+    lib = _lib.lib()
+    assert lib.flame_fused_dequant_transpose_bf16(None, None, 1.0, 0, 16, None) == 0
+    assert lib.flame_fused_dequant_transpose_bf16(None, None, 1.0, 16, 16, None) == 1          # cudaErrorInvalidValue
+
+
+def test_committed_fixture_of_the_reference_kernel(cuda_device, golden_dir):
+    path = os.path.join(golden_dir, "fp8_weight_reference_kernel_sm100.npz")
+    if not os.path.exists(path):
+        pytest.skip("fixture not generated yet")
+    z = np.load(path)
+    sys.path.insert(0, golden_dir)
+    from make_reference_kernel_golden import weight_inputs
+
+    lib = _lib.lib()
+    for name, (codes, m, n) in weight_inputs().items():
+        for k, sc in enumerate(z["scales"]):
+            assert np.array_equal(_run(lib, codes, sc, m, n, cuda_device), z[name][k]), (name, float(sc))
+
+
+def test_equals_the_reference_kernel_on_this_gpu(cuda_device):
+    ref = capi.load_ref_cuda()
+    if ref is None or not hasattr(ref, "flame_fused_dequant_transpose_bf16"):
+        pytest.skip("oracle/_ref/libflame_ref_cuda.so was not built with the weight kernel")
+    lib = _lib.lib()
+    rng = np.random.default_rng(9)
+    for m, n in ((16, 16), (96, 160), (3072, 1024), (37, 53)):
+        codes = rng.integers(0, 256, size=(m, n), dtype=np.uint8)
+        codes.reshape(-1)[:256] = np.arange(256, dtype=np.uint8)
+        c = torch.from_numpy(codes).to(cuda_device)
+        for sc in SCALES:
+            want = torch.empty(m * n, dtype=torch.int16, device=cuda_device)
+            assert ref.flame_fused_dequant_transpose_bf16(c.data_ptr(), want.data_ptr(), float(sc), m, n, None) == 0
+            torch.cuda.synchronize()
+            got = _run(lib, codes, sc, m, n, cuda_device)
+            assert np.array_equal(got, want.cpu().numpy().view(np.uint16).reshape(n, m)), (m, n, sc)

@@ -1,6 +1,7 @@
 """The oracle against the reference's own arithmetic, the golden vectors and itself (CPU only)."""
 import os
 import subprocess
+import sys
 
 import numpy as np
 import pytest
@@ -237,3 +238,55 @@ def test_restatements_agree_on_random_magnitude_spread():
         assert np.array_equal(cf, nf) and np.array_equal(sf.view(np.uint32), nsf.view(np.uint32))
         assert np.array_equal(capi.dequant_fp8_b128(cf, sf), codec_np.dequant_fp8_b128(cf, sf))
         assert np.array_equal(capi.dequant_int8_b128(c8, s8), codec_np.dequant_int8_b128(c8, s8))
+
+
+def test_fp8_weight_decoder_restatement(oracle):
+    """src/cuda/fused_dequant_transpose.cu:37-72: every code, and the transposed layout."""
+    vals = np.array([oracle.load().oracle_fp8_weight_decode(c) for c in range(256)], np.float32)
+    assert vals[0] == 0 and np.signbit(vals[0x80]) and vals[0x80] == 0
+    assert vals[0x01] == 2.0 ** -9 and vals[0x07] == 7 * 2.0 ** -9 and vals[0x08] == 2.0 ** -6
+    assert vals[0x38] == 1.0 and vals[0x77] == 240.0 and vals[0x78] == 256.0 and vals[0xF8] == -256.0
+    assert np.isnan(vals[0x79:0x80]).all() and np.isnan(vals[0xF9:]).all() and np.isfinite(vals[:0x79]).all()
+    codes = np.arange(6, dtype=np.uint8).reshape(2, 3) + 0x38
+    out = oracle.fp8_dequant_transpose(codes, 2.0, 2, 3)
+    want = synthetic_f32_to_bf16(np.array([[1.0, 1.375], [1.125, 1.5], [1.25, 1.625]], np.float32) * 2.0)
+    assert out.shape == (3, 2) and np.array_equal(out, want)
+
+
+def synthetic_f32_to_bf16(x):
+    from flame_b200 import synthetic
+
+    return synthetic.f32_to_bf16_bits(x.reshape(-1)).reshape(x.shape)
+
+
+def test_oracle_reproduces_the_reference_weight_kernel_fixture(oracle, golden_dir):
+    """What the reference's flame_fused_dequant_transpose_bf16 wrote on a B200 (tests/golden/make_reference_kernel_golden.py)."""
+    import os
+
+    path = os.path.join(golden_dir, "fp8_weight_reference_kernel_sm100.npz")
+    if not os.path.exists(path):
+        pytest.skip("fixture not generated yet")
+    z = np.load(path)
+    sys.path.insert(0, golden_dir)
+    from make_reference_kernel_golden import weight_inputs
+
+    for name, (codes, m, n) in weight_inputs().items():
+        for k, sc in enumerate(z["scales"]):
+            assert np.array_equal(oracle.fp8_dequant_transpose(codes, sc, m, n), z[name][k]), (name, float(sc))
+
+
+def test_oracle_reproduces_the_block_by_block_reference_fp8_fixture(oracle, golden_dir):
+    """Per-128-block FP8 pinned to the reference's own kernel run once per block with that block's 1/(absmax/448)."""
+    import os
+
+    path = os.path.join(golden_dir, "fp8_b128_reference_kernel_sm100.npz")
+    if not os.path.exists(path):
+        pytest.skip("fixture not generated yet")
+    z = np.load(path)
+    sys.path.insert(0, golden_dir)
+    from make_reference_kernel_golden import fp8_block_inputs
+
+    for name, bits in fp8_block_inputs().items():
+        codes, scales = oracle.quant_fp8_b128(bits)
+        assert np.array_equal(codes, z[name + "_codes"]), name
+        assert np.array_equal(scales.view(np.uint32), z[name + "_scales"].view(np.uint32)), name
