@@ -327,6 +327,13 @@ __device__ __forceinline__ void fp8_encode_words_ref(const uint32_t* raw, float 
 #pragma unroll
     for (int i = 0; i < NW / 2; ++i) {
       uint32_t o = out[i];
+      // Only a byte whose fast code is at most 0x08 (zero, the sub-normal codes and the smallest normal one) can
+      // belong to an element below 2^-6: (code | 0x80) - 9 keeps bit 7 for every other byte, without borrowing
+      // across bytes.  The element-wise entry point also has to look at NaN elements, which carry code 0x7F.
+      const uint32_t mag = o & 0x7F7F7F7Fu;
+      uint32_t settled = ((mag | 0x80808080u) - 0x09090909u) & 0x80808080u;
+      if (kLegacy) settled &= ~((mag + 0x01010101u) & 0x80808080u);
+      if (settled == 0x80808080u) continue;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const uint32_t rw = raw[2 * i + (k >> 1)];

@@ -167,7 +167,11 @@ struct FlameOffloadPool {
 
   uint8_t* slab = nullptr;
   size_t slab_bytes = 0;
-  std::vector<uint32_t> free_chunks;      // stack
+  // Queue, not stack: a push takes the chunks that were released longest ago.  A chunk just released by a restore may
+  // still be read by that restore's host-to-device copy, and the offload that takes it has to wait for that copy; with
+  // first-in first-out reuse an offload issued beside restores (weights streaming in, the next step's forward) does
+  // not queue up behind them.  Slots, which callers see, stay last in first out as in the reference.
+  std::deque<uint32_t> free_chunks;
   std::vector<int32_t> chunk_last_reader;  // slot whose restore last read the chunk, -1 = none
   size_t total_chunks = 0;
 
@@ -206,14 +210,15 @@ struct FlameOffloadPool {
 
   // A queued offload that never ran wrote nothing: whoever read these chunks last is still their last reader.
   void release_chunks_unwritten(Slot& s) {
-    for (auto it = s.chunks.rbegin(); it != s.chunks.rend(); ++it) free_chunks.push_back(*it);
+    // they go back to the FRONT, in order: nothing was written and nobody reads them, so they are the best to take next
+    for (auto it = s.chunks.rbegin(); it != s.chunks.rend(); ++it) free_chunks.push_front(*it);
     s.chunks.clear();
   }
 
   void release_chunks(Slot& s, int32_t reader) {
-    for (auto it = s.chunks.rbegin(); it != s.chunks.rend(); ++it) {
-      chunk_last_reader[*it] = reader;
-      free_chunks.push_back(*it);
+    for (uint32_t c : s.chunks) {
+      chunk_last_reader[c] = reader;
+      free_chunks.push_back(c);
     }
     s.chunks.clear();
   }
@@ -591,8 +596,7 @@ FlameOffloadPool* flame_offload_pool_create(size_t num_slots, size_t max_bytes, 
   }
   p->slab = static_cast<uint8_t*>(slab);
   p->chunk_last_reader.assign(total, -1);
-  p->free_chunks.reserve(total);
-  for (size_t c = total; c-- > 0;) p->free_chunks.push_back((uint32_t)c);
+  for (size_t c = 0; c < total; ++c) p->free_chunks.push_back((uint32_t)c);
 
   bool ok = true;
   auto chk = [&](cudaError_t err, const char* what) { if (ok && err != cudaSuccess) { fail_cuda(err, what); ok = false; } };
@@ -717,8 +721,8 @@ static FlameOffloadStatus push_impl(FlameOffloadPool* p, const void* src, const 
   s.chunks.clear();
   s.stored_bytes = 0;
   for (size_t k = 0; k < nchunks; ++k) {
-    s.chunks.push_back(p->free_chunks.back());
-    p->free_chunks.pop_back();
+    s.chunks.push_back(p->free_chunks.front());
+    p->free_chunks.pop_front();
     if (p->compressed()) s.stored_bytes += p->stored_for(std::min<uint64_t>(p->chunk_elems, numel - k * p->chunk_elems));
   }
   if (!p->compressed()) s.stored_bytes = bytes;

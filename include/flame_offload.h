@@ -152,14 +152,21 @@ size_t flame_act_packed_bytes(size_t n);
  * out-of-memory handler freeing device memory by moving an activation out, or
  * a step loop with a fixed memory plan in which cudaMalloc/cudaFree would stall
  * the device or fail.  The device staging it needs is a fixed array inside the
- * library: every GPU that loads the library holds about 8.3 MiB of it until the
+ * library: every GPU that uses the library holds about 8.3 MiB of it until the
  * process exits.
  *
+ *   - The CUDA runtime loads a library's kernels and static device arrays when
+ *     they are first used on a device, not when the library is opened, and that
+ *     loading itself takes device memory.  A caller that wants the no-allocation
+ *     property at the moment of need therefore makes one small warm-up call per
+ *     device at start-up, for each codec it will use and for both a 32-byte
+ *     aligned and an unaligned input (they run different kernels), while
+ *     memory is still available.  After that, a call takes no device memory.
  *   - n may be at most FLAME_ACT_NOALLOC_MAX_ELEMS; larger tensors are refused
  *     with cudaErrorInvalidValue (1) and a message in flame_offload_last_error().
  *   - codec is FLAME_OFFLOAD_COMPRESSION_INT8_B128 or _FP8_B128; flags as for
  *     the quantise entry points.  Results are identical to those entry points.
- *   - The first call on each device looks up the array's device address
+ *   - The first call on each device also looks up the array's device address
  *     (cudaGetSymbolAddress); make that first call before starting any stream
  *     capture on that device.
  *   - All calls share the one array.  Calls on the same stream are ordered;

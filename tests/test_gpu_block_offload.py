@@ -148,9 +148,10 @@ def test_fp8_weight_bytes_stream_as_they_are_and_expand_on_the_device(cuda_devic
             assert w["attn.out.weight"].shape == co.shape
             assert np.array_equal(G.bits_of(w["attn.out.weight"]).reshape(-1), capi.fp8_to_bf16(co.reshape(-1), scale_out))
             assert torch.equal(w["norm.weight"].cpu(), blocks[idx]["norm.weight"])
-        # one byte per FP8 element crossed the link (plus the BF16 norm weight and padding to 256 bytes)
+        # one byte per FP8 element crossed the link (plus the BF16 norm weight and padding to 256 bytes); with two
+        # device slots block 1 is still on the device when it is asked for again, so four loads: 0, 1, 2, 0
         per_block = [3 * d * d + d * (d + 8 * b) for b in range(3)]
         moved = off.stats()["bytes_link_in"] - st0["bytes_link_in"]
-        assert sum(per_block[i] for i in (0, 1, 2, 1, 0)) <= moved < sum(per_block[i] for i in (0, 1, 2, 1, 0)) + 5 * 4096
+        assert sum(per_block[i] for i in (0, 1, 2, 0)) <= moved < sum(per_block[i] for i in (0, 1, 2, 0)) + 4 * 4096
     finally:
         off.close()

@@ -58,6 +58,38 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point(cuda_device, codec)
         assert bool((host.numpy()[nbytes:nbytes + 4096] == 0xEE).all())  # nothing written past the result
 
 
+def test_after_a_warm_up_call_no_device_memory_is_taken(cuda_device):
+    """The array, and the kernels, take their device memory when they are first used on a device (CUDA loads a
+    library's modules lazily), not when the library is opened: that is what the warm-up call at start-up is for.
+    After it, a call changes nothing in what the device has free: aligned input (the tiled kernel) and an input
+    that starts one element off a 32-byte boundary (the element-wise kernel), both codecs."""
+    lib = _lib.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    n = 8192 * 5 + 300
+    base = torch.randn(n + 1, device=cuda_device).to(torch.bfloat16)
+    out = torch.empty(lib.flame_act_packed_bytes(n), dtype=torch.uint8, device=cuda_device)
+    inputs = [base[:n], base[1:]]
+    for codec in (INT8, FP8):                                   # the warm-up: one call per codec and kernel kind
+        for x in inputs:
+            assert lib.flame_act_offload_packed_noalloc(x.data_ptr(), out.data_ptr(), n, codec, 0, stream) == 0
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info(cuda_device)
+    for codec in (INT8, FP8):
+        for x in inputs:
+            assert lib.flame_act_offload_packed_noalloc(x.data_ptr(), out.data_ptr(), n, codec, 0, stream) == 0
+            torch.cuda.synchronize()
+            assert np.array_equal(out.cpu().numpy(), _reference_packed(lib, x, codec, 0))
+    free1, _ = torch.cuda.mem_get_info(cuda_device)
+    # out.cpu() and the reference entry point go through torch's caching allocator, which may grow; a second pass
+    # with everything cached must leave the free figure where it is
+    for codec in (INT8, FP8):
+        for x in inputs:
+            assert lib.flame_act_offload_packed_noalloc(x.data_ptr(), out.data_ptr(), n, codec, 0, stream) == 0
+    torch.cuda.synchronize()
+    free2, _ = torch.cuda.mem_get_info(cuda_device)
+    assert free2 == free1, (free0, free1, free2)
+
+
 def test_device_output_and_largest_size(cuda_device):
     lib = _lib.lib()
     n = MAX_ELEMS
