@@ -27,7 +27,7 @@ class PoolConfig(C.Structure):
         ("staging_tiles", C.c_uint32), ("codec_flags", C.c_uint32), ("host_budget_bytes", C.c_uint64),
         ("host_alloc_flags", C.c_uint32), ("codec_max_ctas", C.c_int32), ("numa_node", C.c_int32),
         ("tile_chunks", C.c_uint32), ("d2h_piece_bytes", C.c_uint64), ("h2d_piece_bytes", C.c_uint64),
-        ("deferred_inflight_bytes", C.c_uint64),
+        ("deferred_inflight_bytes", C.c_uint64), ("collect_timing", C.c_uint32), ("reserved0", C.c_uint32),
     ]
 
 
@@ -35,7 +35,7 @@ class Stats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in (
         "pushes", "pulls", "bytes_logical_out", "bytes_logical_in", "bytes_link_out", "bytes_link_in",
         "chunks_out", "chunks_in", "codec_launches", "host_chunks_total", "host_chunks_free", "push_rejected_full",
-        "pushes_cancelled", "pushes_queued")]
+        "pushes_cancelled", "pushes_queued", "offload_span_us", "restore_span_us", "ready_wait_us", "spans_timed", "spans_pending")]
 
 
 class SlotInfo(C.Structure):

@@ -76,7 +76,7 @@ class ActivationOffloadPool:
                  chunk_bytes: int = 0, staging_tiles: int = 0, codec_flags: int = 0,
                  host_budget_bytes: int = 0, host_alloc_flags: int = 0, codec_max_ctas: int = 0,
                  numa_node: int = -2, tile_chunks: int = 0, d2h_piece_bytes: int = 0, h2d_piece_bytes: int = 0,
-                 deferred_inflight_bytes: int = 0):
+                 deferred_inflight_bytes: int = 0, collect_timing: bool = False):
         import torch
 
         self._torch = torch
@@ -87,7 +87,7 @@ class ActivationOffloadPool:
         self.device = torch.device("cuda", index)
         cfg = _lib.PoolConfig(C.sizeof(_lib.PoolConfig), index, chunk_bytes, staging_tiles, codec_flags,
                               host_budget_bytes, host_alloc_flags, codec_max_ctas, numa_node, tile_chunks,
-                              d2h_piece_bytes, h2d_piece_bytes, deferred_inflight_bytes)
+                              d2h_piece_bytes, h2d_piece_bytes, deferred_inflight_bytes, 1 if collect_timing else 0, 0)
         self.deferred = deferred_inflight_bytes > 0
         self._lib = _lib.lib()
         with torch.cuda.device(index):

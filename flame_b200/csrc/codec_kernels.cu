@@ -336,11 +336,21 @@ __device__ __forceinline__ void fp8_encode_words_ref(const uint32_t* raw, float 
       if (settled == 0x80808080u) continue;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
+        if (settled & (0x80u << (8 * k))) continue;
         const uint32_t rw = raw[2 * i + (k >> 1)];
         const float x = (k & 1) ? bf16hi(rw) : bf16lo(rw);
         const float y = __fmul_rn(fabsf(x), inv);
-        const bool redo = kLegacy ? !(y >= 0.015625f) : (y < 0.015625f);
-        if (redo) o = (o & ~(0xFFu << (8 * k))) | (fp8_encode_exact<kLegacy>(x, inv) << (8 * k));
+        uint32_t c;
+        if (y < 0.015625f) {
+          // the reference's arm for magnitudes under 2^-6, in line: (int)(y * 512 + 0.5f) in binary32, at most 7; the
+          // sign is that of `val < 0`, so a zero of either sign encodes as 0x00 (src/cuda/fp8_quant.cu:28-33, 52-56)
+          c = min(__float2uint_rz(__fadd_rn(__fmul_rn(y, 512.0f), 0.5f)), 7u) | ((x < 0.0f) ? 0x80u : 0u);
+        } else if (kLegacy && (y != y)) {
+          c = 0x30u;   // a NaN product: none of the reference's comparisons holds (see fp8_encode_legacy)
+        } else {
+          continue;
+        }
+        o = (o & ~(0xFFu << (8 * k))) | (c << (8 * k));
       }
       out[i] = o;
     }

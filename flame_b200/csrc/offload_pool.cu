@@ -185,6 +185,58 @@ struct FlameOffloadPool {
 
   FlameOffloadStats stats{};
 
+  // Optional timing (FlameOffloadPoolConfig.collect_timing): spans between two timing-enabled events, added to the
+  // statistics once the device has passed them.  Offload spans are opened by whichever thread enqueues the offload
+  // (the pool's own thread in the deferred mode), so the list has a lock of its own.
+  struct Span { cudaEvent_t a, b; int kind; };     // kind 0: offload on the D2H stream, 1: restore on the H2D stream, 2: a wait for a restore
+  bool timing = false;
+  std::mutex timing_mu;
+  std::vector<Span> spans;
+  std::vector<cudaEvent_t> spare_events;
+  uint64_t span_ns[3] = {0, 0, 0};
+  uint64_t spans_done = 0;
+
+  cudaEvent_t timing_event() {      // with timing_mu held
+    if (!spare_events.empty()) { cudaEvent_t e = spare_events.back(); spare_events.pop_back(); return e; }
+    cudaEvent_t e = nullptr;
+    return cudaEventCreate(&e) == cudaSuccess ? e : nullptr;
+  }
+  // Opens a span on `st`; returns its first event (nullptr when timing is off or no event could be made).
+  cudaEvent_t span_open(cudaStream_t st) {
+    if (!timing) return nullptr;
+    std::lock_guard<std::mutex> lk(timing_mu);
+    cudaEvent_t a = timing_event();
+    if (a && cudaEventRecord(a, st) != cudaSuccess) { spare_events.push_back(a); a = nullptr; }
+    return a;
+  }
+  void span_close(cudaEvent_t a, cudaStream_t st, int kind) {
+    if (!a) return;
+    std::lock_guard<std::mutex> lk(timing_mu);
+    cudaEvent_t b = timing_event();
+    if (!b || cudaEventRecord(b, st) != cudaSuccess) { spare_events.push_back(a); if (b) spare_events.push_back(b); return; }
+    spans.push_back({a, b, kind});
+  }
+  // Adds every span the device has finished to the totals and takes its events back.
+  void harvest_spans(size_t only_if_at_least = 0) {
+    if (!timing) return;
+    std::lock_guard<std::mutex> lk(timing_mu);
+    if (spans.size() < only_if_at_least) return;
+    size_t keep = 0;
+    for (size_t i = 0; i < spans.size(); ++i) {
+      const Span sp = spans[i];
+      const cudaError_t q = cudaEventQuery(sp.b);
+      if (q == cudaErrorNotReady) { spans[keep++] = sp; continue; }
+      float ms = 0.0f;
+      if (q == cudaSuccess && cudaEventElapsedTime(&ms, sp.a, sp.b) == cudaSuccess && ms >= 0.0f) {
+        span_ns[sp.kind] += (uint64_t)((double)ms * 1e6);
+        spans_done++;
+      }
+      spare_events.push_back(sp.a);
+      spare_events.push_back(sp.b);
+    }
+    spans.resize(keep);
+  }
+
   // deferred offload
   bool deferred = false;
   uint64_t inflight_budget = 0, inflight_bytes = 0;
@@ -286,9 +338,11 @@ PushPlan make_plan(FlameOffloadPool& p, const Slot& s, const uint8_t* src) {
 cudaError_t issue_push(FlameOffloadPool& p, const PushPlan& plan, PushCounts& n) {
   for (cudaEvent_t ev : plan.readers) POOL_TRY(cudaStreamWaitEvent(p.s_d2h, ev, 0), "push: wait(h2d_done)");
   const size_t nchunks = plan.chunks.size();
+  cudaEvent_t span = nullptr;   // opened when the D2H stream has the source (or the first tile) in front of it
   if (plan.scales_src) {
     // Compressed by its producer: each chunk's codes and scales go straight to their places in the pinned chunk.
     POOL_TRY(cudaStreamWaitEvent(p.s_d2h, plan.producer, 0), "push: wait(producer)");
+    span = p.span_open(p.s_d2h);
     for (size_t k = 0; k < nchunks; ++k) {
       const uint64_t e0 = k * p.chunk_elems;
       const uint64_t ec = std::min<uint64_t>(p.chunk_elems, plan.numel - e0);
@@ -301,6 +355,7 @@ cudaError_t issue_push(FlameOffloadPool& p, const PushPlan& plan, PushCounts& n)
     }
   } else if (!p.compressed()) {
     POOL_TRY(cudaStreamWaitEvent(p.s_d2h, plan.producer, 0), "push: wait(producer)");
+    span = p.span_open(p.s_d2h);
     for (size_t k = 0; k < nchunks; ++k) {
       const uint64_t off = k * p.chunk_src_bytes;
       const uint64_t len = std::min<uint64_t>(p.chunk_src_bytes, plan.bytes - off);
@@ -327,6 +382,7 @@ cudaError_t issue_push(FlameOffloadPool& p, const PushPlan& plan, PushCounts& n)
       n.launches++;
       POOL_TRY(t.full.record(p.s_quant), "push: record(tile full)");
       POOL_TRY(t.full.make_wait(p.s_d2h), "push: wait(tile full)");
+      if (k0 == 0) span = p.span_open(p.s_d2h);
       for (size_t j = 0; j < kn; ++j) {
         const uint64_t ec = std::min<uint64_t>(p.chunk_elems, e - j * p.chunk_elems);
         const size_t link = p.stored_for(ec);
@@ -338,6 +394,7 @@ cudaError_t issue_push(FlameOffloadPool& p, const PushPlan& plan, PushCounts& n)
     }
   }
   POOL_TRY(cudaEventRecord(plan.d2h_done, p.s_d2h), "push: record(d2h_done)");
+  p.span_close(span, p.s_d2h, 0);
   return cudaSuccess;
 }
 
@@ -419,6 +476,7 @@ cudaError_t enqueue_pull(FlameOffloadPool& p, Slot& s, uint8_t* dst, uint8_t* sc
   POOL_TRY(s.consumer.record(compute), "pull: cudaEventRecord(consumer)");
   POOL_TRY(s.d2h_done.make_wait(p.s_h2d), "pull: wait(d2h_done)");
   const size_t nchunks = s.chunks.size();
+  cudaEvent_t span = p.span_open(p.s_h2d);
   if (scales_dst) {
     // The compressed form itself is wanted (the caller dequantises it, several tensors to a launch): each chunk's
     // codes and scales go straight to their places in the caller's two buffers; no staging tile, no kernel.
@@ -475,12 +533,19 @@ cudaError_t enqueue_pull(FlameOffloadPool& p, Slot& s, uint8_t* dst, uint8_t* sc
     POOL_TRY(s.h2d_done.record(p.s_h2d), "pull: record(h2d_done)");
     POOL_TRY(s.ready.record(p.s_dequant), "pull: record(ready)");
   }
-  if (!(flags & FLAME_OFFLOAD_PULL_DEFER_WAIT)) POOL_TRY(s.ready.make_wait(compute), "pull: wait(ready)");
+  p.span_close(span, p.s_h2d, 1);
+  if (!(flags & FLAME_OFFLOAD_PULL_DEFER_WAIT)) {
+    cudaEvent_t w = p.span_open(compute);
+    POOL_TRY(s.ready.make_wait(compute), "pull: wait(ready)");
+    p.span_close(w, compute, 2);
+  }
   p.stats.chunks_in += nchunks;
   return cudaSuccess;
 }
 
 void destroy_pool(FlameOffloadPool* p) {
+  for (auto& sp : p->spans) { cudaEventDestroy(sp.a); cudaEventDestroy(sp.b); }
+  for (cudaEvent_t e : p->spare_events) cudaEventDestroy(e);
   p->hold_after.destroy();
   for (auto& s : p->slots) { s.producer.destroy(); s.d2h_done.destroy(); s.consumer.destroy(); s.h2d_done.destroy(); s.ready.destroy(); }
   for (auto* ring : {&p->out_tiles, &p->in_tiles})
@@ -564,6 +629,7 @@ FlameOffloadPool* flame_offload_pool_create(size_t num_slots, size_t max_bytes, 
   p->codec_max_ctas = cfg.codec_max_ctas;
   p->d2h_piece = cfg.d2h_piece_bytes;
   p->h2d_piece = cfg.h2d_piece_bytes;
+  p->timing = cfg.collect_timing != 0;
 
   // A slot that fits in one chunk gets a chunk of exactly its stored size, so a
   // pool of small slots holds num_slots * stored(max_bytes) pinned bytes like
@@ -758,6 +824,7 @@ static FlameOffloadStatus push_impl(FlameOffloadPool* p, const void* src, const 
   if (trace_on())
     fprintf(stderr, "[flame_offload] push slot=%zu epoch=%llu numel=%zu dtype=%d bytes=%zu stored=%llu chunks=%zu free_chunks=%zu\n", slot,
             (unsigned long long)p->epoch, numel, dtype, bytes, (unsigned long long)s.stored_bytes, nchunks, p->free_chunks.size());
+  p->harvest_spans(512);   // keeps the list of open spans short when nobody reads the statistics
   p->stats.pushes++;
   p->stats.bytes_logical_out += bytes;
   p->stats.host_chunks_free = p->free_chunks.size();
@@ -901,7 +968,9 @@ FlameOffloadStatus flame_offload_pool_wait_ready(FlameOffloadPool* p, size_t slo
   std::lock_guard<std::mutex> lk(p->mu);
   if (slot >= p->slots.size()) return fail(FLAME_OFFLOAD_ERR_STATE, "wait_ready: slot out of range");
   DeviceGuard guard(p->device);
+  cudaEvent_t w = p->span_open((cudaStream_t)stream);
   cudaError_t e = p->slots[slot].ready.make_wait((cudaStream_t)stream);
+  p->span_close(w, (cudaStream_t)stream, 2);
   return e == cudaSuccess ? FLAME_OFFLOAD_OK : fail_cuda(e, "wait_ready: cudaStreamWaitEvent");
 }
 
@@ -1028,6 +1097,16 @@ FlameOffloadStatus flame_offload_pool_stats(const FlameOffloadPool* pc, FlameOff
   auto* p = const_cast<FlameOffloadPool*>(pc);
   if (!p || !out) return fail(FLAME_OFFLOAD_ERR_INVALID, "stats: null argument");
   std::lock_guard<std::mutex> lk(p->mu);
+  if (p->timing) {
+    DeviceGuard guard(p->device);
+    p->harvest_spans();
+    std::lock_guard<std::mutex> tl(p->timing_mu);
+    p->stats.offload_span_us = p->span_ns[0] / 1000u;
+    p->stats.restore_span_us = p->span_ns[1] / 1000u;
+    p->stats.ready_wait_us = p->span_ns[2] / 1000u;
+    p->stats.spans_timed = p->spans_done;
+    p->stats.spans_pending = p->spans.size();
+  }
   *out = p->stats;
   return FLAME_OFFLOAD_OK;
 }

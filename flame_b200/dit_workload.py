@@ -276,6 +276,10 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
                 res["link_gb_per_step"] = round(st["bytes_link_out"] / n / 1e9, 3)
                 if st["push_rejected_full"]:      # a block that found the pool full was recomputed instead: the arm is not what it says
                     res["pushes_rejected_pool_full"] = int(st["push_rejected_full"])
+                if st["spans_timed"]:      # the pool was asked to time itself: where the restores cost the step
+                    res["timing_ms_per_step"] = {"offload_spans": round(st["offload_span_us"] / n / 1e3, 2),
+                                                 "restore_spans": round(st["restore_span_us"] / n / 1e3, 2),
+                                                 "compute_stream_waiting_for_restores": round(st["ready_wait_us"] / n / 1e3, 3)}
                 if deferred_bytes:
                     res["tensors_used_in_place_per_step"] = round(st["pushes_cancelled"] / n, 1)
                     res["tensors_pushed_per_step"] = round(st["pushes"] / n, 1)
@@ -310,7 +314,7 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
         p = plan_blocks(blk, d2h_gbs=link.d2h_gbs, h2d_gbs=link.h2d_gbs, offload=Decision.OFFLOAD_INT8,
                         interference=CAPPED_PLAN_INTERFERENCE, overhead_cap_ms=cap_ms)
         r = run_arm("offload_int8_capped", p.decisions, OffloadCompression.INT8_B128 if Decision.OFFLOAD_INT8 in p.decisions else None,
-                    deferred_bytes=ISSUE_OFF_THREAD, d2h_piece=DEFERRED_D2H_PIECE_BYTES)
+                    deferred_bytes=ISSUE_OFF_THREAD, d2h_piece=DEFERRED_D2H_PIECE_BYTES, collect_timing=True)
         r["plan_est_ms"] = {"stall": round(p.est_stall_ms, 2), "recompute": round(p.est_recompute_ms, 2),
                             "interference": round(p.est_interference_ms, 2), "cap": round(cap_ms, 2)}
         r["plan_resident_gb"] = round(p.resident_bytes / 1e9, 3)

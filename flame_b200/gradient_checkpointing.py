@@ -11,6 +11,7 @@ byte-counter rule; the measured-bandwidth planner lives in ``flame_b200.policy``
 from __future__ import annotations
 
 import enum
+import itertools
 import threading
 import weakref
 from dataclasses import dataclass
@@ -20,12 +21,18 @@ from . import checkpoint as _ckpt
 from .errors import InvalidOperation
 
 
-def tensor_id(t):
-    """Identity of a tensor for the manager's registry (the reference's TensorId): the memory it views and how.
+_NEXT_TENSOR_ID = itertools.count(1)
 
-    A saved-tensor hook does not always receive the Python object the caller holds (an op's saved output arrives
-    as a detached alias), so the key is what both objects share."""
-    return (t.untyped_storage().data_ptr(), t.storage_offset(), tuple(t.shape), tuple(t.stride()), t.dtype)
+
+def tensor_id(t):
+    """Identity of a tensor for the manager's registry (the reference's TensorId): a number given to the tensor
+    object the first time it is asked for and kept on it.  Never derived from the address: a checkpointed block
+    frees its saved tensors as it offloads them, and the allocator hands the same address to the next block's."""
+    tid = getattr(t, "_flame_tensor_id", None)
+    if tid is None:
+        tid = next(_NEXT_TENSOR_ID)
+        t._flame_tensor_id = tid
+    return tid
 
 
 class CheckpointPolicyKind(enum.Enum):

@@ -251,6 +251,11 @@ typedef struct {
                                  and the caller uses the source as it is, so the link never holds backward up
                                  with round trips that free no memory.  About one block's stored bytes
                                  (1-4 x 100 MB) keeps the link busy. */
+  uint32_t collect_timing;    /* non-zero: time every offload, every restore and every wait for a restore with a pair of
+                                 timing-enabled events and report the sums in FlameOffloadStats (the reference traces
+                                 behind environment switches, src/autograd.rs:1086-1089, 1501-1547).  Off by default:
+                                 two more event records per push and four per pull. */
+  uint32_t reserved0;
 } FlameOffloadPoolConfig;
 
 typedef struct {
@@ -263,6 +268,18 @@ typedef struct {
   uint64_t push_rejected_full;                  /* pushes refused: no slot or no pinned chunk left */
   uint64_t pushes_cancelled;                    /* deferred pushes taken back before their copies were enqueued */
   uint64_t pushes_queued;                       /* deferred pushes waiting for their turn right now */
+  /* With FlameOffloadPoolConfig.collect_timing, device time in microseconds, summed over the spans the device has
+   * finished when the statistics are read (spans_pending are still running):
+   *   offload_span_us  per offload, from the moment the device-to-host stream has the tensor (or its first compressed
+   *                    tile) in front of it to the end of its last copy: link time plus what the stream waited for
+   *                    later tiles to be compressed;
+   *   restore_span_us  per restore, from the moment the host-to-device stream may start (the offload has finished) to
+   *                    the end of its last copy;
+   *   ready_wait_us    per wait for a restore (pull_into without DEFER_WAIT, wait_ready), from the moment the caller's
+   *                    stream reaches the wait to the moment it passes: what the restores cost the stream that
+   *                    consumes them. */
+  uint64_t offload_span_us, restore_span_us, ready_wait_us;
+  uint64_t spans_timed, spans_pending;
 } FlameOffloadStats;
 
 /* new(device, num_slots, max_bytes, compression): src/activation_offload.rs:365-427.

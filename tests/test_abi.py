@@ -37,8 +37,8 @@ def test_binding_covers_every_declared_symbol():
 
 def test_struct_sizes_match_the_header():
     assert C.sizeof(_lib.Handle) == 16
-    assert C.sizeof(_lib.PoolConfig) == 72
-    assert C.sizeof(_lib.Stats) == 14 * 8
+    assert C.sizeof(_lib.PoolConfig) == 80
+    assert C.sizeof(_lib.Stats) == 19 * 8
     assert C.sizeof(_lib.SlotInfo) == 40
     assert C.sizeof(_lib.PolicyTensor) == 24
     assert C.sizeof(_lib.PolicyInput) == 72

@@ -4,6 +4,7 @@ Small models do not exercise what a real step does: 28-340 MB tensors that span 
 that the allocator hands out again within a block, restores issued blocks ahead of their use, offloads still queued
 when backward arrives."""
 import gc
+import os
 
 import numpy as np
 import pytest
@@ -89,10 +90,13 @@ def test_uncompressed_offload_reproduces_resident_gradients(cuda_device, dit, fl
         pool.close()
 
 
+# FLAME_TEST_REPEAT=10 runs every combination ten times in one process (evidence against ordering holes between
+# deferred offloads, cancelled tensors and block-wide expansion, which would show as an occasional failure)
+@pytest.mark.parametrize("rep", range(int(os.environ.get("FLAME_TEST_REPEAT", "1"))))
 @pytest.mark.parametrize("fused,budget,batched", [
     (False, 0, False), (True, 0, False), (False, 1 << 40, False), (True, 1 << 40, False), (False, 64 << 20, False),
     (True, 64 << 20, False), (False, 1 << 40, True), (True, 64 << 20, True), (True, 0, True)])
-def test_int8_offload_keeps_the_large_gradients_close(cuda_device, dit, fused, budget, batched):
+def test_int8_offload_keeps_the_large_gradients_close(cuda_device, dit, fused, budget, batched, rep):
     """budget 64 MB: most tensors are still queued when backward arrives; those that a producer compressed are
     dequantised on the device from their codes, the others are used as they are."""
     grads, want, saved = dit
@@ -119,6 +123,8 @@ def test_int8_offload_keeps_the_large_gradients_close(cuda_device, dit, fused, b
         W.FUSED_PRODUCERS = False
         ckpt.set_batched_codec(False)
         ckpt.clear_activation_offload_pool()
+        if "pool" in locals():
+            pool.close()
 
 
 def test_many_training_steps_leave_nothing_behind(cuda_device):

@@ -556,3 +556,33 @@ def test_plain_c_caller_round_trips(cuda_device, tmp_path):
     env["CUDA_VISIBLE_DEVICES"] = str(cuda_device.index or 0)
     r = subprocess.run([exe], capture_output=True, text=True, timeout=120, env=env)
     assert r.returncode == 0 and "abi_roundtrip: ok" in r.stdout, (r.stdout, r.stderr)
+
+
+def test_collect_timing_reports_offload_restore_and_wait_spans(cuda_device):
+    """FlameOffloadPoolConfig.collect_timing: device time of every offload, restore and wait for a restore."""
+    n = 32 << 20                                        # 64 MB of BF16: a few milliseconds each way
+    x = torch.randn(n, device=cuda_device).to(torch.bfloat16)
+    dst = torch.empty_like(x)
+    for mode in (OffloadCompression.NONE, OffloadCompression.INT8_B128):
+        pool = ActivationOffloadPool(cuda_device, 4, 2 * n, mode, collect_timing=True)
+        quiet = ActivationOffloadPool(cuda_device, 4, 2 * n, mode)
+        try:
+            for _ in range(3):
+                pool.pull_into(pool.push(x), dst)                     # the wait is inside pull_into
+                h = pool.push(x)
+                pool.prefetch(h, dst)
+                pool.wait_ready(h.slot)                               # the wait is a call of its own
+                quiet.pull_into(quiet.push(x), dst)
+            torch.cuda.synchronize()
+            st, q = pool.stats(), quiet.stats()
+            assert st["spans_pending"] == 0 and st["spans_timed"] == 3 * 2 * 3          # offload + restore + wait, six round trips
+            link_ms = st["bytes_link_out"] / 6 / 63.0e9 * 1e3                           # one direction at the PCIe Gen5 x16 bound
+            for key in ("offload_span_us", "restore_span_us"):
+                per_trip_ms = st[key] / 6 / 1e3
+                assert link_ms * 0.9 < per_trip_ms < link_ms * 20, (key, per_trip_ms, link_ms)
+            # nothing else runs on the stream, so it waits for about as long as offload and restore take
+            assert st["ready_wait_us"] > 0.5 * st["restore_span_us"]
+            assert q["spans_timed"] == 0 and q["offload_span_us"] == 0 and q["ready_wait_us"] == 0
+        finally:
+            pool.close()
+            quiet.close()
