@@ -340,17 +340,10 @@ __device__ __forceinline__ void fp8_encode_words_ref(const uint32_t* raw, float 
         const uint32_t rw = raw[2 * i + (k >> 1)];
         const float x = (k & 1) ? bf16hi(rw) : bf16lo(rw);
         const float y = __fmul_rn(fabsf(x), inv);
-        uint32_t c;
-        if (y < 0.015625f) {
-          // the reference's arm for magnitudes under 2^-6, in line: (int)(y * 512 + 0.5f) in binary32, at most 7; the
-          // sign is that of `val < 0`, so a zero of either sign encodes as 0x00 (src/cuda/fp8_quant.cu:28-33, 52-56)
-          c = min(__float2uint_rz(__fadd_rn(__fmul_rn(y, 512.0f), 0.5f)), 7u) | ((x < 0.0f) ? 0x80u : 0u);
-        } else if (kLegacy && (y != y)) {
-          c = 0x30u;   // a NaN product: none of the reference's comparisons holds (see fp8_encode_legacy)
-        } else {
-          continue;
-        }
-        o = (o & ~(0xFFu << (8 * k))) | (c << (8 * k));
+        const bool redo = kLegacy ? !(y >= 0.015625f) : (y < 0.015625f);
+        // out of line on purpose: in line, the compiler predicates all 32 copies of the arm and every warp that meets
+        // one small element executes them all (measured: 0.32 of the HBM rate on SwiGLU outputs against 0.71)
+        if (redo) o = (o & ~(0xFFu << (8 * k))) | (fp8_encode_exact<kLegacy>(x, inv) << (8 * k));
       }
       out[i] = o;
     }

@@ -43,8 +43,12 @@
  * src/sage_attention.rs:510-543) wrote on a B200 with row_size = 128
  * (tests/golden/int8_reference_sage_sm100.npz).  The reference has no
  * per-128-block FP8 mode: that variant is the pinned encoder applied to
- * x * (1/scale) with scale = absmax/448, and as a composition it has no
- * reference output to be held against ("parity unpinned" for per-block FP8).
+ * x * (1/scale) with scale = absmax/448, and it is held to what the reference's
+ * own kernel wrote on a B200 when it was launched once per 128-element block
+ * with that block's 1/scale (tests/golden/fp8_b128_reference_kernel_sm100.npz).
+ * The FP8 weight decoder with transpose is held to what the reference's
+ * flame_fused_dequant_transpose_bf16 wrote on a B200
+ * (tests/golden/fp8_weight_reference_kernel_sm100.npz).
  * The uncompressed BF16 round trip is pinned by the reference test at
  * src/activation_offload.rs:843-889.
  */
