@@ -995,7 +995,9 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a replica that failed never reaches the next barrier: the others give up after three minutes instead of ten
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     lib = _lib.lib()  # raises if the CUDA library is missing: there is no fallback
 
     from flame_b200 import replicas

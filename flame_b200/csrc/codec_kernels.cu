@@ -289,9 +289,19 @@ __device__ __forceinline__ uint32_t fp8_encode_pair_fast(float ylo_abs, float yh
   uint32_t h;
   asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(yhi_abs), "f"(ylo_abs));
   const __half2 hh = *reinterpret_cast<const __half2*>(&h);
-  const uint32_t sat = __hge2_mask(hh, __half2half2(__ushort_as_half((unsigned short)0x5BC0)));  // 248.0
   min_all = kNanPropagates ? __hmin2_nan(min_all, hh) : __hmin2(min_all, hh);  // default: a NaN lane is ignored
+#ifdef FLAME_FP8_FMA_SATURATE
+  // The same NaN for magnitudes from 248 up, made on the FMA pipe instead of with a compare mask on the ALU pipe:
+  // d = clamp(8h - 1983, 0, 1) is 1 from 248 up and 0 below (FP16 steps by 1/8 there); h + d*65504 overflows to
+  // +inf when d = 1 and is h when d = 0; z*0 + z turns that infinity into NaN and leaves every finite z alone.
+  const __half2 d = __hfma2_sat(hh, __float2half2_rn(8.0f), __float2half2_rn(-1983.0f));
+  const __half2 z1 = __hfma2(d, __float2half2_rn(65504.0f), hh);
+  const __half2 z = __hfma2(z1, __float2half2_rn(0.0f), z1);
+  const uint32_t h2 = *reinterpret_cast<const uint32_t*>(&z) | 0x00010001u;
+#else
+  const uint32_t sat = __hge2_mask(hh, __half2half2(__ushort_as_half((unsigned short)0x5BC0)));  // 248.0
   const uint32_t h2 = h | 0x00010001u | sat;
+#endif
   uint16_t c;
   asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(c) : "r"(h2));
   return c;  // low byte = code(ylo), high byte = code(yhi); bit 7 may be set on saturated lanes
@@ -1107,33 +1117,19 @@ __device__ __forceinline__ void st_plain32(void* p, const U32x8& r) {  // the ne
 }
 
 // RMSNorm of src/cuda/fused_rms_norm.cu:26-80: rstd = rsqrt(mean(x^2) + eps), y = bf16((x * rstd) * w), fp32
-// arithmetic.  One thread block per row; lane t keeps elements [16t, 16t+16) in registers from the one load to
-// the stores.  kCodec 0 writes y only.
+// arithmetic.  A thread block takes rows blockIdx.x, blockIdx.x + gridDim.x, ...; lane t keeps elements
+// [16t, 16t+16) of the row in registers from the one load to the stores, the weights stay in registers across rows,
+// and the next row's load is issued before the current row is reduced, so that the row-wide reduction (shuffles,
+// one barrier) runs beside a load in flight.  The two buffers of warp sums take turns: a buffer is written again
+// only after every thread has passed the barrier of the row in between.  kCodec 0 writes y only.
 template <int kCodec, bool kFlag>
 __global__ void __launch_bounds__(1024)
 rmsnorm_quant_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, uint16_t* __restrict__ y,
-                     uint8_t* __restrict__ codes, float* __restrict__ scales, float* __restrict__ rstd_out, uint32_t cols, float eps) {
-  __shared__ float warp_sums[32];
+                     uint8_t* __restrict__ codes, float* __restrict__ scales, float* __restrict__ rstd_out, uint32_t rows, uint32_t cols, float eps) {
+  __shared__ float warp_sums[2][32];
   const int tid = threadIdx.x;
   const bool live = (uint32_t)tid < cols / kLaneElems;
-  const size_t e0 = (size_t)blockIdx.x * cols + (size_t)tid * kLaneElems;
-  U32x8 r;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) r.v[i] = 0u;
-  if (live) r = ld_stream32(x + e0);
-  float v[kLaneElems];
-  unpack16(r, v);
-  float s = 0.0f;
-#pragma unroll
-  for (int i = 0; i < kLaneElems; ++i) s = __fmaf_rn(v[i], v[i], s);
-#pragma unroll
-  for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, d);
-  if ((tid & 31) == 0) warp_sums[tid >> 5] = s;
-  __syncthreads();
-  float tot = 0.0f;  // every thread adds the warp sums in the same order: one value for the whole row
-  for (int k = 0; k < (int)(blockDim.x >> 5); ++k) tot += warp_sums[k];
-  const float rstd = rsqrtf(__fadd_rn(__fdiv_rn(tot, (float)cols), eps));
-  if (rstd_out && tid == 0) rstd_out[blockIdx.x] = rstd;
+  const int nwarps = (int)(blockDim.x >> 5);
   U32x8 wr;
 #pragma unroll
   for (int i = 0; i < 8; ++i) wr.v[i] = 0u;
@@ -1142,19 +1138,41 @@ rmsnorm_quant_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict_
     const uint4 a = __ldg(wp), b = __ldg(wp + 1);
     wr.v[0] = a.x; wr.v[1] = a.y; wr.v[2] = a.z; wr.v[3] = a.w; wr.v[4] = b.x; wr.v[5] = b.y; wr.v[6] = b.z; wr.v[7] = b.w;
   }
-  float wv[kLaneElems];
-  unpack16(wr, wv);
-  U32x8 o;
+  uint32_t row = blockIdx.x;
+  U32x8 nxt;
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
-    o.v[i] = pack_bf16x2(__fmul_rn(__fmul_rn(v[2 * i], rstd), wv[2 * i]), __fmul_rn(__fmul_rn(v[2 * i + 1], rstd), wv[2 * i + 1]));
-  if (live) st_plain32(y + e0, o);
-  if (kCodec != 0) {
-    float scale;
-    const uint4 c = compress_lane<kCodec == 0 ? kCodecInt8 : kCodec, kFlag>(o, scale);  // dead lanes hold zeros and sit in groups of their own
-    if (live) {
-      __stcs(reinterpret_cast<uint4*>(codes + e0), c);
-      if ((tid & (kLanesPerBlock - 1)) == 0) scales[e0 / 128] = scale;
+  for (int i = 0; i < 8; ++i) nxt.v[i] = 0u;
+  if (live && row < rows) nxt = ld_stream32(x + (size_t)row * cols + (size_t)tid * kLaneElems);
+  for (int parity = 0; row < rows; row += gridDim.x, parity ^= 1) {
+    const U32x8 r = nxt;
+    const uint32_t next_row = row + gridDim.x;
+    if (live && next_row < rows) nxt = ld_stream32(x + (size_t)next_row * cols + (size_t)tid * kLaneElems);
+    const size_t e0 = (size_t)row * cols + (size_t)tid * kLaneElems;
+    float v[kLaneElems];
+    unpack16(r, v);
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kLaneElems; ++i) s = __fmaf_rn(v[i], v[i], s);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, d);
+    if ((tid & 31) == 0) warp_sums[parity][tid >> 5] = s;
+    __syncthreads();
+    float tot = 0.0f;  // every thread adds the warp sums in the same order: one value for the whole row
+    for (int k = 0; k < nwarps; ++k) tot += warp_sums[parity][k];
+    const float rstd = rsqrtf(__fadd_rn(__fdiv_rn(tot, (float)cols), eps));
+    if (rstd_out && tid == 0) rstd_out[row] = rstd;
+    U32x8 o;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      o.v[i] = pack_bf16x2(__fmul_rn(__fmul_rn(v[2 * i], rstd), bf16lo(wr.v[i])), __fmul_rn(__fmul_rn(v[2 * i + 1], rstd), bf16hi(wr.v[i])));
+    if (live) st_plain32(y + e0, o);
+    if (kCodec != 0) {
+      float scale;
+      const uint4 c = compress_lane<kCodec == 0 ? kCodecInt8 : kCodec, kFlag>(o, scale);  // dead lanes hold zeros and sit in groups of their own
+      if (live) {
+        __stcs(reinterpret_cast<uint4*>(codes + e0), c);
+        if ((tid & (kLanesPerBlock - 1)) == 0) scales[e0 / 128] = scale;
+      }
     }
   }
 }
@@ -1224,9 +1242,16 @@ cudaError_t launch_rmsnorm_quant(int codec, unsigned flags, const void* x, const
   if (!aligned(x, 32) || !aligned(w, 16) || !aligned(y, 16) || (codec != 0 && (!aligned(codes, 16) || !aligned(scales, 4)))) return cudaErrorInvalidValue;
   const int threads = (int)((cols / kLaneElems + 31) / 32 * 32);
   return by_codec(codec, flags, [&](auto c, auto f) {
-    rmsnorm_quant_kernel<decltype(c)::value, decltype(f)::value><<<(unsigned)rows, threads, 0, stream>>>(
+    auto kern = rmsnorm_quant_kernel<decltype(c)::value, decltype(f)::value>;
+    // Every block resident at once and the same number of rows for each (as nearly as the row count allows).
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, 0) != cudaSuccess || per_sm <= 0) per_sm = 1;
+    const size_t resident = (size_t)sm_count() * (size_t)per_sm;
+    const size_t rows_per_block = (rows + resident - 1) / resident;
+    const unsigned grid = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
+    kern<<<grid, threads, 0, stream>>>(
         static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(w), static_cast<uint16_t*>(y),
-        static_cast<uint8_t*>(codes), static_cast<float*>(scales), static_cast<float*>(rstd_out), (uint32_t)cols, eps);
+        static_cast<uint8_t*>(codes), static_cast<float*>(scales), static_cast<float*>(rstd_out), (uint32_t)rows, (uint32_t)cols, eps);
     return cudaGetLastError();
   });
 }

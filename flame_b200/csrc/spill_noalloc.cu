@@ -7,8 +7,15 @@
 // (cudaFree stalls the whole device, and either call can fail once the job
 // has claimed all memory).  The pool and the plain codec entry points need a
 // device staging buffer from somebody.  This entry point brings its own: a
-// fixed array that is part of the library image, so every GPU that loads the
-// library holds kScratchBytes of it from load until the process exits.
+// fixed array that is part of the library image, so every GPU that uses the
+// library holds kScratchBytes of it until the process exits.
+//
+// "Uses", not "opens": the CUDA runtime loads a library's kernels and static
+// device arrays lazily, at the first cudaGetSymbolAddress, launch or occupancy
+// query on a device, and that loading takes device memory.  A caller that needs
+// the no-allocation property at the moment of need therefore makes one small
+// warm-up call per device at start-up (each codec, an aligned and an unaligned
+// input), while memory is still there to be had; from then on a call takes none.
 //
 // The price is a size limit and shared state: tensors of more than
 // FLAME_ACT_NOALLOC_MAX_ELEMS elements are refused, and because every call
@@ -26,7 +33,7 @@ constexpr size_t kMaxElems = FLAME_ACT_NOALLOC_MAX_ELEMS;
 // packed size of the largest accepted tensor: codes | pad to 256 B | one fp32 scale per 128 elements
 constexpr size_t kScratchBytes = ((kMaxElems + 255) / 256) * 256 + 4 * ((kMaxElems + 127) / 128);
 
-// Lives in device memory of every GPU that loads this library.  In host code
+// Lives in device memory of every GPU on which this library has been used.  In host code
 // this name is only a stand-in for the symbol, not a device address: kernels
 // and copies must be given the address that cudaGetSymbolAddress returns.
 static __device__ __align__(256) unsigned char g_spill_scratch[kScratchBytes];

@@ -225,7 +225,7 @@ CAPPED_PLAN_INTERFERENCE = 0.065
 
 def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
                      arms=("offload_int8", "capped", "deferred", "offload_bf16", "recompute", "fused"), custom=(),
-                     resident_budget_blocks: int = 8, sync=None, cap_pct: float = 4.0) -> dict:
+                     resident_budget_blocks: int = 8, sync=None, cap_pct: float = 3.5) -> dict:
     """Step time of each arm relative to resident activations.  Returns a JSON-ready dict.
 
     ``sync``: called before the link probe and before every timed arm.  With several replicas it is a barrier, so
