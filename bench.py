@@ -866,7 +866,7 @@ def run_overhead_replicas(torch, dev, rank: int, world: int, barrier, gather, st
     the resident one."""
     from flame_b200.dit_workload import measure_overhead
 
-    o = measure_overhead(dev, steps=steps, warmup=2, arms=("capped",), sync=barrier)
+    o = measure_overhead(dev, steps=steps, warmup=2, arms=("capped", "deferred_int8"), sync=barrier)
     keys = ("ms_per_step", "overhead_pct", "overhead_pct_vs_mean_baseline", "held_after_forward_gb", "peak_mem_gb")
     mine = o.get("offload_int8_capped", {})
     out = {"replicas": world, "model": o["model"], "cap_pct": o.get("cap_pct"), "interference": o.get("interference"),
@@ -882,6 +882,12 @@ def run_overhead_replicas(torch, dev, rank: int, world: int, barrier, gather, st
     out["planned_blocks_offloaded"] = [int(v) for v in offl]
     out["planned_blocks_recomputed"] = [int(v) for v in reco]
     out["planned_freed_after_forward_gb"] = [round(out["resident_held_after_forward_gb"] - v, 3) for v in out["planned_held_after_forward_gb"]]
+    dfr = o.get("offload_int8_all_deferred", {})
+    # the other adaptive arm: every block handed to a deferred pool, which sends out what the link carries beside forward
+    out["deferred_ms_per_step"] = [round(v, 3) for v in gather(float(dfr.get("ms_per_step", float("nan"))))]
+    out["deferred_overhead_pct_vs_mean_baseline"] = [round(v, 2) for v in gather(float(dfr.get("overhead_pct_vs_mean_baseline", float("nan"))))]
+    out["deferred_freed_after_forward_gb"] = [round(out["resident_held_after_forward_gb"] - v, 3) for v in gather(float(dfr.get("held_after_forward_gb", float("nan"))))]
+    out["deferred_tensors_sent_out_per_step"] = [round(v, 1) for v in gather(float(dfr.get("tensors_pushed_per_step", 0.0)) - float(dfr.get("tensors_used_in_place_per_step", 0.0)))]
     out["rank0"] = {"plan": mine.get("blocks"), "plan_est_ms": mine.get("plan_est_ms"), "offloaded_gb_per_step": mine.get("offloaded_gb_per_step"),
                     "link_gb_per_step": mine.get("link_gb_per_step")}
     out["overhead_pct_worst_replica"] = max(out["planned_overhead_pct_vs_mean_baseline"])

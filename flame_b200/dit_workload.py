@@ -320,12 +320,13 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
         r["plan_resident_gb"] = round(p.resident_bytes / 1e9, 3)
         out["offload_int8_capped"] = r
         out["cap_pct"], out["interference"] = cap_pct, CAPPED_PLAN_INTERFERENCE
-    if "deferred" in arms:
+    if "deferred" in arms or "deferred_int8" in arms:
         # Every block handed to the pool; a deferred pool sends out what the link carries beside the forward pass
         # and backward uses the rest where it is.  No plan, no budget: the link decides.
         one_block = int(saved_bytes * 0.52)
         out["offload_int8_all_deferred"] = run_arm("offload_int8_all_deferred", [Decision.OFFLOAD_INT8] * blocks,
                                                    OffloadCompression.INT8_B128, deferred_bytes=one_block, d2h_piece=DEFERRED_D2H_PIECE_BYTES)
+    if "deferred" in arms:
         out["offload_bf16_all_deferred"] = run_arm("offload_bf16_all_deferred", [Decision.OFFLOAD_BF16] * blocks,
                                                    OffloadCompression.NONE, deferred_bytes=saved_bytes, d2h_piece=DEFERRED_D2H_PIECE_BYTES)
     if "offload_bf16" in arms:
