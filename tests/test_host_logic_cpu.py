@@ -1,4 +1,5 @@
 """Host-side bookkeeping that needs no GPU: the producers' hand-over registry and saved-tensor keys."""
+import pytest
 import torch
 
 from flame_b200 import checkpoint as ckpt
@@ -51,3 +52,26 @@ def test_without_a_pool_the_offload_arm_is_the_recompute_arm_on_cpu():
     lin(x).relu().sum().backward()
     assert torch.equal(g1, x.grad)
     assert ckpt.activation_offload_pool() is None
+
+
+def test_bench_host_helpers_need_no_gpu():
+    """bench.py's helpers that read the host: available memory, the PCIe description of a device that is not there,
+    and the table of pool settings swept under shared links."""
+    import importlib.util
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    avail = bench.host_mem_available_bytes()
+    assert avail is None or avail > (1 << 20)
+    info = bench.pcie_info(torch, 0)
+    assert isinstance(info, dict) and ("error" in info or "bdf" in info)
+    labels = [row[0] for row in bench.LINKSWEEP]
+    assert len(set(labels)) == len(labels) and labels[0].startswith("default")
+    for _, chunk_mb, flags, piece_mb, tile_chunks in bench.LINKSWEEP:
+        assert (chunk_mb << 20) % (64 << 10) == 0 and flags in (0, 1, 4) and piece_mb >= 0 and tile_chunks >= 1
+    comp, deq = bench.roofline_entries("int8", q_ms=1.0, d_ms=2.0, elems=1 << 20, launches=4)
+    assert comp["bound"] == deq["bound"] == "hbm" and comp["achieved"] == round(3.03125 * (1 << 20) / 1e-3 * 1e-9, 1)
+    assert comp["frac"] == round(comp["achieved"] / comp["peak"], 4) and deq["achieved"] * 2 == pytest.approx(comp["achieved"], rel=1e-3)
