@@ -965,8 +965,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--codec", choices=["int8", "fp8", "none"], default="int8")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--chunk-mb", type=int, default=16)
-    ap.add_argument("--tile-chunks", type=int, default=8)
+    ap.add_argument("--chunk-mb", type=int, default=32, help="pipeline chunk in MiB of source; 32 measured 2 percent above 16 on the DiT step's tensors at one GPU, no different at two")
+    ap.add_argument("--tile-chunks", type=int, default=4)
     ap.add_argument("--d2h-piece-mb", type=float, default=0.0, help="issue device-to-host copies in pieces of this size (0 = whole chunks)")
     ap.add_argument("--host-alloc-flags", type=int, default=0, help="cudaHostAlloc flags of the pinned slab (4 = write-combined)")
     ap.add_argument("--waves", type=int, default=0, help="offload and restore a step's tensors in this many waves (0 = as few as the host's memory allows)")

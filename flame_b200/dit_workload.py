@@ -224,7 +224,7 @@ CAPPED_PLAN_INTERFERENCE = 0.065
 
 
 def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
-                     arms=("offload_int8", "capped", "deferred", "offload_bf16", "recompute", "fused"), custom=(),
+                     arms=("offload_int8", "capped", "timed", "deferred", "offload_bf16", "recompute", "fused"), custom=(),
                      resident_budget_blocks: int = 8, sync=None, cap_pct: float = 3.5) -> dict:
     """Step time of each arm relative to resident activations.  Returns a JSON-ready dict.
 
@@ -313,8 +313,15 @@ def measure_overhead(device, steps: int = 3, warmup: int = 3, blocks: int = 20,
         cap_ms = cap_pct / 100.0 * base_ms
         p = plan_blocks(blk, d2h_gbs=link.d2h_gbs, h2d_gbs=link.h2d_gbs, offload=Decision.OFFLOAD_INT8,
                         interference=CAPPED_PLAN_INTERFERENCE, overhead_cap_ms=cap_ms)
-        r = run_arm("offload_int8_capped", p.decisions, OffloadCompression.INT8_B128 if Decision.OFFLOAD_INT8 in p.decisions else None,
-                    deferred_bytes=ISSUE_OFF_THREAD, d2h_piece=DEFERRED_D2H_PIECE_BYTES, collect_timing=True)
+        capped_mode = OffloadCompression.INT8_B128 if Decision.OFFLOAD_INT8 in p.decisions else None
+        r = run_arm("offload_int8_capped", p.decisions, capped_mode, deferred_bytes=ISSUE_OFF_THREAD, d2h_piece=DEFERRED_D2H_PIECE_BYTES)
+        if capped_mode is not None and "timed" in arms:
+            # the same plan once more with the pool timing itself: where the restores cost the step (the event records
+            # this takes are themselves work for the training thread, so the overhead figure is the untimed arm's)
+            t = run_arm("offload_int8_capped_timed", p.decisions, capped_mode, deferred_bytes=ISSUE_OFF_THREAD,
+                        d2h_piece=DEFERRED_D2H_PIECE_BYTES, collect_timing=True)
+            r["timing_ms_per_step"] = t.get("timing_ms_per_step")
+            r["timing_arm_ms_per_step"] = t["ms_per_step"]
         r["plan_est_ms"] = {"stall": round(p.est_stall_ms, 2), "recompute": round(p.est_recompute_ms, 2),
                             "interference": round(p.est_interference_ms, 2), "cap": round(cap_ms, 2)}
         r["plan_resident_gb"] = round(p.resident_bytes / 1e9, 3)
