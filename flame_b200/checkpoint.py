@@ -420,6 +420,14 @@ class _Scheduler:
         if not self._backward_seen:
             self._hold(True)
         self._backward_seen = True
+        # Sources whose copy out has finished are let go as backward proceeds (the pool itself only looks when
+        # something is pushed, and nothing is pushed during backward): their memory is there for the gradients.
+        pool = _ACTIVATION_POOL
+        if pool is not None:
+            try:
+                pool.release_finished_sources()
+            except OffloadError:
+                pass
         for j in range(min(position, len(self.blocks) - 1), max(-1, position - 1 - self.prefetch_blocks), -1):
             ref = self.blocks[j]
             blk = ref() if ref is not None else None

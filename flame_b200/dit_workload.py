@@ -180,6 +180,11 @@ def _time_steps(model, opt, x, cos, sin, steps, warmup):
     m0 = torch.cuda.memory_allocated()
     loss = model(x, cos, sin).float().pow(2).mean()
     torch.cuda.synchronize()
+    pool = ckpt.activation_offload_pool()
+    if pool is not None:
+        if pool.stats()["pushes_queued"] == 0:  # nothing waits for its turn: only copies already on their way are awaited
+            pool.synchronize(60.0)              # (a pool that holds tensors back keeps them back, as in the timed steps)
+        pool.release_finished_sources()         # the pool lets go of a source when it next looks, which is at the next push
     held = torch.cuda.memory_allocated() - m0
     loss.backward()
     opt.step()
