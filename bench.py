@@ -317,6 +317,26 @@ def reference_gpu_path(args):
             out["kernels"]["fused_rms_norm_bf16_us"] = round(us, 2)
             out["kernels"]["fused_rms_norm_bf16_gbs"] = round(4.0 * TOKENS * HIDDEN / us * 1e-3, 1)
             del flush, yr
+        if hasattr(ref, "flame_fused_dequant_transpose_bf16"):   # its FP8 weight kernel (src/cuda/fused_dequant_transpose.cu) at the QKV weight's shape
+            m, n = 3 * HIDDEN, HIDDEN
+            wc = torch.randint(0, 0x78, (m, n), dtype=torch.uint8, device=dev)
+            wo = torch.empty(n, m, dtype=torch.bfloat16, device=dev)
+            flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+            ts = []
+            for k in range(25):
+                flush.zero_()
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record(transfer)
+                assert ref.flame_fused_dequant_transpose_bf16(wc.data_ptr(), wo.data_ptr(), 0.0123, m, n, tp) == 0
+                a1.record(transfer)
+                torch.cuda.synchronize()
+                if k >= 5:
+                    ts.append(a0.elapsed_time(a1) * 1e3)
+            ts.sort()
+            us = ts[len(ts) // 2]
+            out["kernels"]["fused_dequant_transpose_bf16_us"] = round(us, 2)
+            out["kernels"]["fused_dequant_transpose_bf16_gbs"] = round(3.0 * m * n / us * 1e-3, 1)
+            del flush, wc, wo
         for mode in ("fp8", "none"):
             slot_bytes = (max_bytes + 1) // 2 if mode == "fp8" else max_bytes
             host = [ref.flame_cuda_alloc_pinned_host(slot_bytes, 0) for _ in tensors]       # cudaHostAllocDefault, as the pool does
@@ -958,6 +978,61 @@ def run_linksweep(args, torch, dev, rank, world, barrier, max_over_ranks, gather
                               "gbs_per_replica": [round(2 * step_bytes / (v * 1e-3) * 1e-9, 1) for v in per], "pinned_bytes": pinned}), flush=True)
 
 
+def run_weight_kernel(args, torch, lib, dev):
+    """flame_fused_dequant_transpose_bf16 (FP8 weights [M,N] -> BF16 [N,M]) at the DiT block's weight shapes: CUDA-event
+    time per launch, L2 flushed before each, 1 B read + 2 B written per element against the measured HBM rate."""
+    hbm_peak, peak_kind = measured_peaks()
+    st = torch.cuda.current_stream()
+    sp = st.cuda_stream
+    g = torch.Generator(device=dev).manual_seed(0)
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    out = {"mode": "weightkernel", "unit": "GB/s of algorithmic bytes (3 per element)", "peak": hbm_peak, "peak_kind": f"of {peak_kind}",
+           "l2": "flushed before every launch"}
+    for name, (m, n) in (("attn.qkv.weight [9216,3072]", (3 * HIDDEN, HIDDEN)), ("attn.out.weight [3072,3072]", (HIDDEN, HIDDEN)),
+                         ("mlp.up.weight [18432,3072]", (6 * HIDDEN, HIDDEN)), ("mlp.down.weight [3072,9216]", (HIDDEN, 3 * HIDDEN)),
+                         ("odd shape [3001,1537] (element kernel)", (3001, 1537))):
+        codes = torch.randint(0, 0x78, (m, n), dtype=torch.uint8, device=dev, generator=g)
+        dst = torch.empty(n, m, dtype=torch.bfloat16, device=dev)
+
+        def fn():
+            assert lib.flame_fused_dequant_transpose_bf16(codes.data_ptr(), dst.data_ptr(), 0.0123, m, n, sp) == 0
+        for _ in range(5):
+            fn()
+        ts = []
+        for _ in range(30):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st); fn(); e1.record(st)
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        ts.sort()
+        us, alg = ts[len(ts) // 2], 3.0 * m * n
+        out[name] = {"us": round(us, 2), "gbs": round(alg / us * 1e-3, 1), "frac": round(alg / us * 1e-3 / hbm_peak, 3), "alg_bytes": int(alg)}
+        del codes, dst
+    # all four weights of a block back to back, as a block's expansion after its bytes have arrived
+    shapes = [(3 * HIDDEN, HIDDEN), (HIDDEN, HIDDEN), (6 * HIDDEN, HIDDEN), (HIDDEN, 3 * HIDDEN)]
+    sets = [[(torch.randint(0, 0x78, s, dtype=torch.uint8, device=dev, generator=g), torch.empty(s[1], s[0], dtype=torch.bfloat16, device=dev)) for s in shapes]
+            for _ in range(4)]
+
+    def block(k):
+        for (c, d), (m, n) in zip(sets[k % 4], shapes):
+            assert lib.flame_fused_dequant_transpose_bf16(c.data_ptr(), d.data_ptr(), 0.0123, m, n, sp) == 0
+    for k in range(8):
+        block(k)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(st)
+    for k in range(20):
+        block(k)
+    e1.record(st)
+    torch.cuda.synchronize()
+    elems = sum(m * n for m, n in shapes)
+    ms = e0.elapsed_time(e1) / 20
+    out["one block's four weights, 20 blocks back to back"] = {"us": round(ms * 1e3, 2), "gbs": round(3.0 * elems / ms * 1e-6, 1),
+                                                              "frac": round(3.0 * elems / ms * 1e-6 / hbm_peak, 3), "alg_bytes": int(3 * elems)}
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -977,7 +1052,7 @@ def main():
     ap.add_argument("--no-ref-gpu", action="store_true", help="--impl reference: skip timing the reference's own compiled CUDA files")
     ap.add_argument("--only", choices=["all", "value", "codec", "e2e"], default="all",
                     help="profiling: run only one timed region (codec = the device-resident compress/dequantise leg)")
-    ap.add_argument("--mode", choices=["bench", "sweep", "interference", "weights", "producers", "linksweep"], default="bench",
+    ap.add_argument("--mode", choices=["bench", "sweep", "interference", "weights", "producers", "linksweep", "weightkernel"], default="bench",
                     help="sweep: 1 MB..4 GB single tensor x codec x chunk size; interference: copies against HBM-bound kernels; "
                          "weights: block weights streamed host->device through the same pool")
     ap.add_argument("--sweep-max-mb", type=int, default=4096)
@@ -1025,6 +1100,7 @@ def main():
             run_linksweep(args, torch, dev, rank, world, barrier, max_over_ranks, gather)
         elif rank == 0:
             {"producers": lambda: run_producers(args, torch, lib, dev), "weights": lambda: run_weights(args, torch, dev),
+             "weightkernel": lambda: run_weight_kernel(args, torch, lib, dev),
              "interference": lambda: run_interference(args, torch, lib, dev)}[args.mode]()
         if world > 1:
             dist.destroy_process_group()
