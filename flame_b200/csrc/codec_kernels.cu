@@ -267,13 +267,6 @@ template <bool kLegacy>
 __device__ __noinline__ uint32_t fp8_encode_exact(float x, float inv) {
   return kLegacy ? fp8_encode_legacy(x, inv) : fp8_encode_ref_scaled(x, inv);
 }
-// The reference's arm for a magnitude y = |x| * inv under 2^-6 (src/cuda/fp8_quant.cu:28-33, 52-56), for the block codecs:
-// (int)(y * 512 + 0.5f) in binary32, at most 7; the sign is that of `val < 0`, so a product that is zero (a zero element of
-// either sign, or an underflow) encodes without sign.  Equal to fp8_encode_ref_scaled for such y; a fraction of its cost.
-__device__ __noinline__ uint32_t fp8_small_code(float y, float x) {
-  const uint32_t c = min(__float2uint_rz(__fadd_rn(__fmul_rn(y, 512.0f), 0.5f)), 7u);
-  return c | ((x < 0.0f && y > 0.0f) ? 0x80u : 0u);
-}
 __device__ __noinline__ uint32_t fp8_encode_ocp_scaled(float x, float inv) {
   uint16_t r;
   const float y = scaled(x, inv);
@@ -343,18 +336,17 @@ __device__ __forceinline__ void fp8_encode_words_ref(const uint32_t* raw, float 
       uint32_t settled = ((mag | 0x80808080u) - 0x09090909u) & 0x80808080u;
       if (kLegacy) settled &= ~((mag + 0x01010101u) & 0x80808080u);
       if (settled == 0x80808080u) continue;
-      // One candidate byte per word is the rule: walk the unsettled bytes instead of testing all four.
-      uint32_t todo = ~settled & 0x80808080u;
-      while (todo) {
-        const int k = (__ffs(todo) - 1) >> 3;                      // byte index 0..3
-        todo &= todo - 1;
-        const uint32_t rw = (k & 2) ? raw[2 * i + 1] : raw[2 * i];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (settled & (0x80u << (8 * k))) continue;
+        const uint32_t rw = raw[2 * i + (k >> 1)];
         const float x = (k & 1) ? bf16hi(rw) : bf16lo(rw);
         const float y = __fmul_rn(fabsf(x), inv);
         const bool redo = kLegacy ? !(y >= 0.015625f) : (y < 0.015625f);
-        // out of line on purpose: in line, the compiler predicates every copy of the arm and each warp that meets one
-        // small element executes them all (measured: 0.32 of the HBM rate on SwiGLU outputs against 0.7)
-        if (redo) o = (o & ~(0xFFu << (8 * k))) | ((kLegacy ? fp8_encode_exact<true>(x, inv) : fp8_small_code(y, x)) << (8 * k));
+        // out of line on purpose: in line, the compiler predicates all 32 copies of the arm and every warp that meets
+        // one small element executes them all (measured: 0.32 of the HBM rate on SwiGLU outputs against 0.7); walking
+        // the unsettled bytes with a loop and a cheaper helper for the small magnitudes measured slower as well
+        if (redo) o = (o & ~(0xFFu << (8 * k))) | (fp8_encode_exact<kLegacy>(x, inv) << (8 * k));
       }
       out[i] = o;
     }
