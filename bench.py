@@ -979,57 +979,72 @@ def run_linksweep(args, torch, dev, rank, world, barrier, max_over_ranks, gather
 
 
 def run_weight_kernel(args, torch, lib, dev):
-    """flame_fused_dequant_transpose_bf16 (FP8 weights [M,N] -> BF16 [N,M]) at the DiT block's weight shapes: CUDA-event
-    time per launch, L2 flushed before each, 1 B read + 2 B written per element against the measured HBM rate."""
+    """flame_fused_dequant_transpose_bf16 (FP8 weights [M,N] -> BF16 [N,M]) at the DiT block's weight shapes, 1 B read +
+    2 B written per element against the measured HBM rate.  Per shape: one launch between two CUDA events with the L2
+    flushed before it (`us`; the events of this GPU tick in steps of about 2 us and the figure holds the launch's own
+    start-up), and 20 launches back to back over rotating buffer sets that together exceed twice the L2 (`us_back_to_back`).
+    Then a block's four weights, 20 blocks back to back: one call per weight, and all four in one launch."""
+    from flame_b200._lib import WeightJob
     hbm_peak, peak_kind = measured_peaks()
     st = torch.cuda.current_stream()
     sp = st.cuda_stream
     g = torch.Generator(device=dev).manual_seed(0)
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
     out = {"mode": "weightkernel", "unit": "GB/s of algorithmic bytes (3 per element)", "peak": hbm_peak, "peak_kind": f"of {peak_kind}",
-           "l2": "flushed before every launch"}
+           "l2": "us: flushed before every launch; us_back_to_back: buffer sets rotate, more than 2 x L2 between two uses of one"}
+
+    def entry(us, alg):
+        return {"us": round(us, 2), "gbs": round(alg / us * 1e-3, 1), "frac": round(alg / us * 1e-3 / hbm_peak, 3)}
+
+    def timed(fn, reps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for k in range(reps):
+            fn(k)
+        e1.record(st)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
     for name, (m, n) in (("attn.qkv.weight [9216,3072]", (3 * HIDDEN, HIDDEN)), ("attn.out.weight [3072,3072]", (HIDDEN, HIDDEN)),
                          ("mlp.up.weight [18432,3072]", (6 * HIDDEN, HIDDEN)), ("mlp.down.weight [3072,9216]", (HIDDEN, 3 * HIDDEN)),
                          ("odd shape [3001,1537] (element kernel)", (3001, 1537))):
-        codes = torch.randint(0, 0x78, (m, n), dtype=torch.uint8, device=dev, generator=g)
-        dst = torch.empty(n, m, dtype=torch.bfloat16, device=dev)
+        alg = 3.0 * m * n
+        nsets = max(2, int(2 * 126e6 // alg) + 2)
+        sets = [(torch.randint(0, 0x78, (m, n), dtype=torch.uint8, device=dev, generator=g), torch.empty(n, m, dtype=torch.bfloat16, device=dev))
+                for _ in range(nsets)]
 
-        def fn():
-            assert lib.flame_fused_dequant_transpose_bf16(codes.data_ptr(), dst.data_ptr(), 0.0123, m, n, sp) == 0
-        for _ in range(5):
-            fn()
+        def fn(k):
+            c, d = sets[k % nsets]
+            assert lib.flame_fused_dequant_transpose_bf16(c.data_ptr(), d.data_ptr(), 0.0123, m, n, sp) == 0
+        for k in range(5):
+            fn(k)
         ts = []
-        for _ in range(30):
+        for k in range(30):
             flush.zero_()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(st); fn(); e1.record(st)
-            torch.cuda.synchronize()
-            ts.append(e0.elapsed_time(e1) * 1e3)
+            ts.append(timed(fn, 1))
         ts.sort()
-        us, alg = ts[len(ts) // 2], 3.0 * m * n
-        out[name] = {"us": round(us, 2), "gbs": round(alg / us * 1e-3, 1), "frac": round(alg / us * 1e-3 / hbm_peak, 3), "alg_bytes": int(alg)}
-        del codes, dst
+        out[name] = dict(entry(ts[len(ts) // 2], alg), alg_bytes=int(alg))
+        b2b = entry(timed(fn, 20 * nsets), alg)
+        out[name].update(us_back_to_back=b2b["us"], gbs_back_to_back=b2b["gbs"], frac_back_to_back=b2b["frac"], buffer_sets=nsets)
+        del sets
     # all four weights of a block back to back, as a block's expansion after its bytes have arrived
     shapes = [(3 * HIDDEN, HIDDEN), (HIDDEN, HIDDEN), (6 * HIDDEN, HIDDEN), (HIDDEN, 3 * HIDDEN)]
     sets = [[(torch.randint(0, 0x78, s, dtype=torch.uint8, device=dev, generator=g), torch.empty(s[1], s[0], dtype=torch.bfloat16, device=dev)) for s in shapes]
             for _ in range(4)]
+    tables = [(WeightJob * 4)(*[WeightJob(c.data_ptr(), d.data_ptr(), 0.0123, m, n, 0) for (c, d), (m, n) in zip(ws, shapes)]) for ws in sets]
 
     def block(k):
         for (c, d), (m, n) in zip(sets[k % 4], shapes):
             assert lib.flame_fused_dequant_transpose_bf16(c.data_ptr(), d.data_ptr(), 0.0123, m, n, sp) == 0
-    for k in range(8):
-        block(k)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(st)
-    for k in range(20):
-        block(k)
-    e1.record(st)
-    torch.cuda.synchronize()
+
+    def block_multi(k):
+        assert lib.flame_fused_dequant_transpose_bf16_multi(tables[k % 4], 4, sp) == 0
     elems = sum(m * n for m, n in shapes)
-    ms = e0.elapsed_time(e1) / 20
-    out["one block's four weights, 20 blocks back to back"] = {"us": round(ms * 1e3, 2), "gbs": round(3.0 * elems / ms * 1e-6, 1),
-                                                              "frac": round(3.0 * elems / ms * 1e-6 / hbm_peak, 3), "alg_bytes": int(3 * elems)}
+    for label, fn in (("one block's four weights, 20 blocks back to back", block), ("the same, one launch per block (_multi)", block_multi)):
+        for k in range(8):
+            fn(k)
+        out[label] = dict(entry(timed(fn, 20), 3.0 * elems), alg_bytes=int(3 * elems))
     print(json.dumps(out), flush=True)
 
 

@@ -47,6 +47,11 @@ class ActTensor(C.Structure):
     _fields_ = [("bf16", C.c_void_p), ("codes", C.c_void_p), ("scales", C.c_void_p), ("n", C.c_size_t)]
 
 
+class WeightJob(C.Structure):
+    _fields_ = [("input_fp8", C.c_void_p), ("output_bf16", C.c_void_p), ("scale", C.c_float), ("M", C.c_int32), ("N", C.c_int32),
+                ("reserved", C.c_int32)]
+
+
 class ActLaunchInfo(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("grid", "resident_per_sm", "tiles_per_block", "form")]
 
@@ -95,6 +100,7 @@ SIGNATURES = {
     "flame_bf16_to_fp8": (_i, [_vp, _vp, _f, _sz, _vp]),
     "flame_fp8_to_bf16": (_i, [_vp, _vp, _f, _sz, _vp]),
     "flame_fused_dequant_transpose_bf16": (_i, [_vp, _vp, _f, _i, _i, _vp]),
+    "flame_fused_dequant_transpose_bf16_multi": (_i, [C.POINTER(WeightJob), _i, _vp]),
     "flame_act_quant_int8_b128": (_i, [_vp, _vp, _vp, _sz, _u, _vp]),
     "flame_act_dequant_int8_b128": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "flame_act_quant_fp8_b128": (_i, [_vp, _vp, _vp, _sz, _u, _vp]),

@@ -13,8 +13,9 @@ into the slot.
 Weights that already are FP8 E4M3 bytes with one scale per tensor (the checkpoints the reference's inference path
 loads, src/ops/fused_inference.rs:86-175) stream as they are through an uncompressed pool, one byte per element over
 the link, and are expanded on the device when the block is awaited: ``flame_fp8_to_bf16`` for a weight used in its
-stored [M, N] orientation, ``flame_fused_dequant_transpose_bf16`` for one the GEMM wants as [N, M]
-(src/cuda/fused_dequant_transpose.cu), into BF16 buffers that belong to the device slot.
+stored [M, N] orientation, the kernel of ``flame_fused_dequant_transpose_bf16`` for those the GEMM wants as [N, M]
+(src/cuda/fused_dequant_transpose.cu; one launch for all such weights of a block through the ``_multi`` entry point),
+into BF16 buffers that belong to the device slot.
 """
 from __future__ import annotations
 
@@ -167,6 +168,9 @@ class BlockOffloader:
         buf = self._bufs[slot]
         torch = self._torch
         out, eoff = {}, 0
+        lib = _lib.lib()
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        jobs = []          # the block's transposed FP8 weights: one launch for all of them
         for name, shape, dtype, off, nbytes in self._layout[idx]:
             if dtype != torch.uint8:
                 out[name] = buf[off:off + nbytes].view(dtype).view(shape)
@@ -178,13 +182,17 @@ class BlockOffloader:
             m, n = shape
             dst = self._expanded[slot][eoff:eoff + 2 * nbytes].view(torch.bfloat16)
             eoff += (2 * nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
-            stream = torch.cuda.current_stream(self.device).cuda_stream
-            lib = _lib.lib()
-            rc = (lib.flame_fused_dequant_transpose_bf16(buf.data_ptr() + off, dst.data_ptr(), float(scale), m, n, stream) if transpose
-                  else lib.flame_fp8_to_bf16(buf.data_ptr() + off, dst.data_ptr(), float(scale), m * n, stream))
-            if rc != 0:
-                raise CudaError(f"BlockOffloader: FP8 weight expansion of {name} failed ({rc}): {_lib.last_error()}")
+            if transpose:
+                jobs.append(_lib.WeightJob(buf.data_ptr() + off, dst.data_ptr(), float(scale), m, n, 0))
+            else:
+                rc = lib.flame_fp8_to_bf16(buf.data_ptr() + off, dst.data_ptr(), float(scale), m * n, stream)
+                if rc != 0:
+                    raise CudaError(f"BlockOffloader: FP8 weight expansion of {name} failed ({rc}): {_lib.last_error()}")
             out[name] = dst.view(n, m) if transpose else dst.view(m, n)
+        if jobs:
+            rc = lib.flame_fused_dequant_transpose_bf16_multi((_lib.WeightJob * len(jobs))(*jobs), len(jobs), stream)
+            if rc != 0:
+                raise CudaError(f"BlockOffloader: FP8 weight expansion of block {idx} failed ({rc}): {_lib.last_error()}")
         return out
 
     def ensure_block(self, idx: int) -> Dict[str, "object"]:

@@ -120,6 +120,13 @@ int flame_fused_dequant_transpose_bf16(const void* input, void* output, float sc
   return (int)launch_fp8_dequant_transpose(input, output, scale, M, N, (cudaStream_t)stream, 0);
 }
 
+int flame_fused_dequant_transpose_bf16_multi(const FlameWeightJob* jobs, int count, void* stream) {
+  if (count <= 0) return 0;
+  if (!jobs) return (int)cudaErrorInvalidValue;
+  if (fault_fires(FLAME_OFFLOAD_FAULT_KERNEL)) return (int)cudaErrorLaunchFailure;
+  return (int)launch_fp8_dequant_transpose_jobs(jobs, count, (cudaStream_t)stream, 0);
+}
+
 // ---- per-128-block codecs --------------------------------------------------------
 
 static int quant_entry(int codec, const void* in, void* codes, void* scales, size_t n, unsigned flags, void* stream) {

@@ -304,7 +304,8 @@ __device__ __forceinline__ uint32_t fp8_encode_pair_fast(float ylo_abs, float yh
 //   common case  : every magnitude is 0 or >= 2^-6 and no source element is zero: hardware path,
 //                  sign = sign bit of x.
 //   zeros present: same codes, but a zero magnitude keeps sign 0 (`val < 0` is false for -0.0).
-//   a magnitude in (0, 2^-6): the reference's float formula decides; the lane is re-encoded exactly.
+//   a magnitude in (0, 2^-6): the hardware's sub-normal codes 1..7 are the reference's; an element whose fast code
+//                  is 0x00 or 0x08 is encoded again with the exact restatement.
 // kLegacy (the element-wise entry point): a NaN element also sends the lane to the exact arm, which
 // gives it the reference's 0x30; the block codecs keep NaN on the fast path (saturation code, sign of x).
 template <int NW, bool kLegacy = false>
@@ -320,8 +321,8 @@ __device__ __forceinline__ void fp8_encode_words_ref(const uint32_t* raw, float 
     out[i] = (mag & 0x7F7F7F7Fu) | (sgn & 0x80808080u);
   }
   // anything below 2^-6 (0x2400 in FP16)?  Zero counts: rare enough to be handled off the fast path.  The few
-  // elements concerned (zero, a magnitude in (0, 2^-6), and for the element-wise entry point NaN) are encoded
-  // again one by one with the exact restatement; every other byte of the fast path stands.
+  // elements concerned (zero, a magnitude under 2^-10 or in [7.5, 8) * 2^-9, and for the element-wise entry point
+  // NaN) are encoded again one by one with the exact restatement; every other byte of the fast path stands.
   const __half thr = __ushort_as_half((unsigned short)0x2400);
   const bool careful = kLegacy ? !__hge(__hmin_nan(__low2half(min_all), __high2half(min_all)), thr)
                                : __hlt(__hmin(__low2half(min_all), __high2half(min_all)), thr);
@@ -329,11 +330,14 @@ __device__ __forceinline__ void fp8_encode_words_ref(const uint32_t* raw, float 
 #pragma unroll
     for (int i = 0; i < NW / 2; ++i) {
       uint32_t o = out[i];
-      // Only a byte whose fast code is at most 0x08 (zero, the sub-normal codes and the smallest normal one) can
-      // belong to an element below 2^-6: (code | 0x80) - 9 keeps bit 7 for every other byte, without borrowing
-      // across bytes.  The element-wise entry point also has to look at NaN elements, which carry code 0x7F.
+      // Only a byte whose fast code is 0x00 or 0x08 can differ from the reference's: the hardware path rounds a magnitude in
+      // [7.5, 8) * 2^-9 up to the smallest normal code where the reference clamps it to 7; a zero product keeps sign 0
+      // whatever the element's sign; and the float just under 2^-10 gives 1 in the reference's `v * 512 + 0.5f` where exact
+      // half-up rounding gives 0.  The sub-normal codes 1..7 agree for every fp32 magnitude.  (code & 0x77) is zero for
+      // exactly those two codes: (that | 0x80) - 1 keeps bit 7 for every other byte, without borrowing across bytes.
+      // The element-wise entry point also has to look at NaN elements, which carry code 0x7F.
       const uint32_t mag = o & 0x7F7F7F7Fu;
-      uint32_t settled = ((mag | 0x80808080u) - 0x09090909u) & 0x80808080u;
+      uint32_t settled = (((mag & 0x77777777u) | 0x80808080u) - 0x01010101u) & 0x80808080u;
       if (kLegacy) settled &= ~((mag + 0x01010101u) & 0x80808080u);
       if (settled == 0x80808080u) continue;
 #pragma unroll

@@ -4,6 +4,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+struct FlameWeightJob;   // include/flame_offload.h
+
 namespace flame_b200 {
 
 // Same numbering as FLAME_OFFLOAD_COMPRESSION_INT8_B128 / _FP8_B128.
@@ -60,6 +62,7 @@ cudaError_t launch_swiglu_quant(int codec, unsigned flags, const void* gate_up, 
                                 size_t rows, size_t hidden, cudaStream_t stream, int max_ctas);
 // FP8 weights [M, N] -> BF16 [N, M] with the decoder of the reference's fused_dequant_transpose.cu (weight_kernels.cu).
 cudaError_t launch_fp8_dequant_transpose(const void* in_fp8, void* out_bf16, float scale, int M, int N, cudaStream_t stream, int max_ctas);
+cudaError_t launch_fp8_dequant_transpose_jobs(const ::FlameWeightJob* jobs, int count, cudaStream_t stream, int max_ctas);
 int set_max_ctas(int v);
 
 // Inspection hooks (tests): what the calling thread's last compress / dequantise launch chose, and a fresh

@@ -14,12 +14,17 @@
 // bytes in registers with byte permutes, decodes on the conversion hardware, and writes for each of its
 // eight columns the eight rows as one 16-byte store; the eight row groups make 128 contiguous bytes per
 // output row.  Requires M % 8 == 0, N % 8 == 0, an 8-byte aligned input and a 16-byte aligned output;
-// anything else takes the element-per-thread kernel.
+// anything else takes the element-per-thread kernel.  Several weights can share one launch (a job table in
+// the kernel's parameters); the grid is one wave of resident blocks in which every warp takes the same
+// number of tiles.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "codec_kernels.cuh"
+#include "../../include/flame_offload.h"
 
 namespace flame_b200 {
 namespace {
@@ -39,6 +44,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2_w(float lo, float hi) {
 // `__float2bfloat16`.  Where the hardware and the reference's decoder differ (exponent 15 with a mantissa of 1..6:
 // 288..448 to the hardware, NaN to the reference), `nan_bits` says so: bit 7 of byte k is set when code k is one of
 // the decoder's NaN codes.
+template <bool kNanCodes>
 __device__ __forceinline__ void decode4_weight(uint32_t w, uint32_t nan_bits, float scale, uint32_t& o0, uint32_t& o1) {
   uint32_t h01, h23;
   asm("{ .reg .b16 lo, hi;\n\t"
@@ -47,7 +53,7 @@ __device__ __forceinline__ void decode4_weight(uint32_t w, uint32_t nan_bits, fl
       "cvt.rn.f16x2.e4m3x2 %1, hi; }" : "=r"(h01), "=r"(h23) : "r"(w));
   const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&h01)), b = __half22float2(*reinterpret_cast<const __half2*>(&h23));
   float v0 = a.x, v1 = a.y, v2 = b.x, v3 = b.y;
-  if (nan_bits) {  // rare: weights do not normally hold these codes
+  if (kNanCodes) {
     const float qnan = __uint_as_float(0x7FC00000u);
     if (nan_bits & 0x00000080u) v0 = qnan;
     if (nan_bits & 0x00008000u) v1 = qnan;
@@ -71,14 +77,55 @@ __device__ __forceinline__ void transpose4x4_bytes(const uint32_t (&r)[4], uint3
   c[3] = __byte_perm(a1, b1, 0x7632);
 }
 
-__global__ void __launch_bounds__(kWThreads)
-fp8_dequant_transpose_tiles_kernel(const uint8_t* __restrict__ in, uint16_t* __restrict__ out, float scale,
-                                   int M, int N, uint32_t tiles_n, uint64_t tiles) {
+// A lane's 8x8 piece (row j: columns 0..3 in r[j].x, 4..7 in r[j].y) transposed, decoded and written: column c of the
+// piece is eight consecutive BF16 of output row c, one 16-byte store.
+template <bool kNanCodes>
+__device__ __forceinline__ void piece_out(const uint2 (&r)[8], float scale, uint16_t* dst, size_t M) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {       // columns 0..3, then 4..7
+    uint32_t lo[4], hi[4];                     // per column: rows 0..3 and rows 4..7 of the piece
+    { const uint32_t a[4] = {half ? r[0].y : r[0].x, half ? r[1].y : r[1].x, half ? r[2].y : r[2].x, half ? r[3].y : r[3].x}; transpose4x4_bytes(a, lo); }
+    { const uint32_t a[4] = {half ? r[4].y : r[4].x, half ? r[5].y : r[5].x, half ? r[6].y : r[6].x, half ? r[7].y : r[7].x}; transpose4x4_bytes(a, hi); }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint4 o;
+      decode4_weight<kNanCodes>(lo[c], kNanCodes ? nan_codes(lo[c]) : 0u, scale, o.x, o.y);
+      decode4_weight<kNanCodes>(hi[c], kNanCodes ? nan_codes(hi[c]) : 0u, scale, o.z, o.w);
+      __stcs(reinterpret_cast<uint4*>(dst + (size_t)(4 * half + c) * M), o);
+    }
+  }
+}
+
+// Up to kMaxWeightJobs weights in one launch: the tiles of all jobs form one range, which the warps of the grid share
+// round-robin.  A block of a transformer has a handful of weights of 10-60 M elements; one launch per weight leaves the
+// GPU ramping up and draining four times per block.
+constexpr int kMaxWeightJobs = 16;
+struct WeightJobs {
+  const uint8_t* in[kMaxWeightJobs];
+  uint16_t* out[kMaxWeightJobs];
+  uint32_t first_tile[kMaxWeightJobs + 1];   // first_tile[count] = all tiles (the launcher keeps a table under 2^31 tiles)
+  float scale[kMaxWeightJobs];
+  int M[kMaxWeightJobs], N[kMaxWeightJobs];
+  uint32_t tiles_n[kMaxWeightJobs];
+  int count;
+};
+
+__global__ void __launch_bounds__(kWThreads, 6)
+fp8_dequant_transpose_tiles_kernel(const __grid_constant__ WeightJobs T) {
   const int lane = threadIdx.x & 31, rg = lane >> 2, cg = lane & 3;
-  const uint64_t warp0 = (uint64_t)blockIdx.x * (kWThreads / 32) + (threadIdx.x >> 5);
-  const uint64_t nwarps = (uint64_t)gridDim.x * (kWThreads / 32);
-  for (uint64_t t = warp0; t < tiles; t += nwarps) {
-    const int tm = (int)(t / tiles_n), tn = (int)(t - (uint64_t)tm * tiles_n);
+  const uint32_t warp0 = blockIdx.x * (kWThreads / 32) + (threadIdx.x >> 5);
+  const uint32_t nwarps = gridDim.x * (kWThreads / 32);
+  const uint32_t tiles = T.first_tile[T.count];
+  int job = 0;
+  for (uint32_t t = warp0; t < tiles; t += nwarps) {
+    while (t >= T.first_tile[job + 1]) ++job;    // tiles only move forward
+    const uint8_t* __restrict__ in = T.in[job];
+    uint16_t* __restrict__ out = T.out[job];
+    const float scale = T.scale[job];
+    const int M = T.M[job], N = T.N[job];
+    const uint32_t tiles_n = T.tiles_n[job];
+    const uint32_t tj = t - T.first_tile[job];
+    const int tm = (int)(tj / tiles_n), tn = (int)(tj - (uint32_t)tm * tiles_n);
     const int row0 = tm * kTileRows + rg * 8, col0 = tn * kTileCols + cg * 8;
     if (row0 >= M || col0 >= N) continue;       // M % 8 == 0 and N % 8 == 0: a lane's 8x8 piece is inside or outside as a whole
     uint2 r[8];                                  // row j of the piece: columns 0..3 in .x, 4..7 in .y
@@ -86,19 +133,13 @@ fp8_dequant_transpose_tiles_kernel(const uint8_t* __restrict__ in, uint16_t* __r
 #pragma unroll
     for (int j = 0; j < 8; ++j) r[j] = __ldcs(reinterpret_cast<const uint2*>(src + (size_t)j * N));
     uint16_t* dst = out + (size_t)col0 * M + row0;
+    // Does the piece hold one of the decoder's NaN codes?  Weights normally do not: the test is made once per piece and
+    // the common path carries no per-element selects (as predicated code they were a quarter of all issued instructions).
+    uint32_t any_nan = 0;
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {       // columns 0..3, then 4..7
-      uint32_t lo[4], hi[4];                     // per column: rows 0..3 and rows 4..7 of the piece
-      { const uint32_t a[4] = {half ? r[0].y : r[0].x, half ? r[1].y : r[1].x, half ? r[2].y : r[2].x, half ? r[3].y : r[3].x}; transpose4x4_bytes(a, lo); }
-      { const uint32_t a[4] = {half ? r[4].y : r[4].x, half ? r[5].y : r[5].x, half ? r[6].y : r[6].x, half ? r[7].y : r[7].x}; transpose4x4_bytes(a, hi); }
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint4 o;
-        decode4_weight(lo[c], nan_codes(lo[c]), scale, o.x, o.y);
-        decode4_weight(hi[c], nan_codes(hi[c]), scale, o.z, o.w);
-        __stcs(reinterpret_cast<uint4*>(dst + (size_t)(4 * half + c) * M), o);
-      }
-    }
+    for (int j = 0; j < 8; ++j) any_nan |= nan_codes(r[j].x) | nan_codes(r[j].y);
+    if (any_nan == 0) piece_out<false>(r, scale, dst, (size_t)M);
+    else piece_out<true>(r, scale, dst, (size_t)M);
   }
 }
 
@@ -110,36 +151,88 @@ fp8_dequant_transpose_generic_kernel(const uint8_t* __restrict__ in, uint16_t* _
     const size_t m = e / N, n = e - m * N;
     const uint32_t w = in[e];
     uint32_t o0, o1;
-    decode4_weight(w, nan_codes(w) & 0x80u, scale, o0, o1);
+    decode4_weight<true>(w, nan_codes(w) & 0x80u, scale, o0, o1);
     out[n * M + m] = (uint16_t)(o0 & 0xFFFFu);
   }
 }
 
+// Resident blocks per SM of the tile kernel, asked once per device.
+int resident_tile_blocks_per_sm(int dev) {
+  static std::atomic<int> cached[64];
+  if (dev < 0 || dev >= 64) return 4;
+  int v = cached[dev].load(std::memory_order_relaxed);
+  if (v > 0) return v;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, fp8_dequant_transpose_tiles_kernel, kWThreads, 0) != cudaSuccess || v <= 0) v = 4;
+  cached[dev].store(v, std::memory_order_relaxed);
+  return v;
+}
+
 }  // namespace
+
+cudaError_t launch_fp8_dequant_transpose_jobs(const FlameWeightJob* jobs, int count, cudaStream_t stream, int max_ctas) {
+  if (count <= 0) return cudaSuccess;
+  if (!jobs) return cudaErrorInvalidValue;
+  for (int i = 0; i < count; ++i) {
+    if (jobs[i].M < 0 || jobs[i].N < 0) return cudaErrorInvalidValue;
+    if (jobs[i].M > 0 && jobs[i].N > 0 && (!jobs[i].input_fp8 || !jobs[i].output_bf16)) return cudaErrorInvalidValue;
+  }
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // One wave of resident blocks, every warp the same number of tiles (a grid of 8 blocks per SM where 6 fit ran a third of a
+  // second wave on an otherwise idle GPU).
+  uint64_t cap = (uint64_t)sms * (uint64_t)resident_tile_blocks_per_sm(dev);
+  if (max_ctas > 0 && (uint64_t)max_ctas < cap) cap = (uint64_t)max_ctas;
+  const uint64_t warps_per_block = kWThreads / 32;
+  WeightJobs T;
+  T.count = 0;
+  T.first_tile[0] = 0;
+  auto flush = [&]() -> cudaError_t {
+    if (T.count == 0) return cudaSuccess;
+    const uint64_t tiles = T.first_tile[T.count];
+    const uint64_t rounds = (tiles + cap * warps_per_block - 1) / (cap * warps_per_block);
+    uint64_t grid = (tiles + rounds * warps_per_block - 1) / (rounds * warps_per_block);
+    if (grid > cap) grid = cap;
+    fp8_dequant_transpose_tiles_kernel<<<(unsigned)grid, kWThreads, 0, stream>>>(T);
+    T.count = 0;
+    return cudaGetLastError();
+  };
+  for (int i = 0; i < count; ++i) {
+    const int M = jobs[i].M, N = jobs[i].N;
+    if (M == 0 || N == 0) continue;
+    const uint8_t* in = static_cast<const uint8_t*>(jobs[i].input_fp8);
+    uint16_t* out = static_cast<uint16_t*>(jobs[i].output_bf16);
+    const uint64_t job_tiles = (uint64_t)((M + kTileRows - 1) / kTileRows) * (uint64_t)((N + kTileCols - 1) / kTileCols);
+    const bool fast = (M % 8 == 0) && (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(in) & 7u) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0) &&
+                      job_tiles < (1ull << 30);
+    if (!fast) {
+      const size_t total = (size_t)M * N;
+      uint64_t grid = (total + kWThreads - 1) / kWThreads;
+      if (grid > (uint64_t)sms * 8) grid = (uint64_t)sms * 8;
+      fp8_dequant_transpose_generic_kernel<<<(unsigned)grid, kWThreads, 0, stream>>>(in, out, jobs[i].scale, M, N);
+      const cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+      continue;
+    }
+    if (T.count > 0 && (uint64_t)T.first_tile[T.count] + job_tiles >= (1ull << 31)) {
+      const cudaError_t e = flush();
+      if (e != cudaSuccess) return e;
+    }
+    const int j = T.count++;
+    T.in[j] = in; T.out[j] = out; T.scale[j] = jobs[i].scale; T.M[j] = M; T.N[j] = N;
+    T.tiles_n[j] = (uint32_t)((N + kTileCols - 1) / kTileCols);
+    T.first_tile[j + 1] = T.first_tile[j] + (uint32_t)job_tiles;
+    if (T.count == kMaxWeightJobs) {
+      const cudaError_t e = flush();
+      if (e != cudaSuccess) return e;
+    }
+  }
+  return flush();
+}
 
 cudaError_t launch_fp8_dequant_transpose(const void* in, void* out, float scale, int M, int N, cudaStream_t stream, int max_ctas) {
   if (M <= 0 || N <= 0) return cudaSuccess;
-  if (!in || !out) return cudaErrorInvalidValue;
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const bool fast = (M % 8 == 0) && (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(in) & 7u) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
-  if (fast) {
-    const uint32_t tiles_n = (uint32_t)((N + kTileCols - 1) / kTileCols);
-    const uint64_t tiles = (uint64_t)((M + kTileRows - 1) / kTileRows) * tiles_n;
-    uint64_t grid = (tiles + kWThreads / 32 - 1) / (kWThreads / 32);
-    uint64_t cap = (uint64_t)sms * 8;
-    if (max_ctas > 0 && (uint64_t)max_ctas < cap) cap = (uint64_t)max_ctas;
-    if (grid > cap) grid = cap;
-    fp8_dequant_transpose_tiles_kernel<<<(unsigned)grid, kWThreads, 0, stream>>>(static_cast<const uint8_t*>(in), static_cast<uint16_t*>(out), scale,
-                                                                                 M, N, tiles_n, tiles);
-  } else {
-    const size_t total = (size_t)M * N;
-    uint64_t grid = (total + kWThreads - 1) / kWThreads;
-    if (grid > (uint64_t)sms * 8) grid = (uint64_t)sms * 8;
-    fp8_dequant_transpose_generic_kernel<<<(unsigned)grid, kWThreads, 0, stream>>>(static_cast<const uint8_t*>(in), static_cast<uint16_t*>(out), scale,
-                                                                                   M, N);
-  }
-  return cudaGetLastError();
+  const FlameWeightJob job = {in, out, scale, M, N, 0};
+  return launch_fp8_dequant_transpose_jobs(&job, 1, stream, max_ctas);
 }
 
 }  // namespace flame_b200

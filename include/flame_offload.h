@@ -75,8 +75,25 @@ int flame_fp8_to_bf16(const void* input_u8, void* output_bf16, float scale, size
  * src/ops/fused_inference.rs:140-175): input [M, N] row-major FP8 bytes, output [N, M] row-major BF16,
  * out[n][m] = bf16_rn(dec(in[m][n]) * scale) with that file's decoder (sub-normals, exponent 15 with a zero
  * mantissa = 256, exponent 15 with any other mantissa = NaN), bit for bit under IEEE float semantics.
- * M == 0 or N == 0 returns 0 at once.  M % 8 == 0, N % 4 == 0 and 16-byte aligned pointers take the fast kernel. */
+ * M == 0 or N == 0 returns 0 at once.  M % 8 == 0, N % 8 == 0, an 8-byte aligned input and a 16-byte aligned
+ * output take the fast kernel. */
 int flame_fused_dequant_transpose_bf16(const void* input_fp8, void* output_bf16, float scale, int M, int N, void* stream);
+
+/* The same for several weights in one launch (new): what a block of a model needs expanded once its bytes have
+ * arrived.  The reference calls its kernel once per weight (src/ops/fused_inference.rs:140-175); a block's four to
+ * eight weights of 10-60 M elements each then start and drain the GPU once per weight.  Every job has the meaning
+ * of one flame_fused_dequant_transpose_bf16 call; jobs with M == 0 or N == 0 are skipped; a job that misses the
+ * fast kernel's conditions gets a launch of its own.  Outputs must not overlap each other or any input.
+ * count <= 0 returns 0 at once. */
+typedef struct FlameWeightJob {
+  const void* input_fp8;   /* [M, N] row-major E4M3 codes */
+  void* output_bf16;       /* [N, M] row-major BF16 */
+  float scale;
+  int M;
+  int N;
+  int reserved;            /* 0 */
+} FlameWeightJob;          /* 32 bytes */
+int flame_fused_dequant_transpose_bf16_multi(const FlameWeightJob* jobs, int count, void* stream);
 
 /* ------------------------------------------------------------------------
  * 3. Per-128-element-block codecs (new; they take the place of the two calls

@@ -42,6 +42,7 @@ def test_struct_sizes_match_the_header():
     assert C.sizeof(_lib.SlotInfo) == 40
     assert C.sizeof(_lib.PolicyTensor) == 24
     assert C.sizeof(_lib.PolicyInput) == 72
+    assert C.sizeof(_lib.WeightJob) == 32
 
 
 def test_packed_size_helpers():

@@ -45,6 +45,38 @@ def test_odd_shapes_and_pointers_take_the_element_kernel(cuda_device, m, n, io, 
         assert np.array_equal(_run(lib, codes, sc, m, n, cuda_device, io, oo), capi.fp8_dequant_transpose(codes, sc, m, n))
 
 
+def test_several_weights_in_one_launch(cuda_device):
+    """The multi entry point gives every job the bytes of a call of its own: fast and odd shapes mixed, empty jobs skipped,
+    more jobs than one launch's table holds, nothing written outside the outputs."""
+    import ctypes as C
+    lib = _lib.lib()
+    rng = np.random.default_rng(11)
+    shapes = [(64, 128), (7, 5), (72, 104), (0, 16), (200, 96), (8, 8)] + [(16 + 8 * k, 24 + 8 * (k % 5)) for k in range(18)] + [(1024, 3072)]
+    dev, ins, outs, jobs, want = cuda_device, [], [], [], []
+    for k, (m, n) in enumerate(shapes):
+        codes = rng.integers(0, 256, size=(m, n), dtype=np.uint8)
+        sc = SCALES[k % 4]
+        src = torch.from_numpy(codes.reshape(-1).copy()).to(dev) if m * n else torch.zeros(8, dtype=torch.uint8, device=dev)
+        dst = torch.full((m * n + 64,), 0x7F7F, dtype=torch.int16, device=dev)
+        ins.append(src); outs.append(dst)
+        jobs.append(_lib.WeightJob(src.data_ptr(), dst.data_ptr(), float(sc), m, n, 0))
+        want.append(capi.fp8_dequant_transpose(codes, sc, m, n) if m * n else None)
+    arr = (_lib.WeightJob * len(jobs))(*jobs)
+    assert lib.flame_fused_dequant_transpose_bf16_multi(arr, len(jobs), torch.cuda.current_stream(dev).cuda_stream) == 0
+    torch.cuda.synchronize(dev)
+    for (m, n), dst, w in zip(shapes, outs, want):
+        got = dst.cpu().numpy().view(np.uint16)
+        assert (got[m * n:] == 0x7F7F).all(), (m, n)
+        if w is not None:
+            assert np.array_equal(got[:m * n].reshape(n, m), w), (m, n)
+    assert lib.flame_fused_dequant_transpose_bf16_multi(None, 0, None) == 0
+    assert lib.flame_fused_dequant_transpose_bf16_multi(None, 2, None) == 1
+    bad = (_lib.WeightJob * 1)(_lib.WeightJob(None, None, 1.0, 8, 8, 0))
+    assert lib.flame_fused_dequant_transpose_bf16_multi(bad, 1, None) == 1
+    neg = (_lib.WeightJob * 1)(_lib.WeightJob(ins[0].data_ptr(), outs[0].data_ptr(), 1.0, -8, 8, 0))
+    assert lib.flame_fused_dequant_transpose_bf16_multi(neg, 1, None) == 1
+
+
 def test_empty_and_bad_arguments(cuda_device):
     lib = _lib.lib()
     assert lib.flame_fused_dequant_transpose_bf16(None, None, 1.0, 0, 16, None) == 0
