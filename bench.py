@@ -1008,7 +1008,7 @@ def run_weight_kernel(args, torch, lib, dev):
 
     for name, (m, n) in (("attn.qkv.weight [9216,3072]", (3 * HIDDEN, HIDDEN)), ("attn.out.weight [3072,3072]", (HIDDEN, HIDDEN)),
                          ("mlp.up.weight [18432,3072]", (6 * HIDDEN, HIDDEN)), ("mlp.down.weight [3072,9216]", (HIDDEN, 3 * HIDDEN)),
-                         ("odd shape [3001,1537] (element kernel)", (3001, 1537))):
+                         ("odd shape [3001,1537] (shared-memory fallback kernel)", (3001, 1537))):
         alg = 3.0 * m * n
         nsets = max(2, int(2 * 126e6 // alg) + 2)
         sets = [(torch.randint(0, 0x78, (m, n), dtype=torch.uint8, device=dev, generator=g), torch.empty(n, m, dtype=torch.bfloat16, device=dev))

@@ -14,7 +14,7 @@
 // bytes in registers with byte permutes, decodes on the conversion hardware, and writes for each of its
 // eight columns the eight rows as one 16-byte store; the eight row groups make 128 contiguous bytes per
 // output row.  Requires M % 8 == 0, N % 8 == 0, an 8-byte aligned input and a 16-byte aligned output;
-// anything else takes the element-per-thread kernel.  Several weights can share one launch (a job table in
+// anything else takes a kernel that moves 64 x 64 tiles through shared memory.  Several weights can share one launch (a job table in
 // the kernel's parameters); the grid is one wave of resident blocks in which every warp takes the same
 // number of tiles.
 #include <cuda_fp16.h>
@@ -143,16 +143,33 @@ fp8_dequant_transpose_tiles_kernel(const __grid_constant__ WeightJobs T) {
   }
 }
 
-// Any M, N and alignment: one element per thread, reads coalesced along N.
+// Any M, N and alignment: a thread block moves a tile of 64 x 64 codes through shared memory, so that the reads run
+// along N (32 consecutive bytes per warp and row) and the writes along M (32 consecutive BF16 per warp and output row).
+constexpr int kGenTile = 64;
 __global__ void __launch_bounds__(kWThreads)
-fp8_dequant_transpose_generic_kernel(const uint8_t* __restrict__ in, uint16_t* __restrict__ out, float scale, int M, int N) {
-  const size_t total = (size_t)M * N, stride = (size_t)gridDim.x * kWThreads;
-  for (size_t e = (size_t)blockIdx.x * kWThreads + threadIdx.x; e < total; e += stride) {
-    const size_t m = e / N, n = e - m * N;
-    const uint32_t w = in[e];
-    uint32_t o0, o1;
-    decode4_weight<true>(w, nan_codes(w) & 0x80u, scale, o0, o1);
-    out[n * M + m] = (uint16_t)(o0 & 0xFFFFu);
+fp8_dequant_transpose_generic_kernel(const uint8_t* __restrict__ in, uint16_t* __restrict__ out, float scale, int M, int N,
+                                     uint32_t tiles_n, uint32_t tiles) {
+  __shared__ uint8_t tile[kGenTile][kGenTile + 1];
+  for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+    const uint32_t tm = t / tiles_n, tn = t - tm * tiles_n;
+    const size_t m0 = (size_t)tm * kGenTile, n0 = (size_t)tn * kGenTile;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < kGenTile * kGenTile; i += kWThreads) {
+      const int r = i / kGenTile, c = i % kGenTile;
+      if (m0 + r < (size_t)M && n0 + c < (size_t)N) tile[r][c] = in[(m0 + r) * N + n0 + c];
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int i = threadIdx.x; i < kGenTile * kGenTile; i += kWThreads) {
+      const int c = i / kGenTile, r = i % kGenTile;
+      if (m0 + r < (size_t)M && n0 + c < (size_t)N) {
+        const uint32_t w = tile[r][c];
+        uint32_t o0, o1;
+        decode4_weight<true>(w, nan_codes(w) & 0x80u, scale, o0, o1);
+        out[(n0 + c) * M + m0 + r] = (uint16_t)(o0 & 0xFFFFu);
+      }
+    }
+    __syncthreads();
   }
 }
 
@@ -205,10 +222,11 @@ cudaError_t launch_fp8_dequant_transpose_jobs(const FlameWeightJob* jobs, int co
     const bool fast = (M % 8 == 0) && (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(in) & 7u) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0) &&
                       job_tiles < (1ull << 30);
     if (!fast) {
-      const size_t total = (size_t)M * N;
-      uint64_t grid = (total + kWThreads - 1) / kWThreads;
+      const uint64_t gt_n = ((uint64_t)N + kGenTile - 1) / kGenTile, gt = (((uint64_t)M + kGenTile - 1) / kGenTile) * gt_n;   // < 2^52 / 4096
+      if (gt >= (1ull << 32)) return cudaErrorInvalidValue;
+      uint64_t grid = gt;
       if (grid > (uint64_t)sms * 8) grid = (uint64_t)sms * 8;
-      fp8_dequant_transpose_generic_kernel<<<(unsigned)grid, kWThreads, 0, stream>>>(in, out, jobs[i].scale, M, N);
+      fp8_dequant_transpose_generic_kernel<<<(unsigned)grid, kWThreads, 0, stream>>>(in, out, jobs[i].scale, M, N, (uint32_t)gt_n, (uint32_t)gt);
       const cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return e;
       continue;

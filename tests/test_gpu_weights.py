@@ -37,8 +37,9 @@ def test_fast_kernel_equals_the_oracle(cuda_device, m, n):
         assert np.array_equal(_run(lib, codes, sc, m, n, cuda_device), capi.fp8_dequant_transpose(codes, sc, m, n)), (m, n, sc)
 
 
-@pytest.mark.parametrize("m,n,io,oo", [(7, 5, 0, 0), (33, 17, 0, 0), (40, 36, 1, 0), (40, 36, 0, 1), (30, 64, 0, 0), (64, 30, 0, 0), (1, 1, 3, 3)])
-def test_odd_shapes_and_pointers_take_the_element_kernel(cuda_device, m, n, io, oo):
+@pytest.mark.parametrize("m,n,io,oo", [(7, 5, 0, 0), (33, 17, 0, 0), (40, 36, 1, 0), (40, 36, 0, 1), (30, 64, 0, 0), (64, 30, 0, 0), (1, 1, 3, 3),
+                                         (65, 129, 0, 0), (200, 63, 5, 1), (1, 300, 0, 0), (300, 1, 0, 3), (131, 197, 2, 0)])
+def test_odd_shapes_and_pointers_take_the_fallback_kernel(cuda_device, m, n, io, oo):
     lib = _lib.lib()
     codes = np.random.default_rng(m + n + io).integers(0, 256, size=(m, n), dtype=np.uint8)
     for sc in (1.0, 0.37):
