@@ -60,6 +60,9 @@ ALG_BYTES_PER_ELEM = 3.03125  # 2 B read + 1 B code + 4/128 B scale (and the mir
 # proportion to the elements of a launch.  Below the algorithmic figure because the L2 still holds part of the
 # output when the kernel ends.
 NCU_TRAFFIC_PER_ELEM = {"compress": {"int8": 483.1e6 / 169869312, "fp8": 490.0e6 / 169869312}, "dequant": 458.1e6 / 169869312}
+# the FP8 weight kernel on an [18432, 3072] weight: 56.64 MB read + 57.5 MB written inside the launch (the other half of the
+# 113 MB output was still in the L2 when it ended)
+NCU_TRAFFIC_PER_WEIGHT_ELEM = (56.64e6 + 57.5e6) / 56623104
 PCIE_GEN5_X16_GBS = 63.0      # 32 GT/s x 16 lanes x 128/130 / 8
 TOKENS, HIDDEN, BLOCKS = 4608, 3072, 20
 # saved set of one block, as last dims: norm1 out, QKV, attention out, norm2 out, SwiGLU gate+up
@@ -978,6 +981,81 @@ def run_linksweep(args, torch, dev, rank, world, barrier, max_over_ranks, gather
                               "gbs_per_replica": [round(2 * step_bytes / (v * 1e-3) * 1e-9, 1) for v in per], "pinned_bytes": pinned}), flush=True)
 
 
+def run_weight_stream(torch, lib, dev, steps: int, warmup: int) -> dict:
+    """The weight-side reuse of the pool in short form, for the default line: FP8 E4M3 weights of DiT blocks (one byte per
+    element over the link, through an uncompressed pool) handed out as transposed BF16 by BlockOffloader, every block once in
+    forward and once in reverse order; and the expansion kernel alone on a block's four weights, back to back.  One expanded
+    weight is compared with the CPU restatement of the reference's decoder after the timed region."""
+    from flame_b200 import BlockOffloader, OffloadCompression
+    from flame_b200._lib import WeightJob
+    hbm_peak, peak_kind = measured_peaks()
+    g = torch.Generator(device=dev).manual_seed(7)
+    shapes = {"attn.qkv.weight": (3 * HIDDEN, HIDDEN), "attn.out.weight": (HIDDEN, HIDDEN),
+              "mlp.up.weight": (6 * HIDDEN, HIDDEN), "mlp.down.weight": (HIDDEN, 3 * HIDDEN)}
+    scale, nblocks = 0.0123, 6
+    blocks = [{k: torch.randint(0, 0x78, v, dtype=torch.uint8, device=dev, generator=g) | (torch.randint(0, 2, v, dtype=torch.uint8, device=dev, generator=g) << 7)
+               for k, v in shapes.items()} for _ in range(nblocks)]
+    probe = blocks[2]["attn.out.weight"].cpu().numpy()
+    elems = sum(m * n for m, n in shapes.values())
+    off = BlockOffloader(dev, blocks, OffloadCompression.NONE, chunk_bytes=32 << 20, fp8_weights={k: (scale, True) for k in shapes})
+    del blocks
+    torch.cuda.empty_cache()
+    order = list(range(nblocks)) + list(reversed(range(nblocks)))
+    stream = torch.cuda.current_stream()
+    sink = torch.zeros(1, dtype=torch.float32, device=dev)
+
+    def step():
+        off.prefetch_block(order[0])
+        for i, idx in enumerate(order):
+            w = off.await_block(idx)
+            if i + 1 < len(order):
+                off.prefetch_block(order[i + 1])
+            sink.add_(w["attn.out.weight"][0, 0].float())      # a consumer on the compute stream, so each block is really waited for
+    for _ in range(max(1, warmup)):
+        step()
+    torch.cuda.synchronize()
+    st0 = off.stats()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    st1 = off.stats()
+    link = (st1["bytes_link_in"] - st0["bytes_link_in"]) / steps
+    loaded = sum(1 for i, idx in enumerate(order) if i == 0 or order[i - 1] != idx)
+    got = off.ensure_block(2)["attn.out.weight"]
+    torch.cuda.synchronize()
+    from oracle import capi as oracle
+    m, n = shapes["attn.out.weight"]
+    ok = bool((got.view(torch.int16).cpu().numpy().view("uint16") == oracle.fp8_dequant_transpose(probe, scale, m, n)).all())
+    off.close()
+    # the expansion kernel alone: a block's four weights in one launch, 20 blocks back to back over four buffer sets (1.1 GB each way)
+    sets = [[(torch.randint(0, 0x78, s, dtype=torch.uint8, device=dev, generator=g), torch.empty(s[1], s[0], dtype=torch.bfloat16, device=dev)) for s in shapes.values()]
+            for _ in range(4)]
+    tables = [(WeightJob * 4)(*[WeightJob(c.data_ptr(), d.data_ptr(), scale, c.shape[0], c.shape[1], 0) for c, d in ws]) for ws in sets]
+    sp = stream.cuda_stream
+    for k in range(8):
+        assert lib.flame_fused_dequant_transpose_bf16_multi(tables[k % 4], 4, sp) == 0
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for k in range(20):
+        assert lib.flame_fused_dequant_transpose_bf16_multi(tables[k % 4], 4, sp) == 0
+    e1.record(stream)
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / 20
+    return {"workload": f"{nblocks} DiT blocks of FP8 E4M3 weights (qkv, out, up, down: {elems / 1e6:.1f} M codes per block), streamed host->device and "
+                        "expanded to transposed BF16; every block once forward and once in reverse per step",
+            "value": round(loaded * elems * 2 / (ms * 1e-3) * 1e-9, 2), "unit": "GB/s BF16-equivalent", "ms_per_step": round(ms, 3), "steps": steps,
+            "blocks_loaded_per_step": loaded, "h2d_link_gbs": round(link / (ms * 1e-3) * 1e-9, 2),
+            "h2d_frac_of_bound": round(link / (ms * 1e-3) * 1e-9 / PCIE_GEN5_X16_GBS, 3), "verified_against_oracle": ok,
+            "roofline": {"bound": "hbm", "kernel": "fp8_dequant_transpose_tiles_kernel", "achieved": round(3.0 * elems / us * 1e-3, 1), "peak": hbm_peak,
+                         "unit": "GB/s", "frac": round(3.0 * elems / us * 1e-3 / hbm_peak, 4), "peak_kind": f"of {peak_kind}", "traffic": int(elems * NCU_TRAFFIC_PER_WEIGHT_ELEM),
+                         "alg_bytes_per_launch": int(3 * elems), "avg_launch_us": round(us, 2),
+                         "leg": "a block's four weights in one launch, 20 launches back to back over four buffer sets"}}
+
+
 def run_weight_kernel(args, torch, lib, dev):
     """flame_fused_dequant_transpose_bf16 (FP8 weights [M,N] -> BF16 [N,M]) at the DiT block's weight shapes, 1 B read +
     2 B written per element against the measured HBM rate.  Per shape: one launch between two CUDA events with the L2
@@ -1064,6 +1142,7 @@ def main():
     ap.add_argument("--no-dit", action="store_true", help="skip the DiT training-step overhead measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-fp8-mixed", action="store_true", help="skip the FP8 mixed-activation-set block")
+    ap.add_argument("--no-weights", action="store_true", help="skip the FP8 weight-streaming block")
     ap.add_argument("--no-ref-gpu", action="store_true", help="--impl reference: skip timing the reference's own compiled CUDA files")
     ap.add_argument("--only", choices=["all", "value", "codec", "e2e"], default="all",
                     help="profiling: run only one timed region (codec = the device-resident compress/dequantise leg)")
@@ -1317,6 +1396,12 @@ def main():
             line["fp8_mixed"] = run_fp8_mixed(torch, lib, dev, steps=max(3, min(args.steps, 10)), warmup=3)
         except Exception as exc:
             line["fp8_mixed"] = {"error": f"{type(exc).__name__}: {exc}"}
+        torch.cuda.empty_cache()
+    if rank == 0 and world == 1 and full and not args.no_weights:
+        try:
+            line["weights_fp8"] = run_weight_stream(torch, lib, dev, steps=max(3, min(args.steps, 10)), warmup=3)
+        except Exception as exc:
+            line["weights_fp8"] = {"error": f"{type(exc).__name__}: {exc}"}
         torch.cuda.empty_cache()
     if rank == 0 and world == 1 and not args.no_cpu:
         gbs, cores, sample, _ = cpu_leg(12.0, args.codec)

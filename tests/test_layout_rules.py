@@ -41,7 +41,7 @@ def test_bench_uses_the_oracle_only_as_checker_and_cpu_baseline():
             if isinstance(node, ast.Call) and isinstance(node.func, ast.Name) and node.func.id == "reference_gpu_path":
                 callers.add(fn.name)
     # checkers (run after the timed loops), the CPU baseline, and the reference arm's own GPU path
-    assert users <= {"verify_against_oracle", "verify_restored", "run_fp8_mixed", "cpu_leg", "reference_gpu_path"}, users
+    assert users <= {"verify_against_oracle", "verify_restored", "run_fp8_mixed", "run_weight_stream", "cpu_leg", "reference_gpu_path"}, users
     assert not any(isinstance(n, (ast.Import, ast.ImportFrom)) and "oracle" in ast.dump(n) for n in tree.body), "no module-level import of the oracle"
     # the compiled reference files are timed by the --impl reference arm only, never by this library's arm
     assert callers == {"run_reference_arm"}, callers
