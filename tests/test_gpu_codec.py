@@ -467,3 +467,55 @@ def test_large_tensor_properties(cuda_device):
     want_c, want_s = capi.quant_int8_b128(G.bits_of(x[lo:hi]))
     assert np.array_equal(codes[lo:hi].cpu().numpy().view(np.int8), want_c)
     assert np.array_equal(scales[lo // 128: hi // 128].cpu().numpy(), want_s)
+
+
+def _randn_bf16_bits(n: int, device, seed: int) -> torch.Tensor:
+    """n BF16 values N(0,1) as an int16 tensor, made in pieces so that no fp32 copy of the whole exists."""
+    x = torch.empty(n, dtype=torch.bfloat16, device=device)
+    g = torch.Generator(device=device).manual_seed(seed)
+    piece = 1 << 27
+    for lo in range(0, n, piece):
+        hi = min(n, lo + piece)
+        x[lo:hi] = torch.randn(hi - lo, device=device, dtype=torch.float32, generator=g).to(torch.bfloat16)
+    return x
+
+
+@pytest.mark.parametrize("codec", ["int8", "fp8"])
+def test_more_than_2_to_the_32_elements_in_one_call(cuda_device, codec):
+    """2^32 + 128 * 1000 + 37 elements: element, block and tile indices beyond 32 bits.  The first tiles, the blocks on
+    both sides of element 2^32 and the ragged tail against the oracle; the whole tensor against the same tensor
+    compressed in two calls; the round trip within the codec's step per block, piece by piece."""
+    n = (1 << 32) + 128 * 1000 + 37
+    free, _ = torch.cuda.mem_get_info(cuda_device)
+    if free < (40 << 30):
+        pytest.skip("needs 40 GB of free device memory")
+    x = _randn_bf16_bits(n, cuda_device, 5)
+    codes, scales = G.quant(codec, x)
+    q_oracle = capi.quant_int8_b128 if codec == "int8" else capi.quant_fp8_b128
+    d_oracle = capi.dequant_int8_b128 if codec == "int8" else capi.dequant_fp8_b128
+    windows = [(0, 128 * 200), ((1 << 32) - 128 * 150, (1 << 32) + 128 * 150), ((1 << 31) - 128 * 64, (1 << 31) + 128 * 64), (n - 37 - 128 * 90, n)]
+    for lo, hi in windows:
+        wc, ws = q_oracle(G.bits_of(x[lo:hi]))
+        assert np.array_equal(codes[lo:hi].cpu().numpy(), wc.view(np.uint8)), (lo, hi)
+        assert np.array_equal(scales[lo // 128: (hi + 127) // 128].cpu().numpy().view(np.uint32), ws.view(np.uint32)), (lo, hi)
+    cut = (1 << 31) + 128 * 3
+    c0, s0 = G.quant(codec, x[:cut])
+    assert torch.equal(codes[:cut], c0) and torch.equal(scales[: cut // 128], s0)
+    del c0, s0
+    c1, s1 = G.quant(codec, x[cut:])
+    assert torch.equal(codes[cut:], c1) and torch.equal(scales[cut // 128:], s1)
+    del c1, s1
+    out = G.dequant(codec, codes, scales, n)
+    for lo, hi in windows:
+        want = d_oracle(codes[lo:hi].cpu().numpy().view(np.int8 if codec == "int8" else np.uint8), scales[lo // 128: (hi + 127) // 128].cpu().numpy())
+        assert np.array_equal(G.bits_of(out[lo:hi]), want), (lo, hi)
+    # size-independent property over the whole tensor: |x - restored| stays within one int8 step (scale) per block, and within
+    # the FP8 format's worst relative step of the block maximum (the reference's encoder sends [248, 448] to one code: 0.53)
+    full = n - n % 128
+    piece = 1 << 27
+    for lo in range(0, full, piece):
+        hi = min(full, lo + piece)
+        err = (out[lo:hi].float() - x[lo:hi].float()).abs().view(-1, 128).amax(dim=1)
+        sc = scales[lo // 128: hi // 128]
+        bound = sc if codec == "int8" else sc * 448.0 * 0.53
+        assert bool((err <= bound).all()), lo

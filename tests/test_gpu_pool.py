@@ -586,3 +586,34 @@ def test_collect_timing_reports_offload_restore_and_wait_spans(cuda_device):
         finally:
             pool.close()
             quiet.close()
+
+
+@pytest.mark.parametrize("mode", [INT8B, NONE])
+def test_one_tensor_of_more_than_4_gib_through_the_pool(cuda_device, mode):
+    """2^31 + 128 * 77 + 5 BF16 elements (4.3 GB) in one push: byte offsets beyond 32 bits in the slab, the chunk list and
+    the restore.  What comes back equals the codec applied on the device without the pool (int8), or the source."""
+    n = (1 << 31) + 128 * 77 + 5
+    free, _ = torch.cuda.mem_get_info(cuda_device)
+    if free < (30 << 30):
+        pytest.skip("needs 30 GB of free device memory")
+    x = torch.empty(n, dtype=torch.bfloat16, device=cuda_device)
+    g = torch.Generator(device=cuda_device).manual_seed(9)
+    for lo in range(0, n, 1 << 27):
+        hi = min(n, lo + (1 << 27))
+        x[lo:hi] = torch.randn(hi - lo, device=cuda_device, dtype=torch.float32, generator=g).to(torch.bfloat16)
+    pool = ActivationOffloadPool(cuda_device, 1, 2 * n, mode, chunk_bytes=32 << 20)
+    h = pool.push(x)
+    dst = torch.empty_like(x)
+    pool.pull_into(h, dst)
+    torch.cuda.synchronize()
+    if mode == INT8B:
+        codes, scales = G.quant("int8", x)
+        want = G.dequant("int8", codes, scales, n)
+        del codes, scales
+    else:
+        want = x
+    assert torch.equal(dst.view(torch.int16), want.view(torch.int16))
+    st = pool.stats()
+    assert st["bytes_logical_out"] == 2 * n and st["bytes_link_out"] == st["bytes_link_in"]
+    assert st["bytes_link_out"] == (capi.packed_bytes(n) if mode == INT8B else 2 * n)
+    pool.close()
