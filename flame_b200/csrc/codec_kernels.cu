@@ -282,8 +282,8 @@ __device__ __noinline__ uint32_t fp8_encode_ocp_scaled(float x, float inv) {
 // crossing one, and puts exact ties just above: round-to-nearest-even of that
 // equals round-half-up of |y|.  |y| >= 248 must give 0x7F: those lanes are made
 // NaN, which the converter encodes as 0x7F.  Zero gives 0.  `min_all` collects the
-// smallest magnitude seen, so that the caller can tell whether any lane needs
-// more care (see fp8_encode_words_ref).
+// smallest magnitude seen, for the element-wise entry point (see
+// fp8_encode_words_ref; the block codecs do not read it and the compiler drops it).
 template <bool kNanPropagates = false>
 __device__ __forceinline__ uint32_t fp8_encode_pair_fast(float ylo_abs, float yhi_abs, __half2& min_all) {
   uint32_t h;
@@ -300,17 +300,22 @@ __device__ __forceinline__ uint32_t fp8_encode_pair_fast(float ylo_abs, float yh
 }
 
 // NW words (two BF16 each) of one lane with the reference encoder: codes of x * inv, inv finite and positive.
-// The words carry the sign bits.
-//   common case  : every magnitude is 0 or >= 2^-6 and no source element is zero: hardware path,
-//                  sign = sign bit of x.
-//   zeros present: same codes, but a zero magnitude keeps sign 0 (`val < 0` is false for -0.0).
-//   a magnitude in (0, 2^-6): the hardware's sub-normal codes 1..7 are the reference's; an element whose fast code
-//                  is 0x00 or 0x08 is encoded again with the exact restatement.
-// kLegacy (the element-wise entry point): a NaN element also sends the lane to the exact arm, which
-// gives it the reference's 0x30; the block codecs keep NaN on the fast path (saturation code, sign of x).
+// The words carry the sign bits.  The hardware path gives every element its code and the sign bit of x; its
+// sub-normal codes 1..7 are the reference's for every binary32 magnitude.  Two codes can differ and are looked at
+// again:
+//   0x08: the hardware rounds a magnitude in [7.5, 8) * 2^-9 up to the smallest normal code, the reference clamps
+//         it to 7;
+//   0x00: a zero product keeps sign 0 whatever the element's sign (`val < 0` is false for -0.0), and the float just
+//         under 2^-10 gives 1 in the reference's `v * 512 + 0.5f` where exact half-up rounding gives 0.
+// (code & 0x77) is zero for exactly those two codes: (that | 0x80) - 1 keeps bit 7 of every other byte, without
+// borrowing across bytes, and the AND over a lane's words says whether any of its elements needs the second look.
+// kLegacy (the element-wise entry point): a NaN element also needs it (the reference's 0x30); there a running FP16
+// minimum that propagates NaN is the test, and code 0x7F counts as unsettled too.  The block codecs keep NaN on
+// the fast path (saturation code, sign of x).
 template <int NW, bool kLegacy = false>
 __device__ __forceinline__ void fp8_encode_words_ref(const uint32_t* raw, float inv, uint32_t* out) {
-  __half2 min_all = __half2half2(__ushort_as_half((unsigned short)0x7BFF));  // 65504
+  __half2 min_all = __half2half2(__ushort_as_half((unsigned short)0x7BFF));  // 65504; unused (and dropped) unless kLegacy
+  uint32_t all_settled = 0x80808080u;
 #pragma unroll
   for (int i = 0; i < NW / 2; ++i) {
     const uint32_t w0 = raw[2 * i], w1 = raw[2 * i + 1];
@@ -319,39 +324,35 @@ __device__ __forceinline__ void fp8_encode_words_ref(const uint32_t* raw, float 
     const uint32_t mag = __byte_perm(c01, c23, 0x5410);
     const uint32_t sgn = __byte_perm(w0, w1, 0x7531);  // high bytes of the four BF16
     out[i] = (mag & 0x7F7F7F7Fu) | (sgn & 0x80808080u);
+    if (!kLegacy) all_settled &= ((mag & 0x77777777u) | 0x80808080u) - 0x01010101u;
   }
-  // anything below 2^-6 (0x2400 in FP16)?  Zero counts: rare enough to be handled off the fast path.  The few
-  // elements concerned (zero, a magnitude under 2^-10 or in [7.5, 8) * 2^-9, and for the element-wise entry point
-  // NaN) are encoded again one by one with the exact restatement; every other byte of the fast path stands.
-  const __half thr = __ushort_as_half((unsigned short)0x2400);
-  const bool careful = kLegacy ? !__hge(__hmin_nan(__low2half(min_all), __high2half(min_all)), thr)
-                               : __hlt(__hmin(__low2half(min_all), __high2half(min_all)), thr);
+  // kLegacy: anything below 2^-6 (0x2400 in FP16), zero included, or NaN?
+  const bool careful = kLegacy ? !__hge(__hmin_nan(__low2half(min_all), __high2half(min_all)), __ushort_as_half((unsigned short)0x2400))
+                               : (all_settled & 0x80808080u) != 0x80808080u;
   if (careful) {
 #pragma unroll
     for (int i = 0; i < NW / 2; ++i) {
       uint32_t o = out[i];
-      // Only a byte whose fast code is 0x00 or 0x08 can differ from the reference's: the hardware path rounds a magnitude in
-      // [7.5, 8) * 2^-9 up to the smallest normal code where the reference clamps it to 7; a zero product keeps sign 0
-      // whatever the element's sign; and the float just under 2^-10 gives 1 in the reference's `v * 512 + 0.5f` where exact
-      // half-up rounding gives 0.  The sub-normal codes 1..7 agree for every fp32 magnitude.  (code & 0x77) is zero for
-      // exactly those two codes: (that | 0x80) - 1 keeps bit 7 for every other byte, without borrowing across bytes.
-      // The element-wise entry point also has to look at NaN elements, which carry code 0x7F.
       const uint32_t mag = o & 0x7F7F7F7Fu;
       uint32_t settled = (((mag & 0x77777777u) | 0x80808080u) - 0x01010101u) & 0x80808080u;
       if (kLegacy) settled &= ~((mag + 0x01010101u) & 0x80808080u);
       if (settled == 0x80808080u) continue;
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        if (settled & (0x80u << (8 * k))) continue;
-        const uint32_t rw = raw[2 * i + (k >> 1)];
-        const float x = (k & 1) ? bf16hi(rw) : bf16lo(rw);
+      // A loop over the word's unsettled bytes with the exact restatement in its body: a loop is not turned into
+      // predicated code (as straight-line code the 32 copies of this arm were, and every warp that met one small
+      // element executed them all: 0.32 of the HBM rate on SwiGLU outputs), and a kernel without a call keeps its
+      // registers (with the restatement out of line: 0.77 on the same data against 0.82 this way).
+      uint32_t todo = (~settled >> 7) & 0x01010101u;   // one bit per unsettled byte, at the byte's lowest bit
+      do {
+        const int b = __ffs(todo) - 1;                 // 0, 8, 16 or 24
+        todo &= todo - 1;
+        const uint32_t rw = (b & 16) ? raw[2 * i + 1] : raw[2 * i];
+        const float x = (b & 8) ? bf16hi(rw) : bf16lo(rw);
         const float y = __fmul_rn(fabsf(x), inv);
-        const bool redo = kLegacy ? !(y >= 0.015625f) : (y < 0.015625f);
-        // out of line on purpose: in line, the compiler predicates all 32 copies of the arm and every warp that meets
-        // one small element executes them all (measured: 0.32 of the HBM rate on SwiGLU outputs against 0.7); walking
-        // the unsettled bytes with a loop and a cheaper helper for the small magnitudes measured slower as well
-        if (redo) o = (o & ~(0xFFu << (8 * k))) | (fp8_encode_exact<kLegacy>(x, inv) << (8 * k));
-      }
+        if (kLegacy ? !(y >= 0.015625f) : (y < 0.015625f)) {
+          const uint32_t code = kLegacy ? fp8_encode_legacy(x, inv) : fp8_encode_ref_scaled(x, inv);
+          o = (o & ~(0xFFu << b)) | (code << b);
+        }
+      } while (todo);
       out[i] = o;
     }
   }
