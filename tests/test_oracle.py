@@ -220,6 +220,21 @@ def test_int8_kernel_quotient_shortcut_is_exact(tmp_path):
     assert checked > 10_000_000 and bad == 0
 
 
+def test_fp8_hardware_path_differs_from_the_reference_only_at_codes_00_and_08(tmp_path):
+    """The FP8 compress kernel converts on the conversion hardware and encodes again, exactly, only elements whose
+    code came out as 0x00 or 0x08.  Host model of that path against the oracle: every binary32 magnitude in
+    [2^-20, 2^-5) and a sparse sweep over all others."""
+    here = os.path.dirname(__file__)
+    exe = str(tmp_path / "fp8_fast_path_check")
+    subprocess.run(["gcc", "-O2", "-ffp-contract=off", "-o", exe, os.path.join(here, "helpers", "fp8_fast_path_check.c"),
+                    os.path.join(os.path.dirname(here), "oracle", "codec_oracle.c"), "-lm", "-lpthread"], check=True)
+    r = subprocess.run([exe, "257"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    checked, unexpected, at_08, at_00 = map(int, r.stdout.split())
+    assert checked > 130_000_000 and unexpected == 0
+    assert at_08 >= 1 << 20 and at_00 == 1      # [7.5, 8) * 2^-9, and the float just under 2^-10
+
+
 def test_restatements_agree_on_random_magnitude_spread():
     """C and numpy restatements on blocks whose magnitudes span the BF16 range (seeded)."""
     rng = np.random.default_rng(7)
