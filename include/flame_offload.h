@@ -110,6 +110,10 @@ int flame_fused_dequant_transpose_bf16_multi(const FlameWeightJob* jobs, int cou
  *    Returns 0 or a cudaError_t value; cudaErrorInvalidValue (1) for NULL
  *    pointers with n > 0.  Any pointer alignment is accepted (32-byte aligned
  *    BF16 buffers and 16-byte aligned code/scale buffers take the fast kernels).
+ *    Each call is a few kernel launches on `stream` and nothing else (no
+ *    allocation, no synchronisation), so the calls can be recorded in a CUDA
+ *    graph; call each entry point once on the device before the capture, so
+ *    that the runtime has loaded the kernels.
  * ---------------------------------------------------------------------- */
 #define FLAME_ACT_BLOCK 128
 #define FLAME_ACT_INT8_MUL_INV 1u /* int8: code = rne(x * (1/scale)) instead of the division */

@@ -519,3 +519,41 @@ def test_more_than_2_to_the_32_elements_in_one_call(cuda_device, codec):
         sc = scales[lo // 128: hi // 128]
         bound = sc if codec == "int8" else sc * 448.0 * 0.53
         assert bool((err <= bound).all()), lo
+
+
+@pytest.mark.parametrize("codec", ["int8", "fp8"])
+def test_codec_launches_replay_from_a_cuda_graph(cuda_device, codec):
+    """The codec entry points are plain launches on the caller's stream: compress + dequantise captured once in a CUDA
+    graph and replayed on new contents of the same buffers give the oracle's bytes for the new contents."""
+    lib = _lib.lib()
+    n = (1 << 21) + 128 * 5          # full tiles and a ragged one
+    rng_bits = [synthetic.normal_with_outliers(n, seed) for seed in (21, 22)]
+    x = G.to_dev(rng_bits[0], cuda_device)
+    codes = torch.empty(n, dtype=torch.uint8, device=cuda_device)
+    scales = torch.empty(n // 128, dtype=torch.float32, device=cuda_device)
+    out = torch.empty(n, dtype=torch.bfloat16, device=cuda_device)
+    quant = getattr(lib, f"flame_act_quant_{codec}_b128")
+    dequant = getattr(lib, f"flame_act_dequant_{codec}_b128")
+    side = torch.cuda.Stream(device=cuda_device)
+    side.wait_stream(torch.cuda.current_stream(cuda_device))
+    with torch.cuda.stream(side):     # first use outside the capture: module loading and the occupancy query happen here
+        assert quant(x.data_ptr(), codes.data_ptr(), scales.data_ptr(), n, 0, side.cuda_stream) == 0
+        assert dequant(codes.data_ptr(), scales.data_ptr(), out.data_ptr(), n, side.cuda_stream) == 0
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        sp = torch.cuda.current_stream(cuda_device).cuda_stream
+        assert quant(x.data_ptr(), codes.data_ptr(), scales.data_ptr(), n, 0, sp) == 0
+        assert dequant(codes.data_ptr(), scales.data_ptr(), out.data_ptr(), n, sp) == 0
+    q_oracle = capi.quant_int8_b128 if codec == "int8" else capi.quant_fp8_b128
+    d_oracle = capi.dequant_int8_b128 if codec == "int8" else capi.dequant_fp8_b128
+    for bits in (rng_bits[1], rng_bits[0]):
+        x.copy_(G.to_dev(bits, cuda_device))
+        codes.zero_(); scales.zero_(); out.zero_()
+        torch.cuda.synchronize(cuda_device)
+        graph.replay()
+        torch.cuda.synchronize(cuda_device)
+        wc, ws = q_oracle(bits)
+        assert np.array_equal(codes.cpu().numpy(), wc.view(np.uint8))
+        assert np.array_equal(scales.cpu().numpy().view(np.uint32), ws.view(np.uint32))
+        assert np.array_equal(G.bits_of(out), d_oracle(wc, ws))
