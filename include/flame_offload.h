@@ -80,10 +80,10 @@ int flame_fp8_to_bf16(const void* input_u8, void* output_bf16, float scale, size
 int flame_fused_dequant_transpose_bf16(const void* input_fp8, void* output_bf16, float scale, int M, int N, void* stream);
 
 /* The same for several weights in one launch (new): what a block of a model needs expanded once its bytes have
- * arrived.  The reference calls its kernel once per weight (src/ops/fused_inference.rs:140-175); a block's four to
- * eight weights of 10-60 M elements each then start and drain the GPU once per weight.  Every job has the meaning
- * of one flame_fused_dequant_transpose_bf16 call; jobs with M == 0 or N == 0 are skipped; a job that misses the
- * fast kernel's conditions gets a launch of its own.  Outputs must not overlap each other or any input.
+ * arrived.  The reference calls its kernel once per weight (src/ops/fused_inference.rs:140-175); here the caller makes
+ * one call, and the library one launch, for a block's four to eight weights.  Every job has the meaning of one
+ * flame_fused_dequant_transpose_bf16 call; jobs with M == 0 or N == 0 are skipped; a job that misses the fast
+ * kernel's conditions gets a launch of its own.  Outputs must not overlap each other or any input.
  * count <= 0 returns 0 at once. */
 typedef struct FlameWeightJob {
   const void* input_fp8;   /* [M, N] row-major E4M3 codes */
