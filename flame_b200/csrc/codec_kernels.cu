@@ -560,6 +560,7 @@ struct CompressForm {
 template <int kCodec, bool kFlag, bool kStaged, int kForm>
 __global__ void __launch_bounds__(kThreads, CompressForm<kForm>::kMinBlocks)
 compress_b128_kernel(const __grid_constant__ JobTable T, unsigned rounds, unsigned multi_ctas, unsigned multi_tiles) {
+  pdl_prologue();
   // staged variant only: two slices of (codes | scales) per warp in dynamic shared memory
   extern __shared__ __align__(128) uint8_t smem_tiles[];
   constexpr bool kPipelined = CompressForm<kForm>::kPipelined;
@@ -701,6 +702,7 @@ __device__ __forceinline__ uint16_t decode1(uint8_t c, float scale) {
 template <int kCodec>
 __global__ void __launch_bounds__(kThreads, 5)
 dequant_b128_kernel(const __grid_constant__ JobTable T, unsigned rounds) {
+  pdl_prologue();
   constexpr int kDU = kDequantUnroll;
   const int tid = threadIdx.x;
   uint32_t j = 0;
@@ -962,8 +964,7 @@ cudaError_t launch_compress_kernel(const JobTable& T, cudaStream_t stream, int m
     ctas = multi_ctas + (unsigned)singles;
   }
   g_last_launch = {(int)ctas, per_sm, (int)g.tiles_per_cta, kForm | (kStaged ? 4 : 0)};
-  kern<<<ctas, kThreads, smem, stream>>>(T, g.tiles_per_cta, multi_ctas, multi_tiles);
-  return cudaGetLastError();
+  return launch_after(kern, ctas, kThreads, smem, stream, T, (unsigned)g.tiles_per_cta, multi_ctas, multi_tiles);
 }
 
 // Which form of the kernel a codec takes (defaults measured on a B200; FLAME_ACT_COMPRESS_FORM=0/1/2 or
@@ -1049,13 +1050,13 @@ cudaError_t launch_dequant_multi(int codec, const TensorJob* jobs, size_t count,
       const int per_sm = resident_ctas_per_sm(reinterpret_cast<const void*>(kern));
       const Grid g = grid_balanced(T.total_tiles, per_sm, max_ctas, 2, 2);
       g_last_launch = {g.ctas, per_sm, (int)g.tiles_per_cta, 0};
-      kern<<<g.ctas, kThreads, 0, stream>>>(T, g.tiles_per_cta);
+      { const cudaError_t e = launch_after(kern, (unsigned)g.ctas, kThreads, 0, stream, T, (unsigned)g.tiles_per_cta); if (e != cudaSuccess) return e; }
     } else {
       auto kern = dequant_b128_kernel<kCodecFp8>;
       const int per_sm = resident_ctas_per_sm(reinterpret_cast<const void*>(kern));
       const Grid g = grid_balanced(T.total_tiles, per_sm, max_ctas, 2, 2);
       g_last_launch = {g.ctas, per_sm, (int)g.tiles_per_cta, 0};
-      kern<<<g.ctas, kThreads, 0, stream>>>(T, g.tiles_per_cta);
+      { const cudaError_t e = launch_after(kern, (unsigned)g.ctas, kThreads, 0, stream, T, (unsigned)g.tiles_per_cta); if (e != cudaSuccess) return e; }
     }
     T.count = 0; T.total_tiles = 0;
     return cudaGetLastError();

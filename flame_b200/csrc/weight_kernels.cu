@@ -112,6 +112,7 @@ struct WeightJobs {
 
 __global__ void __launch_bounds__(kWThreads, 6)
 fp8_dequant_transpose_tiles_kernel(const __grid_constant__ WeightJobs T) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31, rg = lane >> 2, cg = lane & 3;
   const uint32_t warp0 = blockIdx.x * (kWThreads / 32) + (threadIdx.x >> 5);
   const uint32_t nwarps = gridDim.x * (kWThreads / 32);
@@ -209,9 +210,9 @@ cudaError_t launch_fp8_dequant_transpose_jobs(const FlameWeightJob* jobs, int co
     const uint64_t rounds = (tiles + cap * warps_per_block - 1) / (cap * warps_per_block);
     uint64_t grid = (tiles + rounds * warps_per_block - 1) / (rounds * warps_per_block);
     if (grid > cap) grid = cap;
-    fp8_dequant_transpose_tiles_kernel<<<(unsigned)grid, kWThreads, 0, stream>>>(T);
+    const cudaError_t e = launch_after(fp8_dequant_transpose_tiles_kernel, (unsigned)grid, kWThreads, 0, stream, T);
     T.count = 0;
-    return cudaGetLastError();
+    return e;
   };
   for (int i = 0; i < count; ++i) {
     const int M = jobs[i].M, N = jobs[i].N;

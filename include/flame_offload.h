@@ -113,7 +113,12 @@ int flame_fused_dequant_transpose_bf16_multi(const FlameWeightJob* jobs, int cou
  *    Each call is a few kernel launches on `stream` and nothing else (no
  *    allocation, no synchronisation), so the calls can be recorded in a CUDA
  *    graph; call each entry point once on the device before the capture, so
- *    that the runtime has loaded the kernels.
+ *    that the runtime has loaded the kernels.  The fast kernels (and the FP8
+ *    weight kernel above) are launched with programmatic stream serialisation
+ *    and wait inside the kernel for whatever precedes them in the stream, so
+ *    that one of them directly behind another starts without a launch's
+ *    start-up time; stream order and results are unchanged.  The environment
+ *    variable FLAME_ACT_PDL=0 makes them plain launches.
  * ---------------------------------------------------------------------- */
 #define FLAME_ACT_BLOCK 128
 #define FLAME_ACT_INT8_MUL_INV 1u /* int8: code = rne(x * (1/scale)) instead of the division */

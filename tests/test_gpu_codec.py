@@ -122,6 +122,50 @@ def test_each_kernel_is_sized_by_its_own_occupancy(cuda_device, order):
     assert got["fp8"]["fresh"] == lib.flame_act_query_resident_blocks(3, 0, -1, 1)
 
 
+_BACK_TO_BACK_SCRIPT = r"""
+import sys, hashlib
+import numpy as np, torch
+sys.path.insert(0, {root!r})
+from flame_b200 import _lib, synthetic
+lib = _lib.lib()
+torch.cuda.set_device(0)
+n = (1 << 23) + 128 * 3
+h = hashlib.sha256()
+xs = [torch.from_numpy(synthetic.normal_with_outliers(n, seed).view(np.int16)).cuda().view(torch.bfloat16) for seed in (1, 2, 3)]
+codes = [torch.empty(n, dtype=torch.uint8, device="cuda") for _ in xs]
+scales = [torch.empty((n + 127) // 128, dtype=torch.float32, device="cuda") for _ in xs]
+outs = [torch.empty_like(x) for x in xs]
+for codec in ("int8", "fp8"):
+    q, d = getattr(lib, "flame_act_quant_%s_b128" % codec), getattr(lib, "flame_act_dequant_%s_b128" % codec)
+    for rep in range(3):                       # kernels directly behind one another in one stream, each reading what the last wrote
+        for x, c, s, o in zip(xs, codes, scales, outs):
+            assert q(x.data_ptr(), c.data_ptr(), s.data_ptr(), n, 0, None) == 0
+            assert d(c.data_ptr(), s.data_ptr(), o.data_ptr(), n, None) == 0
+            assert q(o.data_ptr(), c.data_ptr(), s.data_ptr(), n, 0, None) == 0      # codes of the restored tensor
+    torch.cuda.synchronize()
+    for t in codes + scales + outs:
+        h.update(t.view(torch.uint8).cpu().numpy().tobytes())
+print(h.hexdigest())
+"""
+
+
+def test_kernels_behind_one_another_give_the_same_bytes_with_and_without_the_launch_attribute(cuda_device):
+    """The fast kernels are launched with programmatic stream serialisation and wait inside the kernel for their
+    predecessors.  A chain in which every kernel reads what the one before it wrote gives the same bytes as the same
+    chain with plain launches (FLAME_ACT_PDL=0)."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    digests = []
+    for pdl in ("1", "0"):
+        env = dict(os.environ, FLAME_ACT_PDL=pdl)
+        r = subprocess.run([sys.executable, "-c", _BACK_TO_BACK_SCRIPT.format(root=root)], capture_output=True, text=True, timeout=600, env=env)
+        assert r.returncode == 0, r.stderr[-2000:]
+        digests.append(r.stdout.strip().splitlines()[-1])
+    assert digests[0] == digests[1]
+
+
 def test_empty_input_is_a_no_op(cuda_device):
     lib = _lib.lib()
     assert lib.flame_act_quant_int8_b128(None, None, None, 0, 0, None) == 0
