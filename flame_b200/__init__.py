@@ -22,6 +22,7 @@ from .activation_offload import (  # noqa: F401
     Unsupported,
     CudaError,
 )
+from .errors import InvalidShape  # noqa: F401
 
 from .block_offload import BlockOffloader  # noqa: F401,E402
 
@@ -29,5 +30,5 @@ __all__ = [
     "BlockOffloader",
     "PinnedAllocFlags", "PinnedHostBuffer", "StagingDeviceBuf", "PinnedPool",
     "ActivationOffloadPool", "OffloadCompression", "OffloadHandle",
-    "OffloadError", "InvalidInput", "InvalidOperation", "Unsupported", "CudaError",
+    "OffloadError", "InvalidInput", "InvalidOperation", "InvalidShape", "Unsupported", "CudaError",
 ]

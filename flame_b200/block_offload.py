@@ -21,7 +21,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Mapping, Optional, Sequence
 
-from . import _lib
+from . import _lib, fused_inference
 from .activation_offload import ActivationOffloadPool, OffloadCompression
 from .errors import CudaError, InvalidInput, InvalidOperation, Unsupported
 
@@ -168,8 +168,6 @@ class BlockOffloader:
         buf = self._bufs[slot]
         torch = self._torch
         out, eoff = {}, 0
-        lib = _lib.lib()
-        stream = torch.cuda.current_stream(self.device).cuda_stream
         jobs = []          # the block's transposed FP8 weights: one launch for all of them
         for name, shape, dtype, off, nbytes in self._layout[idx]:
             if dtype != torch.uint8:
@@ -182,17 +180,20 @@ class BlockOffloader:
             m, n = shape
             dst = self._expanded[slot][eoff:eoff + 2 * nbytes].view(torch.bfloat16)
             eoff += (2 * nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
-            if transpose:
-                jobs.append(_lib.WeightJob(buf.data_ptr() + off, dst.data_ptr(), float(scale), m, n, 0))
-            else:
-                rc = lib.flame_fp8_to_bf16(buf.data_ptr() + off, dst.data_ptr(), float(scale), m * n, stream)
-                if rc != 0:
-                    raise CudaError(f"BlockOffloader: FP8 weight expansion of {name} failed ({rc}): {_lib.last_error()}")
+            codes = buf[off:off + nbytes]
+            try:
+                if transpose:
+                    jobs.append((codes, scale, dst, m, n))
+                else:
+                    fused_inference.dequant_fp8_to_bf16_into(codes, scale, dst)
+            except CudaError as exc:
+                raise CudaError(f"BlockOffloader: FP8 weight expansion of {name} failed: {exc}; {_lib.last_error()}") from exc
             out[name] = dst.view(n, m) if transpose else dst.view(m, n)
         if jobs:
-            rc = lib.flame_fused_dequant_transpose_bf16_multi((_lib.WeightJob * len(jobs))(*jobs), len(jobs), stream)
-            if rc != 0:
-                raise CudaError(f"BlockOffloader: FP8 weight expansion of block {idx} failed ({rc}): {_lib.last_error()}")
+            try:
+                fused_inference.dequant_fp8_transpose_many(jobs)
+            except CudaError as exc:
+                raise CudaError(f"BlockOffloader: FP8 weight expansion of block {idx} failed: {exc}; {_lib.last_error()}") from exc
         return out
 
     def ensure_block(self, idx: int) -> Dict[str, "object"]:

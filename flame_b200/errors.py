@@ -13,6 +13,10 @@ class InvalidOperation(OffloadError):
     """Error::InvalidOperation: pool full, stale handle, slot out of range, double pull."""
 
 
+class InvalidShape(OffloadError):
+    """Error::InvalidShape: an output tensor whose element count does not match the weight."""
+
+
 class Unsupported(OffloadError):
     """Error::Unsupported: dtype the path does not move, compression of a non-BF16 tensor."""
 

@@ -114,3 +114,41 @@ def test_equals_the_reference_kernel_on_this_gpu(cuda_device):
             torch.cuda.synchronize()
             got = _run(lib, codes, sc, m, n, cuda_device)
             assert np.array_equal(got, want.cpu().numpy().view(np.uint16).reshape(n, m)), (m, n, sc)
+
+
+def test_host_functions_of_the_inference_path(cuda_device):
+    """dequant_fp8_to_bf16 / _into / dequant_fp8_transpose_into / _many (src/ops/fused_inference.rs:86-185) over torch
+    tensors: the oracle's bytes, the reference's shape error, nothing allocated by the `_into` forms."""
+    from flame_b200 import InvalidInput, InvalidShape, fused_inference as fi
+
+    rng = np.random.default_rng(3)
+    m, n, scale = 72, 104, 0.37
+    codes = rng.integers(0, 256, size=(m, n), dtype=np.uint8)
+    dev_codes = torch.from_numpy(codes).to(cuda_device)
+    want_t = capi.fp8_dequant_transpose(codes, scale, m, n)
+    want = capi.fp8_to_bf16(codes.reshape(-1), scale).reshape(m, n)                 # the element-wise decoder, src/cuda/fp8_dequant.cu
+    out_t = torch.empty(n, m, dtype=torch.bfloat16, device=cuda_device)
+    fi.dequant_fp8_transpose_into(dev_codes, scale, out_t, m, n)
+    plain = fi.dequant_fp8_to_bf16(dev_codes, scale, (m, n))
+    into = torch.empty(m, n, dtype=torch.bfloat16, device=cuda_device)
+    torch.cuda.synchronize(cuda_device)
+    before = torch.cuda.memory_allocated(cuda_device)
+    fi.dequant_fp8_to_bf16_into(dev_codes, scale, into)
+    fi.dequant_fp8_transpose_into(dev_codes, scale, out_t, m, n)
+    assert torch.cuda.memory_allocated(cuda_device) == before
+    torch.cuda.synchronize(cuda_device)
+    assert np.array_equal(out_t.view(torch.int16).cpu().numpy().view(np.uint16), want_t)
+    assert np.array_equal(plain.view(torch.int16).cpu().numpy().view(np.uint16), want)
+    assert torch.equal(plain.view(torch.int16), into.view(torch.int16))
+    outs = [torch.empty(n, m, dtype=torch.bfloat16, device=cuda_device) for _ in range(3)]
+    fi.dequant_fp8_transpose_many([(dev_codes, scale, o, m, n) for o in outs])
+    fi.dequant_fp8_transpose_many([])
+    torch.cuda.synchronize(cuda_device)
+    for o in outs:
+        assert torch.equal(o.view(torch.int16), out_t.view(torch.int16))
+    with pytest.raises(InvalidShape, match=r"expected %d \(N=%d x M=%d\)" % (m * n, n, m)):
+        fi.dequant_fp8_transpose_into(dev_codes, scale, torch.empty(n, m + 1, dtype=torch.bfloat16, device=cuda_device), m, n)
+    with pytest.raises(InvalidInput):
+        fi.dequant_fp8_transpose_into(dev_codes.to(torch.int32), scale, out_t, m, n)
+    with pytest.raises(InvalidInput):
+        fi.dequant_fp8_to_bf16_into(dev_codes, scale, torch.empty(m, n, dtype=torch.float32, device=cuda_device))
