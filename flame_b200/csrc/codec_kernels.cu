@@ -1278,8 +1278,10 @@ cudaError_t launch_bf16_to_fp8(const void* in, void* out, float inv_scale, size_
   auto* i = static_cast<const uint16_t*>(in);
   auto* o = static_cast<uint8_t*>(out);
   if (aligned(in, 32) && aligned(out, 16)) {
-    const int grid = grid_for((n / kLaneElems + kThreads - 1) / kThreads + 1, 8, max_ctas);
-    bf16_to_fp8_vec_kernel<<<grid, kThreads, 0, stream>>>(i, o, inv_scale, n);
+    // as for the block codecs: a few rounds per thread block instead of hundreds of rounds of a fixed grid
+    const int per_sm = resident_ctas_per_sm(reinterpret_cast<const void*>(bf16_to_fp8_vec_kernel));
+    const Grid g = grid_balanced((n / kLaneElems + kThreads - 1) / kThreads + 1, per_sm, max_ctas, 8, 6);
+    bf16_to_fp8_vec_kernel<<<g.ctas, kThreads, 0, stream>>>(i, o, inv_scale, n);
   } else {
     const int grid = grid_for((n + kThreads - 1) / kThreads, 8, max_ctas);
     bf16_to_fp8_scalar_kernel<<<grid, kThreads, 0, stream>>>(i, o, inv_scale, n);
@@ -1292,8 +1294,9 @@ cudaError_t launch_fp8_to_bf16(const void* in, void* out, float scale, size_t n,
   auto* i = static_cast<const uint8_t*>(in);
   auto* o = static_cast<uint16_t*>(out);
   if (aligned(in, 16) && aligned(out, 32)) {
-    const int grid = grid_for((n / kLaneElems + kThreads - 1) / kThreads + 1, 8, max_ctas);
-    fp8_to_bf16_vec_kernel<<<grid, kThreads, 0, stream>>>(i, o, scale, n);
+    const int per_sm = resident_ctas_per_sm(reinterpret_cast<const void*>(fp8_to_bf16_vec_kernel));
+    const Grid g = grid_balanced((n / kLaneElems + kThreads - 1) / kThreads + 1, per_sm, max_ctas, 2, 2);
+    fp8_to_bf16_vec_kernel<<<g.ctas, kThreads, 0, stream>>>(i, o, scale, n);
   } else {
     const int grid = grid_for((n + kThreads - 1) / kThreads, 8, max_ctas);
     fp8_to_bf16_scalar_kernel<<<grid, kThreads, 0, stream>>>(i, o, scale, n);
